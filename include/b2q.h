@@ -1,0 +1,212 @@
+/* b2q.h — C ABI of libb2q.so: B200 (sm_100a) quantized-linear hot path.
+ *
+ * Every entry point takes raw DEVICE pointers and plain integers, launches on the
+ * CUDA stream it is given (a cudaStream_t passed as void*; NULL = legacy default
+ * stream), never synchronises the host, never allocates, never throws and never
+ * aborts.  The return value is 0 on success or a negative B2Q_ERR_* code; a
+ * message is available from b2q_strerror().  Nothing is retained past the call.
+ *
+ * Each group below cites the interface of intel/llm-scaler's
+ * vllm/custom-esimd-kernels-vllm package (paths relative to that directory)
+ * that it replaces.  The torch custom-op layer in
+ * custom_esimd_kernels_vllm/_register.py binds these symbols through ctypes
+ * under the reference's own schema strings.
+ */
+#ifndef B2Q_H_
+#define B2Q_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define B2Q_API __attribute__((visibility("default")))
+#else
+#define B2Q_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------- */
+#define B2Q_OK                 0
+#define B2Q_ERR_NULL          -1  /* a required pointer is NULL                     */
+#define B2Q_ERR_SHAPE         -2  /* a dimension violates the op's contract         */
+#define B2Q_ERR_DTYPE         -3  /* unknown / unsupported element type code        */
+#define B2Q_ERR_ALIGN         -4  /* a pointer or pitch is not 16-byte aligned      */
+#define B2Q_ERR_LAYOUT        -5  /* unknown / unsupported weight layout code       */
+#define B2Q_ERR_UNSUPPORTED   -6  /* valid request with no kernel behind it yet     */
+#define B2Q_ERR_CUDA          -7  /* a CUDA runtime / driver call failed            */
+#define B2Q_ERR_WORKSPACE     -8  /* caller-provided workspace is too small         */
+#define B2Q_ERR_TIMEOUT       -9  /* a bounded device-side wait expired             */
+#define B2Q_ERR_LIMIT        -10  /* size exceeds a fixed built-in capacity         */
+
+/* ---- element types of activations / outputs / scales -------------------- */
+#define B2Q_BF16 0
+#define B2Q_F16  1
+#define B2Q_F32  2
+
+/* ---- INT4 weight layouts (value = (q - 8) * scale, q in [0,15]) ---------
+ * NMAJOR        int32 [N, K/8] == uint8 [N, K/2]; nibble i of a word (bits
+ *               4i..4i+3) is k = 8*word + i ("low nibble = even k").
+ *               Scales [N, K/g].              (csrc/xpu/q4_0_quant.sycl:9-13)
+ * KMAJOR        int32 [K/8, N] contiguous, same nibble order; scales [K/g, N]
+ *               (GPTQ / oneDNN view materialised; tests/test_moe_int4_kernel.py:384-396)
+ * KMAJOR_MARLIN int32 [K/8, N] with nibbles shuffled [0,4,1,5,2,6,3,7]; scales
+ *               [K/g, N]  (csrc/moe_prefill/moe_prefill_int4.sycl:128-137)
+ * NMAJOR_S4     uint8 [N, K/2] two's-complement nibbles (value = s4 * scale)
+ *               (csrc/moe_batch/int4_nmajor_gemm.h:137)
+ */
+#define B2Q_W4_NMAJOR        0
+#define B2Q_W4_KMAJOR        1
+#define B2Q_W4_KMAJOR_MARLIN 2
+#define B2Q_W4_NMAJOR_S4     3
+
+/* ---- FP8 formats and scale granularities -------------------------------- */
+#define B2Q_E4M3 0
+#define B2Q_E5M2 1
+#define B2Q_SCALE_CHANNEL  0   /* one scale per output row n:  [N]           */
+#define B2Q_SCALE_TENSOR   1   /* one fp32 scalar, read on the device        */
+#define B2Q_SCALE_BLOCK128 2   /* fp32 [ceil(N/128), ceil(K/128)]            */
+
+/* ---- activation functions fused into grouped GEMM epilogues ------------- */
+#define B2Q_ACT_NONE      0
+#define B2Q_ACT_SILU_MUL  1    /* out[:, j] = silu(g[:, j]) * g[:, I + j]    */
+
+B2Q_API const char* b2q_strerror(int code);
+B2Q_API int b2q_version(void);
+/* Compute capability check of the current device: 0 when it is sm_100. */
+B2Q_API int b2q_device_ok(void);
+
+/* ---- dequantisation (the bit-exactness gate) ----------------------------
+ * out[N, K] (row-major, out_dtype) = round_to_out_dtype((q - 8) * scale).
+ * Restates the unpack contract of tests/test_gemv_int4.py:172-210 and
+ * tests/test_moe_int4_kernel.py:68-83.                                        */
+B2Q_API int b2q_dequant_int4(const void* w, int w_layout, const void* scale, int scale_dtype,
+                     void* out, int out_dtype, int64_t N, int64_t K, int group,
+                     void* stream);
+/* out[N, K] = decode(w[n,k]) * scale (fp32 math, one rounding to out_dtype).
+ * tests/test_fp8_blockscale_gemm.py:31-36; patch test at
+ * vllm/patches/vllm_for_multi_arc.patch:477-580.                              */
+B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, int scale_dtype,
+                    int scale_mode, void* out, int out_dtype, int64_t N, int64_t K,
+                    void* stream);
+
+/* ---- dense weight-only linear: out[M, N] = x[M, K] * dequant(W)[N, K]^T --
+ * fp32 accumulate, one rounding to act_dtype (x and out share act_dtype).
+ * Replaces esimd_gemv_int4 / esimd_gemm_int4_pgrp
+ * (csrc/xpu/torch_extension.cc:53-55, csrc/xpu/torch_extension_gemm.cc:20-22;
+ *  kernels csrc/xpu/esimd_kernels/int4_GEMV.h:165-304, int4_GEMM.h:81-320).
+ * Any M >= 1.  K % group == 0, group == 128, K % 8 == 0.
+ * scale strides are in elements: scale(n, kg) = scale[n*s_stride_n + kg*s_stride_g].
+ * ldx / ldo are row pitches of x / out in elements.                           */
+B2Q_API int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx,
+                    const void* w, int w_layout,
+                    const void* scale, int scale_dtype, int64_t s_stride_n, int64_t s_stride_g,
+                    void* out, int64_t ldo,
+                    int64_t M, int64_t N, int64_t K, int group, void* stream);
+
+/* Replaces esimd_gemv_fp8_pern / esimd_gemv_fp8_pert / esimd_gemm_fp8_pert /
+ * esimd_gemm_fp8_blockscale (csrc/xpu/torch_extension.cc:9-37,
+ * csrc/xpu/torch_extension_gemm.cc:14-28; kernels fp8_GEMV_v2.h:46-403,
+ * fp8_GEMM_pert.h:4030-4075, fp8_GEMM_blockscale.h:64-223).
+ * w is [N, K] one byte per element, row-major.  Activation stays 16-bit
+ * (w8a16); e4m3 decode is exact including subnormals.  K % 16 == 0.           */
+B2Q_API int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx,
+                   const void* w, int fp8_format,
+                   const void* scale, int scale_dtype, int scale_mode,
+                   void* out, int64_t ldo,
+                   int64_t M, int64_t N, int64_t K, void* stream);
+
+/* Per-token, per-128-column dynamic e4m3 quantisation of activations:
+ * xs[m, kb] = max(amax(x[m, 128kb:128kb+128]), 1e-12) / 448 ; xq = e4m3(x / xs).
+ * (the (1,128) dynamic activation key of
+ *  vllm/patches/vllm_for_multi_arc.patch:2628-2634)                           */
+B2Q_API int b2q_act_quant_fp8_1x128(const void* x, int act_dtype, int64_t ldx,
+                            void* xq, float* xs, int64_t M, int64_t K, void* stream);
+
+/* W8A8 block-scaled GEMM: out = dq(xq, xs) * dq(w, ws)^T, e4m3 x e4m3 tensor
+ * cores, fp32 promotion per 128-deep K block.  Same weight contract as
+ * esimd_gemm_fp8_blockscale.  M, N arbitrary; K % 128 == 0.                   */
+B2Q_API int b2q_gemm_fp8_block_w8a8(const void* xq, const float* xs,
+                            const void* w, const float* ws,
+                            void* out, int out_dtype, int64_t ldo,
+                            int64_t M, int64_t N, int64_t K, void* stream);
+
+/* ---- MoE routing ---------------------------------------------------------
+ * softmax over E in fp32 -> top_k rounds of (max, lowest index among equal)
+ * -> optional renormalisation.  weights[T, k] in w_dtype, ids[T, k] int32.
+ * Replaces esimd_moe_topk / topk_v2 / moe_topk_int4 / moe_topk_softmax
+ * (csrc/xpu/esimd_kernels/moe_ops.h:106-231).  E <= 1024, top_k <= 32.         */
+B2Q_API int b2q_moe_topk(const void* logits, int logits_dtype, int64_t T, int E, int top_k,
+                 int renorm, void* weights, int w_dtype, int32_t* ids, void* stream);
+
+/* Counting sort of the T*k (token, slot) pairs by expert id; stable in pair
+ * index.  expert_offsets has E+1 entries (exclusive prefix, last = T*k);
+ * expert_tokens[pos] = pair index; pair_to_perm[pair] = pos (may be NULL);
+ * rows_per_expert[E] (may be NULL).  Replaces moe_prefill_gather_forward_v2
+ * (csrc/moe_prefill/moe_prefill_int4.sycl:40-106, 458-488) and the atomic
+ * scatter of moe_ops.h:437-569.  workspace: b2q_moe_route_workspace_bytes().   */
+B2Q_API size_t b2q_moe_route_workspace_bytes(int64_t n_pairs, int E);
+B2Q_API int b2q_moe_route(const int32_t* ids, int64_t n_pairs, int E,
+                  int32_t* expert_offsets, int32_t* expert_tokens,
+                  int32_t* pair_to_perm, int32_t* rows_per_expert,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+/* dst[r, :] = src[idx[r] / div, :] for r < rows (row gather; div = top_k maps
+ * pair index -> token).  Replaces moe_prefill_scatter_x_forward (:818-859).   */
+B2Q_API int b2q_gather_rows(const void* src, const int32_t* idx, int div, void* dst,
+                    int64_t rows, int64_t cols, int elem_bytes, void* stream);
+
+/* out[r, j] = silu(in[r, j]) * in[r, I + j], fp32 math.
+ * Replaces esimd_moe_silu_mul (moe_ops.h:576-621).                            */
+B2Q_API int b2q_silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, void* stream);
+
+/* out[t, :] = sum_s w[t, s] * y[perm ? perm[t*k+s] : t*k+s, :], fp32 sum.
+ * w_by_row != 0 reads the weight at the row position instead of at (t, s).
+ * Replaces moe_prefill_accumulate{,_permuted}_forward_v2 (:398-454) and
+ * esimd_moe_gather (moe_ops.h:627-676).                                       */
+B2Q_API int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int32_t* perm,
+                    void* out, int dtype, int64_t T, int top_k, int64_t H, int w_by_row, void* stream);
+
+/* ---- MoE grouped GEMMs ----------------------------------------------------
+ * Rows [expert_offsets[e], expert_offsets[e+1]) of the (virtual) expert-sorted
+ * input use expert e's weight.  If row_map != NULL the input row of sorted row
+ * r is x[row_map[r] / row_div]; otherwise it is x[r].  Output row r is written
+ * at out[out_map ? out_map[r] : r].  act = B2Q_ACT_SILU_MUL treats the weight
+ * as [gate rows ; up rows] (N = 2*I) and writes I columns.
+ * INT4: w is E stacked matrices in w_layout, scales E stacked.
+ * Replaces moe_prefill_up/down_forward_v2 (:493-621), moe_gemm_int4_nmajor
+ * (csrc/moe_batch/moe_int4.sycl:3373-3552).                                    */
+B2Q_API size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int act);
+B2Q_API int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx,
+                      const int32_t* row_map, int row_div,
+                      const void* w, int w_layout, const void* scale, int scale_dtype,
+                      const int32_t* expert_offsets, int E,
+                      void* out, int64_t ldo, const int32_t* out_map,
+                      int64_t rows, int64_t N, int64_t K, int group, int act,
+                      void* workspace, size_t workspace_bytes, void* stream);
+/* FP8 e4m3 [E, N, K] with scale_mode CHANNEL ([E,N] fp32), TENSOR ([E] fp32)
+ * or BLOCK128 ([E, ceil(N/128), ceil(K/128)] fp32).  Replaces
+ * esimd_moe_gemm_fp8{,_pert,_blockscale} (csrc/xpu/torch_extension_moe.cc:41-56).*/
+B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
+                     const int32_t* row_map, int row_div,
+                     const void* w, int fp8_format, const float* scale, int scale_mode,
+                     const int32_t* expert_offsets, int E,
+                     void* out, int64_t ldo, const int32_t* out_map,
+                     int64_t rows, int64_t N, int64_t K, int act,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Kernel selection override for benchmarking: 0 = automatic,
+ * 1 = force the mma.sync streaming kernel, 2 = force the tcgen05 kernel.     */
+B2Q_API void b2q_set_force_kernel(int which);
+/* Name of the kernel family the last b2q_linear_* / b2q_moe_gemm_* call on this
+ * thread launched ("smallm", "umma", ...).                                    */
+B2Q_API const char* b2q_last_kernel(void);
+/* Number of kernel launches issued by this library on this thread so far.     */
+B2Q_API uint64_t b2q_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2Q_H_ */

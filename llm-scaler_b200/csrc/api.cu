@@ -1,0 +1,374 @@
+// C ABI of libb2q.so: argument validation and kernel selection.  Nothing here
+// allocates or synchronises; every launch goes to the caller's stream.
+#include "common.cuh"
+#include "smallm.cuh"
+#include "umma_gemm.cuh"
+
+namespace b2q {
+
+ThreadState& tls() {
+  static thread_local ThreadState s;
+  return s;
+}
+
+// implemented in dequant.cu / moe_aux.cu
+int dequant_int4(const void*, int, const void*, int, void*, int, int64_t, int64_t, int, cudaStream_t);
+int dequant_fp8(const void*, int, const void*, int, int, void*, int, int64_t, int64_t, cudaStream_t);
+int moe_topk(const void*, int, int64_t, int, int, int, void*, int, int32_t*, cudaStream_t);
+size_t moe_route_workspace_bytes(int64_t, int);
+int moe_route(const int32_t*, int64_t, int, int32_t*, int32_t*, int32_t*, int32_t*, void*, cudaStream_t);
+int moe_build_tiles(const int32_t*, int, int, int32_t*, cudaStream_t);
+int gather_rows(const void*, const int32_t*, int, void*, int64_t, int64_t, int, cudaStream_t);
+int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t);
+int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
+int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Token-tile height of the streaming kernel's grouped mode, from the mean rows per expert.
+static inline int grouped_tile(int64_t rows, int E) {
+  const int64_t avg = E > 0 ? (rows + E - 1) / E : rows;
+  return avg <= 8 ? 8 : (avg <= 16 ? 16 : (avg <= 32 ? 32 : 64));
+}
+static inline size_t tile_list_bytes(int64_t rows, int E, int tile) {
+  return align_up(16 + 8 * (size_t)((rows + tile - 1) / tile + E), 256);
+}
+
+}  // namespace b2q
+
+using namespace b2q;
+
+extern "C" {
+
+const char* b2q_strerror(int code) {
+  switch (code) {
+    case B2Q_OK: return "ok";
+    case B2Q_ERR_NULL: return "b2q: a required pointer is NULL";
+    case B2Q_ERR_SHAPE: return "b2q: a dimension violates the op's contract";
+    case B2Q_ERR_DTYPE: return "b2q: unsupported element type";
+    case B2Q_ERR_ALIGN: return "b2q: pointer or row pitch is not 16-byte aligned";
+    case B2Q_ERR_LAYOUT: return "b2q: unsupported weight layout";
+    case B2Q_ERR_UNSUPPORTED: return "b2q: no kernel for this combination";
+    case B2Q_ERR_CUDA: return "b2q: CUDA call failed";
+    case B2Q_ERR_WORKSPACE: return "b2q: workspace too small";
+    case B2Q_ERR_TIMEOUT: return "b2q: bounded device-side wait expired";
+    case B2Q_ERR_LIMIT: return "b2q: size exceeds a built-in capacity";
+    default: return "b2q: unknown error code";
+  }
+}
+
+int b2q_version(void) { return 100; }
+
+int b2q_device_ok(void) {
+  int dev = 0, major = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return B2Q_ERR_CUDA;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return B2Q_ERR_CUDA;
+  return major == 10 ? B2Q_OK : B2Q_ERR_UNSUPPORTED;
+}
+
+void b2q_set_force_kernel(int which) { tls().force_kernel = which; }
+const char* b2q_last_kernel(void) { return tls().last_kernel; }
+uint64_t b2q_launch_count(void) { return tls().launches; }
+
+int b2q_dequant_int4(const void* w, int w_layout, const void* scale, int scale_dtype, void* out, int out_dtype,
+                     int64_t N, int64_t K, int group, void* stream) {
+  if (!w || !scale || !out) return B2Q_ERR_NULL;
+  if (w_layout < 0 || w_layout > 3) return B2Q_ERR_LAYOUT;
+  if (!is16(scale_dtype) && scale_dtype != B2Q_F32) return B2Q_ERR_DTYPE;
+  if (out_dtype < 0 || out_dtype > 2) return B2Q_ERR_DTYPE;
+  if (N < 0 || K < 0 || group <= 0 || (K % group) != 0 || (K % 8) != 0 || (group % 8) != 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(out) || !aligned16(w)) return B2Q_ERR_ALIGN;
+  if (N == 0 || K == 0) return B2Q_OK;
+  return dequant_int4(w, w_layout, scale, scale_dtype, out, out_dtype, N, K, group, (cudaStream_t)stream);
+}
+
+int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, int scale_dtype, int scale_mode, void* out,
+                    int out_dtype, int64_t N, int64_t K, void* stream) {
+  if (!w || !scale || !out) return B2Q_ERR_NULL;
+  if (fp8_format != B2Q_E4M3 && fp8_format != B2Q_E5M2) return B2Q_ERR_DTYPE;
+  if (scale_mode < 0 || scale_mode > 2) return B2Q_ERR_LAYOUT;
+  if (scale_dtype < 0 || scale_dtype > 2 || out_dtype < 0 || out_dtype > 2) return B2Q_ERR_DTYPE;
+  if (N < 0 || K < 0 || (K % 8) != 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(out) || (reinterpret_cast<uintptr_t>(w) & 7u)) return B2Q_ERR_ALIGN;
+  if (N == 0 || K == 0) return B2Q_OK;
+  return dequant_fp8(w, fp8_format, scale, scale_dtype, scale_mode, out, out_dtype, N, K, (cudaStream_t)stream);
+}
+
+int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, int w_layout, const void* scale,
+                    int scale_dtype, int64_t s_stride_n, int64_t s_stride_g, void* out, int64_t ldo, int64_t M,
+                    int64_t N, int64_t K, int group, void* stream) {
+  if (!x || !w || !scale || !out) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (scale_dtype < 0 || scale_dtype > 2) return B2Q_ERR_DTYPE;
+  if (w_layout < 0 || w_layout > 3) return B2Q_ERR_LAYOUT;
+  if (group != 128) return B2Q_ERR_SHAPE;
+  if (M < 0 || N < 0 || K <= 0 || (K % group) != 0 || ldx < K || ldo < N) return B2Q_ERR_SHAPE;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (!aligned16(x) || !aligned16(w) || ((ldx * 2) & 15)) return B2Q_ERR_ALIGN;
+  if (M == 0 || N == 0) return B2Q_OK;
+  const bool kmajor = (w_layout == B2Q_W4_KMAJOR || w_layout == B2Q_W4_KMAJOR_MARLIN);
+  cudaStream_t st = (cudaStream_t)stream;
+  const int force = tls().force_kernel;
+
+  UmmaW4Args ua{};
+  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16);
+  ua.w = w; ua.layout = w_layout; ua.scale = scale; ua.scale_dtype = scale_dtype;
+  ua.s_stride_n = s_stride_n; ua.s_stride_g = s_stride_g;
+  ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
+  const bool umma_ok = umma_w4_supported(ua);
+  const bool want_umma = force == 2 || (force == 0 && (kmajor || M > 32));
+  if (umma_ok && want_umma) return umma_w4_linear(ua, st);
+  if (kmajor) return B2Q_ERR_UNSUPPORTED;
+
+  SmallMParams p{};
+  p.x = x; p.ldx = ldx;
+  p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K / 2;
+  p.scale = scale; p.scale_dtype = scale_dtype; p.s_stride_n = s_stride_n; p.s_stride_g = s_stride_g;
+  p.out = out; p.ldo = ldo; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.xor_mask = (w_layout == B2Q_W4_NMAJOR_S4) ? 0x88888888u : 0u;
+  return smallm_int4(p, act_dtype == B2Q_BF16, (int)M, 0, st);
+}
+
+int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
+                   int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                   void* stream) {
+  if (!x || !w || !scale || !out) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (fp8_format != B2Q_E4M3 && fp8_format != B2Q_E5M2) return B2Q_ERR_DTYPE;
+  if (scale_mode < 0 || scale_mode > 2) return B2Q_ERR_LAYOUT;
+  if (scale_dtype < 0 || scale_dtype > 2) return B2Q_ERR_DTYPE;
+  if (scale_mode == B2Q_SCALE_BLOCK128 && (scale_dtype != B2Q_F32 || fp8_format != B2Q_E4M3)) return B2Q_ERR_DTYPE;
+  if (M < 0 || N < 0 || K <= 0 || (K % 16) != 0 || ldx < K || ldo < N) return B2Q_ERR_SHAPE;
+  if (scale_mode == B2Q_SCALE_BLOCK128 && (K % 128) != 0) return B2Q_ERR_SHAPE;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (!aligned16(x) || !aligned16(w) || ((ldx * 2) & 15)) return B2Q_ERR_ALIGN;
+  if (M == 0 || N == 0) return B2Q_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int force = tls().force_kernel;
+
+  UmmaW8Args ua{};
+  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16);
+  ua.w = w; ua.fmt = fp8_format; ua.scale = scale; ua.scale_dtype = scale_dtype; ua.scale_mode = scale_mode;
+  ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
+  const bool umma_ok = umma_w8_supported(ua);
+  const bool want_umma = force == 2 || (force == 0 && M > 16);
+  if (umma_ok && want_umma) return umma_w8_linear(ua, st);
+
+  SmallMParams p{};
+  p.x = x; p.ldx = ldx;
+  p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K;
+  p.scale = scale; p.scale_dtype = scale_dtype;
+  p.s_stride_n = (scale_mode == B2Q_SCALE_CHANNEL) ? 1 : 0;
+  p.out = out; p.ldo = ldo; p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  const int smode = scale_mode == B2Q_SCALE_BLOCK128 ? SM_BLOCK : SM_POST;
+  return act_dtype == B2Q_BF16 ? smallm_fp8_bf16(p, fp8_format, smode, (int)M, 0, st)
+                               : smallm_fp8_f16(p, fp8_format, smode, (int)M, 0, st);
+}
+
+int b2q_act_quant_fp8_1x128(const void* x, int act_dtype, int64_t ldx, void* xq, float* xs, int64_t M, int64_t K,
+                            void* stream) {
+  if (!x || !xq || !xs) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (M < 0 || K < 0 || (K % 128) != 0 || ldx < K) return B2Q_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(x) & 7u) || ((ldx * 2) & 7) || (reinterpret_cast<uintptr_t>(xq) & 3u)) return B2Q_ERR_ALIGN;
+  return act_quant_1x128(x, act_dtype, ldx, xq, xs, M, K, (cudaStream_t)stream);
+}
+
+int b2q_gemm_fp8_block_w8a8(const void* xq, const float* xs, const void* w, const float* ws, void* out, int out_dtype,
+                            int64_t ldo, int64_t M, int64_t N, int64_t K, void* stream) {
+  if (!xq || !xs || !w || !ws || !out) return B2Q_ERR_NULL;
+  if (!is16(out_dtype)) return B2Q_ERR_DTYPE;
+  if (M < 0 || N < 0 || K <= 0 || (K % 128) != 0 || ldo < N) return B2Q_ERR_SHAPE;
+  if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (!aligned16(xq) || !aligned16(w)) return B2Q_ERR_ALIGN;
+  if (M == 0 || N == 0) return B2Q_OK;
+  UmmaW8A8Args a{};
+  a.xq = xq; a.xs = xs; a.w = w; a.ws = ws; a.out = out; a.bf16 = (out_dtype == B2Q_BF16); a.ldo = ldo;
+  a.M = (int)M; a.N = (int)N; a.K = (int)K;
+  return umma_w8a8_block(a, (cudaStream_t)stream);
+}
+
+int b2q_moe_topk(const void* logits, int logits_dtype, int64_t T, int E, int top_k, int renorm, void* weights,
+                 int w_dtype, int32_t* ids, void* stream) {
+  if (!logits || !weights || !ids) return B2Q_ERR_NULL;
+  if (logits_dtype < 0 || logits_dtype > 2 || w_dtype < 0 || w_dtype > 2) return B2Q_ERR_DTYPE;
+  if (T < 0 || E <= 0 || top_k <= 0 || top_k > E) return B2Q_ERR_SHAPE;
+  if (E > 1024 || top_k > 32) return B2Q_ERR_LIMIT;
+  return moe_topk(logits, logits_dtype, T, E, top_k, renorm, weights, w_dtype, ids, (cudaStream_t)stream);
+}
+
+size_t b2q_moe_route_workspace_bytes(int64_t n_pairs, int E) { return moe_route_workspace_bytes(n_pairs, E); }
+
+int b2q_moe_route(const int32_t* ids, int64_t n_pairs, int E, int32_t* expert_offsets, int32_t* expert_tokens,
+                  int32_t* pair_to_perm, int32_t* rows_per_expert, void* workspace, size_t workspace_bytes,
+                  void* stream) {
+  if (!ids || !expert_offsets || !expert_tokens || !workspace) return B2Q_ERR_NULL;
+  if (n_pairs < 0 || E <= 0) return B2Q_ERR_SHAPE;
+  if (E > 1024 || n_pairs > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (workspace_bytes < moe_route_workspace_bytes(n_pairs, E)) return B2Q_ERR_WORKSPACE;
+  return moe_route(ids, n_pairs, E, expert_offsets, expert_tokens, pair_to_perm, rows_per_expert, workspace,
+                   (cudaStream_t)stream);
+}
+
+int b2q_gather_rows(const void* src, const int32_t* idx, int div, void* dst, int64_t rows, int64_t cols,
+                    int elem_bytes, void* stream) {
+  if (!src || !dst) return B2Q_ERR_NULL;
+  if (rows < 0 || cols < 0 || div <= 0 || elem_bytes <= 0 || ((cols * elem_bytes) % 16) != 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(src) || !aligned16(dst)) return B2Q_ERR_ALIGN;
+  return gather_rows(src, idx, div, dst, rows, cols, elem_bytes, (cudaStream_t)stream);
+}
+
+int b2q_silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, void* stream) {
+  if (!in || !out) return B2Q_ERR_NULL;
+  if (!is16(dtype)) return B2Q_ERR_DTYPE;
+  if (rows < 0 || I < 0 || (I % 8) != 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(in) || !aligned16(out)) return B2Q_ERR_ALIGN;
+  return silu_mul(in, out, dtype, rows, I, nullptr, (cudaStream_t)stream);
+}
+
+int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int32_t* perm, void* out, int dtype, int64_t T,
+                    int top_k, int64_t H, int w_by_row, void* stream) {
+  if (!y || !w || !out) return B2Q_ERR_NULL;
+  if (!is16(dtype) || w_dtype < 0 || w_dtype > 2) return B2Q_ERR_DTYPE;
+  if (T < 0 || top_k <= 0 || H < 0 || (H % 8) != 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(y) || !aligned16(out)) return B2Q_ERR_ALIGN;
+  return moe_combine(y, w, w_dtype, perm, out, dtype, T, top_k, H, w_by_row, (cudaStream_t)stream);
+}
+
+size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int act) {
+  // tile lists for the largest (8-row) tiling of either kernel family, plus the
+  // un-activated [rows, N] intermediate the streaming kernel needs for SiLU*mul.
+  size_t b = tile_list_bytes(rows, E, 8);
+  if (act != B2Q_ACT_NONE) b += align_up((size_t)rows * (size_t)N * 2, 256);
+  return b;
+}
+
+int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* row_map, int row_div, const void* w,
+                      int w_layout, const void* scale, int scale_dtype, const int32_t* expert_offsets, int E,
+                      void* out, int64_t ldo, const int32_t* out_map, int64_t rows, int64_t N, int64_t K, int group,
+                      int act, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !w || !scale || !expert_offsets || !out || !workspace) return B2Q_ERR_NULL;
+  if (!is16(act_dtype) || scale_dtype < 0 || scale_dtype > 2) return B2Q_ERR_DTYPE;
+  if (w_layout < 0 || w_layout > 3) return B2Q_ERR_LAYOUT;
+  if (group != 128) return B2Q_ERR_SHAPE;
+  if (rows < 0 || N <= 0 || K <= 0 || (K % group) != 0 || E <= 0 || ldx < K) return B2Q_ERR_SHAPE;
+  if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0)) return B2Q_ERR_SHAPE;
+  if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL) return B2Q_ERR_UNSUPPORTED;
+  if (E > 1024 || rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (row_map && row_div <= 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(workspace) || ((ldx * 2) & 15)) return B2Q_ERR_ALIGN;
+  if (workspace_bytes < b2q_moe_gemm_workspace_bytes(rows, E, N, act)) return B2Q_ERR_WORKSPACE;
+  if (rows == 0) return B2Q_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool kmajor = (w_layout == B2Q_W4_KMAJOR || w_layout == B2Q_W4_KMAJOR_MARLIN);
+  const int force = tls().force_kernel;
+  int32_t* tiles = reinterpret_cast<int32_t*>(workspace);
+
+  UmmaW4Args ua{};
+  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16);
+  ua.w = w; ua.layout = w_layout; ua.scale = scale; ua.scale_dtype = scale_dtype;
+  ua.s_stride_n = kmajor ? 1 : K / group; ua.s_stride_g = kmajor ? N : 1;
+  ua.out = out; ua.ldo = ldo; ua.M = (int)rows; ua.N = (int)N; ua.K = (int)K;
+  ua.expert_offsets = expert_offsets; ua.E = E; ua.row_map = row_map; ua.row_div = row_div; ua.out_map = out_map;
+  ua.act = act; ua.tiles = tiles;
+  const int64_t avg = (rows + E - 1) / E;
+  const bool want_umma = force == 2 || (force == 0 && (kmajor || avg > 16));
+  if (umma_w4_supported(ua) && want_umma) {
+    const int tile = umma_w4_token_tile(ua);
+    int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+    if (rc) return rc;
+    ua.tile_cap = (int)((rows + tile - 1) / tile + E);
+    return umma_w4_linear(ua, st);
+  }
+  if (kmajor) return B2Q_ERR_UNSUPPORTED;
+
+  const int tile = grouped_tile(rows, E);
+  int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+  if (rc) return rc;
+  SmallMParams p{};
+  p.x = x; p.ldx = ldx;
+  p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K / 2;
+  p.scale = scale; p.scale_dtype = scale_dtype; p.s_stride_n = K / group; p.s_stride_g = 1;
+  p.M = (int)rows; p.N = (int)N; p.K = (int)K;
+  p.xor_mask = (w_layout == B2Q_W4_NMAJOR_S4) ? 0x88888888u : 0u;
+  p.tiles = tiles; p.expert_offsets = expert_offsets; p.row_map = row_map; p.row_div = row_div > 0 ? row_div : 1;
+  p.w_expert_bytes = N * (K / 2); p.s_expert_elems = N * (K / group);
+  const int cap = (int)((rows + tile - 1) / tile + E);
+  if (act == B2Q_ACT_NONE) {
+    p.out = out; p.ldo = ldo; p.out_map = out_map;
+    return smallm_int4(p, act_dtype == B2Q_BF16, tile, cap, st);
+  }
+  void* g = reinterpret_cast<uint8_t*>(workspace) + tile_list_bytes(rows, E, 8);
+  p.out = g; p.ldo = N; p.out_map = nullptr;
+  rc = smallm_int4(p, act_dtype == B2Q_BF16, tile, cap, st);
+  if (rc) return rc;
+  if (ldo != N / 2) return B2Q_ERR_SHAPE;
+  return silu_mul(g, out, act_dtype, rows, N / 2, out_map, st);
+}
+
+int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx, const int32_t* row_map, int row_div, const void* w,
+                     int fp8_format, const float* scale, int scale_mode, const int32_t* expert_offsets, int E,
+                     void* out, int64_t ldo, const int32_t* out_map, int64_t rows, int64_t N, int64_t K, int act,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !w || !scale || !expert_offsets || !out || !workspace) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (fp8_format != B2Q_E4M3 && fp8_format != B2Q_E5M2) return B2Q_ERR_DTYPE;
+  if (scale_mode < 0 || scale_mode > 2) return B2Q_ERR_LAYOUT;
+  if (scale_mode == B2Q_SCALE_BLOCK128 && fp8_format != B2Q_E4M3) return B2Q_ERR_DTYPE;
+  if (rows < 0 || N <= 0 || K <= 0 || (K % 16) != 0 || E <= 0 || ldx < K) return B2Q_ERR_SHAPE;
+  if (scale_mode == B2Q_SCALE_BLOCK128 && ((K % 128) != 0 || (N % 128) != 0)) return B2Q_ERR_SHAPE;
+  if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL) return B2Q_ERR_UNSUPPORTED;
+  if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0)) return B2Q_ERR_SHAPE;
+  if (E > 1024 || rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (row_map && row_div <= 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(w) || !aligned16(workspace) || ((ldx * 2) & 15)) return B2Q_ERR_ALIGN;
+  if (workspace_bytes < b2q_moe_gemm_workspace_bytes(rows, E, N, act)) return B2Q_ERR_WORKSPACE;
+  if (rows == 0) return B2Q_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  int32_t* tiles = reinterpret_cast<int32_t*>(workspace);
+  const int force = tls().force_kernel;
+  const int64_t kblocks = (K + 127) / 128, nblocks = (N + 127) / 128;
+  const int64_t s_expert = scale_mode == B2Q_SCALE_CHANNEL ? N : (scale_mode == B2Q_SCALE_TENSOR ? 1 : nblocks * kblocks);
+
+  UmmaW8Args ua{};
+  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16);
+  ua.w = w; ua.fmt = fp8_format; ua.scale = scale; ua.scale_dtype = B2Q_F32; ua.scale_mode = scale_mode;
+  ua.out = out; ua.ldo = ldo; ua.M = (int)rows; ua.N = (int)N; ua.K = (int)K;
+  ua.expert_offsets = expert_offsets; ua.E = E; ua.row_map = row_map; ua.row_div = row_div; ua.out_map = out_map;
+  ua.act = act; ua.tiles = tiles; ua.s_expert_elems = s_expert;
+  const int64_t avg = (rows + E - 1) / E;
+  const bool want_umma = force == 2 || (force == 0 && avg > 16);
+  if (umma_w8_supported(ua) && want_umma) {
+    const int tile = umma_w8_token_tile(ua);
+    int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+    if (rc) return rc;
+    ua.tile_cap = (int)((rows + tile - 1) / tile + E);
+    return umma_w8_linear(ua, st);
+  }
+
+  const int tile = grouped_tile(rows, E);
+  int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+  if (rc) return rc;
+  SmallMParams p{};
+  p.x = x; p.ldx = ldx;
+  p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K;
+  p.scale = scale; p.scale_dtype = B2Q_F32; p.s_stride_n = (scale_mode == B2Q_SCALE_CHANNEL) ? 1 : 0;
+  p.M = (int)rows; p.N = (int)N; p.K = (int)K;
+  p.tiles = tiles; p.expert_offsets = expert_offsets; p.row_map = row_map; p.row_div = row_div > 0 ? row_div : 1;
+  p.w_expert_bytes = N * K; p.s_expert_elems = s_expert;
+  const int smode = scale_mode == B2Q_SCALE_BLOCK128 ? SM_BLOCK : SM_POST;
+  const int cap = (int)((rows + tile - 1) / tile + E);
+  const bool bf = act_dtype == B2Q_BF16;
+  if (act == B2Q_ACT_NONE) {
+    p.out = out; p.ldo = ldo; p.out_map = out_map;
+    return bf ? smallm_fp8_bf16(p, fp8_format, smode, tile, cap, st) : smallm_fp8_f16(p, fp8_format, smode, tile, cap, st);
+  }
+  void* g = reinterpret_cast<uint8_t*>(workspace) + tile_list_bytes(rows, E, 8);
+  p.out = g; p.ldo = N; p.out_map = nullptr;
+  rc = bf ? smallm_fp8_bf16(p, fp8_format, smode, tile, cap, st) : smallm_fp8_f16(p, fp8_format, smode, tile, cap, st);
+  if (rc) return rc;
+  if (ldo != N / 2) return B2Q_ERR_SHAPE;
+  return silu_mul(g, out, act_dtype, rows, N / 2, out_map, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,384 @@
+// MoE routing / permutation / activation / combine kernels and the dynamic
+// 1x128 activation quantiser.  All are HBM- or latency-bound integer / elementwise
+// work; none uses tensor cores.
+#include "common.cuh"
+#include <cuda_fp8.h>
+#include <math.h>
+
+namespace b2q {
+
+// ---------------------------------------------------------------------------
+// softmax -> top-k -> renormalise.  One warp per token; lane l owns experts
+// l, l+32, ... so loads are coalesced.  Selection order and tie rule follow
+// MoE_TopK_V2_Kernel (csrc/xpu/esimd_kernels/moe_ops.h:106-219): k rounds of
+// "global maximum, lowest index among bit-equal maxima, then mark as taken".
+// ---------------------------------------------------------------------------
+template <int PER_LANE>
+__global__ void moe_topk_kernel(const void* __restrict__ logits, int ldt, int64_t T, int E, int top_k, int renorm,
+                                void* __restrict__ weights, int wdt, int32_t* __restrict__ ids) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t tok = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (tok >= T) return;
+  float v[PER_LANE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? load_scalar(logits, tok * E + e, ldt) : -INFINITY;
+    mx = fmaxf(mx, v[j]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? expf(v[j] - mx) : 0.f;
+    sum += v[j];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.0f / sum;
+#pragma unroll
+  for (int j = 0; j < PER_LANE; ++j) {
+    const int e = lane + 32 * j;
+    v[j] = e < E ? v[j] * inv : -2.f;
+  }
+  float tv = 0.f;   // lane r keeps the r-th selected probability
+  int ti = 0;
+  float tsum = 0.f;
+  for (int r = 0; r < top_k; ++r) {
+    float bv = -3.f;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int j = 0; j < PER_LANE; ++j) {
+      const int e = lane + 32 * j;
+      if (v[j] > bv) { bv = v[j]; bi = e; }   // ascending e: first hit is the lowest index
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int j = 0; j < PER_LANE; ++j)
+        if (lane + 32 * j == bi) v[j] = -1.f;
+    }
+    if (lane == r) { tv = bv; ti = bi; }
+    tsum += bv;
+  }
+  if (lane < top_k) {
+    if (renorm) tv *= (1.0f / tsum);
+    store_scalar(weights, tok * top_k + lane, wdt, tv);
+    ids[tok * top_k + lane] = ti;
+  }
+}
+
+int moe_topk(const void* logits, int ldt, int64_t T, int E, int top_k, int renorm, void* weights, int wdt,
+             int32_t* ids, cudaStream_t st) {
+  const int wpb = 8;
+  const int grid = (int)((T + wpb - 1) / wpb);
+  if (grid == 0) return B2Q_OK;
+#define B2Q_TOPK(P) moe_topk_kernel<P><<<grid, wpb * 32, 0, st>>>(logits, ldt, T, E, top_k, renorm, weights, wdt, ids)
+  if (E <= 64) B2Q_TOPK(2);
+  else if (E <= 128) B2Q_TOPK(4);
+  else if (E <= 256) B2Q_TOPK(8);
+  else if (E <= 512) B2Q_TOPK(16);
+  else B2Q_TOPK(32);
+#undef B2Q_TOPK
+  note_launch("moe_topk");
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Stable counting sort of (token, slot) pairs by expert.  Three launches:
+// per-chunk histogram, prefix over (expert, chunk), stable scatter.  Pair ids
+// outside [0, E) are dropped (pair_to_perm = -1): that is how an expert map
+// marks experts owned by another rank.
+// ---------------------------------------------------------------------------
+constexpr int ROUTE_CHUNK = 256;  // pairs per CTA (8 warps)
+
+__global__ void route_hist_kernel(const int32_t* __restrict__ ids, int64_t n_pairs, int E, int32_t* __restrict__ counts) {
+  extern __shared__ int32_t sh[];
+  for (int i = threadIdx.x; i < E; i += blockDim.x) sh[i] = 0;
+  __syncthreads();
+  const int64_t i = (int64_t)blockIdx.x * ROUTE_CHUNK + threadIdx.x;
+  if (i < n_pairs) {
+    const int e = ids[i];
+    if (e >= 0 && e < E) atomicAdd(&sh[e], 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) counts[(int64_t)blockIdx.x * E + e] = sh[e];
+}
+
+// counts[b][e] -> exclusive running sum over b (in place); expert_offsets[E+1]; rows_per_expert[E]
+__global__ void route_prefix_kernel(int32_t* __restrict__ counts, int nchunks, int E, int32_t* __restrict__ expert_offsets,
+                                    int32_t* __restrict__ rows_per_expert) {
+  __shared__ int32_t tot[1024];
+  __shared__ int32_t scan[1024];
+  const int e = threadIdx.x;
+  int run = 0;
+  if (e < E) {
+    for (int b = 0; b < nchunks; ++b) {
+      const int c = counts[(int64_t)b * E + e];
+      counts[(int64_t)b * E + e] = run;
+      run += c;
+    }
+  }
+  tot[e] = e < E ? run : 0;
+  __syncthreads();
+  // Hillis-Steele inclusive scan over 1024 slots
+  int val = tot[e];
+  scan[e] = val;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int add = e >= off ? scan[e - off] : 0;
+    __syncthreads();
+    val += add;
+    scan[e] = val;
+    __syncthreads();
+  }
+  if (e < E) {
+    expert_offsets[e] = val - tot[e];
+    if (rows_per_expert) rows_per_expert[e] = tot[e];
+    if (e == E - 1) expert_offsets[E] = val;
+  }
+}
+
+__global__ void route_scatter_kernel(const int32_t* __restrict__ ids, int64_t n_pairs, int E,
+                                     const int32_t* __restrict__ base, const int32_t* __restrict__ expert_offsets,
+                                     int32_t* __restrict__ expert_tokens, int32_t* __restrict__ pair_to_perm) {
+  extern __shared__ int32_t wc[];  // [8][E] per-warp counts
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 8 * E; i += blockDim.x) wc[i] = 0;
+  __syncthreads();
+  const int64_t i = (int64_t)blockIdx.x * ROUTE_CHUNK + threadIdx.x;
+  int e = -1;
+  if (i < n_pairs) { e = ids[i]; if (e < 0 || e >= E) e = -1; }
+  const unsigned peers = __match_any_sync(0xffffffffu, e);
+  const int rank = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && rank == 0) wc[warp * E + e] = __popc(peers);
+  __syncthreads();
+  if (i < n_pairs) {
+    if (e >= 0) {
+      int before = 0;
+      for (int w2 = 0; w2 < warp; ++w2) before += wc[w2 * E + e];
+      const int pos = expert_offsets[e] + base[(int64_t)blockIdx.x * E + e] + before + rank;
+      expert_tokens[pos] = (int32_t)i;
+      if (pair_to_perm) pair_to_perm[i] = pos;
+    } else if (pair_to_perm) {
+      pair_to_perm[i] = -1;
+    }
+  }
+}
+
+size_t moe_route_workspace_bytes(int64_t n_pairs, int E) {
+  const int64_t nchunks = (n_pairs + ROUTE_CHUNK - 1) / ROUTE_CHUNK;
+  return (size_t)(nchunks > 0 ? nchunks : 1) * (size_t)E * sizeof(int32_t);
+}
+
+int moe_route(const int32_t* ids, int64_t n_pairs, int E, int32_t* expert_offsets, int32_t* expert_tokens,
+              int32_t* pair_to_perm, int32_t* rows_per_expert, void* workspace, cudaStream_t st) {
+  const int nchunks = (int)((n_pairs + ROUTE_CHUNK - 1) / ROUTE_CHUNK);
+  int32_t* counts = reinterpret_cast<int32_t*>(workspace);
+  if (nchunks > 0) {
+    route_hist_kernel<<<nchunks, ROUTE_CHUNK, E * sizeof(int32_t), st>>>(ids, n_pairs, E, counts);
+    note_launch("route_hist");
+  }
+  route_prefix_kernel<<<1, 1024, 0, st>>>(counts, nchunks, E, expert_offsets, rows_per_expert);
+  note_launch("route_prefix");
+  if (nchunks > 0) {
+    route_scatter_kernel<<<nchunks, ROUTE_CHUNK, 8 * E * sizeof(int32_t), st>>>(ids, n_pairs, E, counts, expert_offsets,
+                                                                                 expert_tokens, pair_to_perm);
+    note_launch("route_scatter");
+  }
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Tile list for grouped GEMMs: for every expert with rows, ceil(rows/tile) entries
+// (expert, first row within the expert).  n_tiles is written to tiles[0].x's
+// neighbour: layout = int32 n_tiles, 3 pad ints, then int2 entries.
+// ---------------------------------------------------------------------------
+__global__ void moe_tiles_kernel(const int32_t* __restrict__ expert_offsets, int E, int tile, int32_t* __restrict__ ws) {
+  __shared__ int32_t scan[1024];
+  const int e = threadIdx.x;
+  const int rows = e < E ? expert_offsets[e + 1] - expert_offsets[e] : 0;
+  const int nt = (rows + tile - 1) / tile;
+  int val = nt;
+  scan[e] = val;
+  __syncthreads();
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int add = e >= off ? scan[e - off] : 0;
+    __syncthreads();
+    val += add;
+    scan[e] = val;
+    __syncthreads();
+  }
+  int2* list = reinterpret_cast<int2*>(ws + 4);
+  const int start = val - nt;
+  for (int i = 0; i < nt; ++i) list[start + i] = make_int2(e, i * tile);
+  if (e == 1023) ws[0] = val;
+}
+
+int moe_build_tiles(const int32_t* expert_offsets, int E, int tile, int32_t* ws, cudaStream_t st) {
+  moe_tiles_kernel<<<1, 1024, 0, st>>>(expert_offsets, E, tile, ws);
+  note_launch("moe_tiles");
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ idx, int div,
+                                   uint4* __restrict__ dst, int64_t rows, int64_t vec_per_row) {
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const int64_t s = idx ? (int64_t)(idx[r] / div) : r;
+    for (int64_t c = threadIdx.x; c < vec_per_row; c += blockDim.x) dst[r * vec_per_row + c] = src[s * vec_per_row + c];
+  }
+}
+
+int gather_rows(const void* src, const int32_t* idx, int div, void* dst, int64_t rows, int64_t cols, int elem_bytes,
+                cudaStream_t st) {
+  if (rows == 0) return B2Q_OK;
+  const int64_t vec = cols * elem_bytes / 16;
+  const int grid = (int)(rows < 148 * 32 ? rows : 148 * 32);
+  gather_rows_kernel<<<grid, 128, 0, st>>>(reinterpret_cast<const uint4*>(src), idx, div, reinterpret_cast<uint4*>(dst),
+                                           rows, vec);
+  note_launch("gather_rows");
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+template <bool BF16>
+__global__ void silu_mul_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t rows, int64_t I8,
+                                const int32_t* __restrict__ out_map) {
+  using A = Act<BF16>;
+  using T = typename A::T;
+  const int64_t total = rows * I8;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = idx / I8, c = idx % I8;
+    const uint4 g = in[r * 2 * I8 + c];
+    const uint4 u = in[r * 2 * I8 + I8 + c];
+    const T* gp = reinterpret_cast<const T*>(&g);
+    const T* up = reinterpret_cast<const T*>(&u);
+    uint4 o;
+    T* op = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gv = A::to_f(gp[j]);
+      const float s = gv / (1.0f + expf(-gv));
+      op[j] = A::from_f(s * A::to_f(up[j]));
+    }
+    out[(out_map ? (int64_t)out_map[r] : r) * I8 + c] = o;
+  }
+}
+
+int silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, const int32_t* out_map, cudaStream_t st) {
+  if (rows == 0) return B2Q_OK;
+  const int64_t total = rows * (I / 8);
+  int64_t g = (total + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  if (dtype == B2Q_BF16)
+    silu_mul_kernel<true><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map);
+  else
+    silu_mul_kernel<false><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map);
+  note_launch("silu_mul");
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// out[t, :] = sum_s w[t, s] * y[row(t, s), :], slots added in order s = 0..k-1 in fp32.
+template <bool BF16>
+__global__ void moe_combine_kernel(const uint4* __restrict__ y, const void* __restrict__ w, int wdt,
+                                   const int32_t* __restrict__ perm, uint4* __restrict__ out, int64_t T, int top_k,
+                                   int64_t H8, int w_by_row) {
+  using A = Act<BF16>;
+  using Ty = typename A::T;
+  const int64_t total = T * H8;
+  for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
+       idx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t t = idx / H8, c = idx % H8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < top_k; ++s) {
+      const int64_t pair = t * top_k + s;
+      const int64_t row = perm ? (int64_t)perm[pair] : pair;
+      if (row < 0) continue;
+      const float wt = load_scalar(w, w_by_row ? row : pair, wdt);
+      const uint4 v = y[row * H8 + c];
+      const Ty* vp = reinterpret_cast<const Ty*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += wt * A::to_f(vp[j]);
+    }
+    uint4 o;
+    Ty* op = reinterpret_cast<Ty*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) op[j] = A::from_f(acc[j]);
+    out[idx] = o;
+  }
+}
+
+int moe_combine(const void* y, const void* w, int wdt, const int32_t* perm, void* out, int dtype, int64_t T, int top_k,
+                int64_t H, int w_by_row, cudaStream_t st) {
+  if (T == 0) return B2Q_OK;
+  const int64_t total = T * (H / 8);
+  int64_t g = (total + 255) / 256;
+  if (g > 148 * 16) g = 148 * 16;
+  if (dtype == B2Q_BF16)
+    moe_combine_kernel<true><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(y), w, wdt, perm,
+                                                     reinterpret_cast<uint4*>(out), T, top_k, H / 8, w_by_row);
+  else
+    moe_combine_kernel<false><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(y), w, wdt, perm,
+                                                      reinterpret_cast<uint4*>(out), T, top_k, H / 8, w_by_row);
+  note_launch("moe_combine");
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Dynamic e4m3 quantisation of activations, one warp per (row, 128 columns).
+// scale = max(amax, 1e-12) / 448 ; q = e4m3_rn(x / scale) with true division,
+// the recipe of tests/test_fp8_blockscale_gemm.py:13-28 applied to a 1x128 tile.
+template <bool BF16>
+__global__ void act_quant_1x128_kernel(const void* __restrict__ x, int64_t ldx, uint8_t* __restrict__ xq,
+                                       float* __restrict__ xs, int64_t M, int64_t K) {
+  using A = Act<BF16>;
+  using T = typename A::T;
+  const int64_t kb_n = K >> 7;
+  const int64_t wid = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= M * kb_n) return;
+  const int64_t m = wid / kb_n, kb = wid % kb_n;
+  const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const T*>(x) + m * ldx + kb * 128 + lane * 4);
+  const T* rp = reinterpret_cast<const T*>(&raw);
+  float v[4];
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[j] = A::to_f(rp[j]); amax = fmaxf(amax, fabsf(v[j])); }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float s = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+  uint32_t pk = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const uint32_t b = __nv_cvt_float_to_fp8(__fdiv_rn(v[j], s), __NV_SATFINITE, __NV_E4M3);
+    pk |= b << (8 * j);
+  }
+  *reinterpret_cast<uint32_t*>(xq + m * K + kb * 128 + lane * 4) = pk;
+  if (lane == 0) xs[m * kb_n + kb] = s;
+}
+
+int act_quant_1x128(const void* x, int dtype, int64_t ldx, void* xq, float* xs, int64_t M, int64_t K, cudaStream_t st) {
+  const int64_t warps = M * (K >> 7);
+  if (warps == 0) return B2Q_OK;
+  const int grid = (int)((warps + 7) / 8);
+  if (dtype == B2Q_BF16)
+    act_quant_1x128_kernel<true><<<grid, 256, 0, st>>>(x, ldx, reinterpret_cast<uint8_t*>(xq), xs, M, K);
+  else
+    act_quant_1x128_kernel<false><<<grid, 256, 0, st>>>(x, ldx, reinterpret_cast<uint8_t*>(xq), xs, M, K);
+  note_launch("act_quant_1x128");
+  return launch_status();
+}
+
+}  // namespace b2q

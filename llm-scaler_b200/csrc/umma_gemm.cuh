@@ -1,0 +1,51 @@
+// Host-side interface of the tcgen05 (UMMA) weight-only GEMM family.
+#pragma once
+#include "common.cuh"
+
+namespace b2q {
+
+// Common tail of the argument blocks: optional grouped (MoE) mode.
+struct UmmaGroupArgs {
+  const int32_t* expert_offsets = nullptr;  // [E+1]; nullptr = dense
+  int E = 0;
+  const int32_t* row_map = nullptr; int row_div = 1;
+  const int32_t* out_map = nullptr;
+  int act = B2Q_ACT_NONE;
+  const int32_t* tiles = nullptr;           // device tile list {n, pad3, int2...}
+  int tile_cap = 0;
+  int64_t s_expert_elems = 0;
+};
+
+struct UmmaW4Args : UmmaGroupArgs {
+  const void* x; int64_t ldx; bool bf16;
+  const void* w; int layout;
+  const void* scale; int scale_dtype; int64_t s_stride_n, s_stride_g;
+  void* out; int64_t ldo;
+  int M, N, K;
+};
+
+struct UmmaW8Args : UmmaGroupArgs {
+  const void* x; int64_t ldx; bool bf16;
+  const void* w; int fmt;
+  const void* scale; int scale_dtype; int scale_mode;
+  void* out; int64_t ldo;
+  int M, N, K;
+};
+
+struct UmmaW8A8Args {
+  const void* xq; const float* xs; const void* w; const float* ws;
+  void* out; bool bf16; int64_t ldo;
+  int M, N, K;
+};
+
+bool umma_w4_supported(const UmmaW4Args& a);
+int umma_w4_token_tile(const UmmaW4Args& a);
+int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st);
+
+bool umma_w8_supported(const UmmaW8Args& a);
+int umma_w8_token_tile(const UmmaW8Args& a);
+int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st);
+
+int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st);
+
+}  // namespace b2q

@@ -1,0 +1,304 @@
+"""Host side of every op: shape / dtype checks that mirror the reference's TORCH_CHECKs,
+output allocation where the reference op allocates, and one call into libb2q.so.
+
+Each function is what the matching `torch.ops.<namespace>.<op>` dispatches to for CUDA
+tensors (see _register.py).  torch is used for device memory, streams and tiny index
+plumbing only; all arithmetic on the path runs in libb2q.so kernels.
+"""
+import torch
+
+from . import _lib as L
+
+GROUP = 128
+
+
+def _chk(cond, msg):
+    if not cond:
+        raise RuntimeError(msg)
+
+
+# --------------------------------------------------------------------------- INT4 dense
+def _int4_view(weight: torch.Tensor, scale: torch.Tensor):
+    """Classify an INT4 weight/scale pair.  Returns (tensor_for_ptr, layout, N, K, s_stride_n, s_stride_g).
+
+    Accepted presentations (all alias the formats of include/b2q.h):
+      uint8 [N, K/2] / int32 [N, K/8] contiguous            -> NMAJOR
+      int32 [K/8, N] with strides (1, K/8) (the .t() view)  -> NMAJOR on the same bytes
+      int32 [K/8, N] contiguous with scales [K/g, N]        -> KMAJOR
+    """
+    _chk(weight.dim() == 2 and scale.dim() == 2, "int4 weight and scale must be 2-D")
+    if weight.dtype == torch.uint8:
+        _chk(weight.is_contiguous(), "uint8 int4 weight must be contiguous [N, K/2]")
+        N, K = weight.shape[0], weight.shape[1] * 2
+        layout, wt = L.W4_NMAJOR, weight
+    elif weight.dtype == torch.int32:
+        a, b = weight.shape
+        if not weight.is_contiguous() and weight.stride(0) == 1 and weight.stride(1) == a:
+            wt, N, K, layout = weight.t(), b, a * 8, L.W4_NMAJOR
+        else:
+            _chk(weight.is_contiguous(), "int4 weight must be contiguous or a transposed view of a contiguous tensor")
+            nmaj = scale.shape[0] == a and scale.shape[1] * GROUP == b * 8
+            kmaj = scale.shape[1] == b and scale.shape[0] * GROUP == a * 8
+            if nmaj or not kmaj:
+                wt, N, K, layout = weight, a, b * 8, L.W4_NMAJOR
+            else:
+                wt, N, K, layout = weight, b, a * 8, L.W4_KMAJOR
+    else:
+        raise RuntimeError("int4 weight must be uint8 or int32, got %s" % weight.dtype)
+    _chk(K % GROUP == 0, "K must be a multiple of the group size 128")
+    G = K // GROUP
+    if tuple(scale.shape) == (N, G):
+        sn, sg = scale.stride(0), scale.stride(1)
+    elif tuple(scale.shape) == (G, N):
+        sn, sg = scale.stride(1), scale.stride(0)
+    else:
+        raise RuntimeError("int4 scale shape %s does not match N=%d, K/128=%d" % (tuple(scale.shape), N, G))
+    return wt, layout, N, K, sn, sg
+
+
+def linear_int4(input, weight, weight_scale, output):
+    L.require_cuda(input, weight, weight_scale, output)
+    _chk(input.dim() == 2 and output.dim() == 2, "input/output must be 2-D")
+    _chk(input.dtype in (torch.bfloat16, torch.float16), "activation must be bf16 or fp16")
+    _chk(output.dtype == input.dtype, "output dtype must equal input dtype")
+    wt, layout, N, K, sn, sg = _int4_view(weight, weight_scale)
+    M = input.shape[0]
+    _chk(input.shape[1] == K, "input K does not match weight")
+    _chk(tuple(output.shape) == (M, N), "output must be [M, N]")
+    _chk(input.stride(1) == 1 and output.stride(1) == 1, "input/output rows must be contiguous")
+    with L.on_device(input):
+        L.check(L.lib.b2q_linear_int4(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else K,
+                                       wt.data_ptr(), layout, weight_scale.data_ptr(), L.dt(weight_scale), sn, sg,
+                                       output.data_ptr(), output.stride(0) if M > 1 else N, M, N, K, GROUP,
+                                       L.stream(input)))
+    return output
+
+
+def dequant_int4(weight, weight_scale, out_dtype=torch.bfloat16, layout=None):
+    """Debug / bit-exactness gate: [N, K] dequantised weight."""
+    L.require_cuda(weight, weight_scale)
+    if layout is None:
+        wt, layout, N, K, sn, sg = _int4_view(weight, weight_scale)
+        _chk((layout == L.W4_NMAJOR and sg == 1) or (layout != L.W4_NMAJOR and sn == 1), "scale must be contiguous")
+    else:
+        wt = weight
+        if layout in (L.W4_KMAJOR, L.W4_KMAJOR_MARLIN):
+            N, K = weight.shape[1], weight.shape[0] * 8
+        else:
+            N = weight.shape[0]
+            K = weight.shape[1] * (2 if weight.dtype == torch.uint8 else 8)
+    out = torch.empty(N, K, dtype=out_dtype, device=weight.device)
+    with L.on_device(weight):
+        L.check(L.lib.b2q_dequant_int4(wt.data_ptr(), layout, weight_scale.data_ptr(), L.dt(weight_scale),
+                                        out.data_ptr(), L.dt(out), N, K, GROUP, L.stream(weight)))
+    return out
+
+
+# --------------------------------------------------------------------------- FP8 dense
+def linear_fp8(input, weight, weight_scale, output, scale_mode, N=None, K=None):
+    L.require_cuda(input, weight, weight_scale, output)
+    _chk(input.dim() == 2 and output.dim() == 2 and weight.dim() == 2, "input/weight/output must be 2-D")
+    _chk(input.dtype in (torch.bfloat16, torch.float16), "activation must be bf16 or fp16")
+    _chk(output.dtype == input.dtype, "output dtype must equal input dtype")
+    _chk(weight.is_contiguous(), "fp8 weight must be a contiguous [N, K] tensor (a transposed view is read wrongly)")
+    wn, wk = weight.shape
+    _chk((N is None or N == wn) and (K is None or K == wk), "N/K do not match the weight shape")
+    M = input.shape[0]
+    _chk(input.shape[1] == wk and tuple(output.shape) == (M, wn), "shape mismatch")
+    _chk(input.stride(1) == 1 and output.stride(1) == 1, "input/output rows must be contiguous")
+    if scale_mode == L.SCALE_CHANNEL:
+        _chk(weight_scale.numel() == wn and weight_scale.is_contiguous(), "per-channel scale must have N elements")
+    elif scale_mode == L.SCALE_TENSOR:
+        _chk(weight_scale.numel() == 1 and weight_scale.dtype == torch.float32, "per-tensor scale must be one fp32")
+    else:
+        _chk(weight_scale.dtype == torch.float32 and weight_scale.is_contiguous(), "block scale must be fp32")
+        _chk(tuple(weight_scale.shape) == ((wn + 127) // 128, (wk + 127) // 128), "block scale shape mismatch")
+    with L.on_device(input):
+        L.check(L.lib.b2q_linear_fp8(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else wk,
+                                      weight.data_ptr(), L.fp8_fmt(weight), weight_scale.data_ptr(),
+                                      L.dt(weight_scale), scale_mode, output.data_ptr(),
+                                      output.stride(0) if M > 1 else wn, M, wn, wk, L.stream(input)))
+    return output
+
+
+def dequant_fp8(weight, weight_scale, scale_mode, out_dtype=torch.float32):
+    L.require_cuda(weight, weight_scale)
+    N, K = weight.shape
+    out = torch.empty(N, K, dtype=out_dtype, device=weight.device)
+    with L.on_device(weight):
+        L.check(L.lib.b2q_dequant_fp8(weight.data_ptr(), L.fp8_fmt(weight), weight_scale.data_ptr(),
+                                       L.dt(weight_scale), scale_mode, out.data_ptr(), L.dt(out), N, K,
+                                       L.stream(weight)))
+    return out
+
+
+def act_quant_fp8_1x128(x):
+    L.require_cuda(x)
+    M, K = x.shape
+    _chk(K % 128 == 0 and x.stride(1) == 1, "K must be a multiple of 128 and rows contiguous")
+    xq = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    xs = torch.empty(M, K // 128, dtype=torch.float32, device=x.device)
+    with L.on_device(x):
+        L.check(L.lib.b2q_act_quant_fp8_1x128(x.data_ptr(), L.dt(x), x.stride(0) if M > 1 else K, xq.data_ptr(),
+                                               xs.data_ptr(), M, K, L.stream(x)))
+    return xq, xs
+
+
+def gemm_fp8_block_w8a8(xq, xs, weight, weight_scale, output):
+    L.require_cuda(xq, xs, weight, weight_scale, output)
+    M, K = xq.shape
+    N = weight.shape[0]
+    _chk(weight.shape[1] == K and tuple(output.shape) == (M, N), "shape mismatch")
+    _chk(xq.is_contiguous() and xs.is_contiguous() and weight.is_contiguous() and weight_scale.is_contiguous(),
+         "operands must be contiguous")
+    with L.on_device(xq):
+        L.check(L.lib.b2q_gemm_fp8_block_w8a8(xq.data_ptr(), xs.data_ptr(), weight.data_ptr(),
+                                               weight_scale.data_ptr(), output.data_ptr(), L.dt(output),
+                                               output.stride(0), M, N, K, L.stream(xq)))
+    return output
+
+
+# --------------------------------------------------------------------------- MoE pieces
+def moe_topk(logits, top_k, renorm=True, weights=None, ids=None, weight_dtype=None):
+    L.require_cuda(logits)
+    _chk(logits.dim() == 2 and logits.is_contiguous(), "router logits must be contiguous [T, E]")
+    T, E = logits.shape
+    if weights is None:
+        weights = torch.empty(T, top_k, dtype=weight_dtype or logits.dtype, device=logits.device)
+    if ids is None:
+        ids = torch.empty(T, top_k, dtype=torch.int32, device=logits.device)
+    _chk(ids.dtype == torch.int32 and ids.is_contiguous() and weights.is_contiguous(), "bad top-k outputs")
+    with L.on_device(logits):
+        L.check(L.lib.b2q_moe_topk(logits.data_ptr(), L.dt(logits), T, E, top_k, 1 if renorm else 0,
+                                    weights.data_ptr(), L.dt(weights), ids.data_ptr(), L.stream(logits)))
+    return weights, ids
+
+
+def moe_route(ids, num_experts):
+    """Returns expert_offsets [E+1], expert_tokens [T*k], pair_to_perm [T*k], rows_per_expert [E] (all int32)."""
+    L.require_cuda(ids)
+    _chk(ids.dtype == torch.int32 and ids.is_contiguous(), "expert ids must be contiguous int32")
+    n = ids.numel()
+    dev = ids.device
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    tokens = torch.empty(n, dtype=torch.int32, device=dev)
+    p2p = torch.empty(n, dtype=torch.int32, device=dev)
+    rows = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    wsb = L.lib.b2q_moe_route_workspace_bytes(n, num_experts)
+    ws = torch.empty(wsb, dtype=torch.uint8, device=dev)
+    with L.on_device(ids):
+        L.check(L.lib.b2q_moe_route(ids.data_ptr(), n, num_experts, offsets.data_ptr(), tokens.data_ptr(),
+                                     p2p.data_ptr(), rows.data_ptr(), ws.data_ptr(), wsb, L.stream(ids)))
+    return offsets, tokens, p2p, rows
+
+
+def gather_rows(src, idx, div, rows=None):
+    L.require_cuda(src)
+    _chk(src.dim() == 2 and src.is_contiguous(), "source must be contiguous 2-D")
+    rows = idx.numel() if rows is None else rows
+    out = torch.empty(rows, src.shape[1], dtype=src.dtype, device=src.device)
+    with L.on_device(src):
+        L.check(L.lib.b2q_gather_rows(src.data_ptr(), L.ptr(idx), div, out.data_ptr(), rows, src.shape[1],
+                                       src.element_size(), L.stream(src)))
+    return out
+
+
+def silu_mul(gate_up, out=None):
+    L.require_cuda(gate_up)
+    _chk(gate_up.dim() == 2 and gate_up.is_contiguous(), "gate_up must be contiguous [rows, 2I]")
+    rows, two_i = gate_up.shape
+    if out is None:
+        out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+    with L.on_device(gate_up):
+        L.check(L.lib.b2q_silu_mul(gate_up.data_ptr(), out.data_ptr(), L.dt(gate_up), rows, two_i // 2,
+                                    L.stream(gate_up)))
+    return out
+
+
+def moe_combine(y, weights, perm, T, top_k, out=None, w_by_row=False):
+    L.require_cuda(y, weights)
+    _chk(y.dim() == 2 and y.is_contiguous() and weights.is_contiguous(), "combine operands must be contiguous")
+    H = y.shape[1]
+    if out is None:
+        out = torch.empty(T, H, dtype=y.dtype, device=y.device)
+    with L.on_device(y):
+        L.check(L.lib.b2q_moe_combine(y.data_ptr(), weights.data_ptr(), L.dt(weights), L.ptr(perm), out.data_ptr(),
+                                       L.dt(y), T, top_k, H, 1 if w_by_row else 0, L.stream(y)))
+    return out
+
+
+def _moe_int4_layout(weight, scale, K):
+    """Stacked expert weights: int32 [E, N, K/8] / uint8 [E, N, K/2] (N-major) or int32 [E, K/8, N] (K-major)."""
+    _chk(weight.dim() == 3 and scale.dim() == 3 and weight.is_contiguous() and scale.is_contiguous(),
+         "expert weights and scales must be contiguous 3-D")
+    if weight.dtype == torch.uint8:
+        _chk(weight.shape[2] * 2 == K, "uint8 expert weight must be [E, N, K/2]")
+        return weight.shape[1], None
+    _chk(weight.dtype == torch.int32, "expert weight must be int32 or uint8")
+    if weight.shape[2] * 8 == K and scale.shape[1] == weight.shape[1] and scale.shape[2] * GROUP == K:
+        return weight.shape[1], False
+    _chk(weight.shape[1] * 8 == K and scale.shape[2] == weight.shape[2] and scale.shape[1] * GROUP == K,
+         "expert weight / scale shapes do not match K=%d" % K)
+    return weight.shape[2], True
+
+
+def moe_gemm_int4(x, weight, scale, expert_offsets, rows, *, row_map=None, row_div=1, out_map=None, act=L.ACT_NONE,
+                  out_rows=None, layout=None):
+    """Grouped INT4 GEMM over expert-sorted rows (see b2q_moe_gemm_int4 in include/b2q.h)."""
+    L.require_cuda(x, weight, scale, expert_offsets)
+    _chk(x.dim() == 2 and x.stride(1) == 1, "x rows must be contiguous")
+    K = x.shape[1]
+    N, kmajor = _moe_int4_layout(weight, scale, K)
+    if layout is None:
+        layout = L.W4_NMAJOR if not kmajor else L.W4_KMAJOR_MARLIN
+    E = weight.shape[0]
+    _chk(expert_offsets.dtype == torch.int32 and expert_offsets.numel() == E + 1, "expert_offsets must be int32 [E+1]")
+    n_out = N // 2 if act == L.ACT_SILU_MUL else N
+    out = torch.empty(out_rows if out_rows is not None else rows, n_out, dtype=x.dtype, device=x.device)
+    wsb = L.lib.b2q_moe_gemm_workspace_bytes(rows, E, N, act)
+    ws = torch.empty(wsb, dtype=torch.uint8, device=x.device)
+    with L.on_device(x):
+        L.check(L.lib.b2q_moe_gemm_int4(x.data_ptr(), L.dt(x), x.stride(0), L.ptr(row_map), row_div,
+                                         weight.data_ptr(), layout, scale.data_ptr(), L.dt(scale),
+                                         expert_offsets.data_ptr(), E, out.data_ptr(), n_out, L.ptr(out_map),
+                                         rows, N, K, GROUP, act, ws.data_ptr(), wsb, L.stream(x)))
+    return out
+
+
+def moe_gemm_fp8(x, weight, scale, expert_offsets, rows, scale_mode, *, out=None, row_map=None, row_div=1,
+                 out_map=None, act=L.ACT_NONE):
+    L.require_cuda(x, weight, scale, expert_offsets)
+    _chk(x.dim() == 2 and x.stride(1) == 1 and weight.dim() == 3 and weight.is_contiguous(), "bad operands")
+    E, N, K = weight.shape
+    _chk(x.shape[1] == K, "K mismatch")
+    _chk(scale.dtype == torch.float32 and scale.is_contiguous(), "scales must be contiguous fp32")
+    if expert_offsets.dtype != torch.int32:
+        expert_offsets = expert_offsets.view(torch.int32) if expert_offsets.element_size() == 4 else expert_offsets.to(torch.int32)
+    _chk(expert_offsets.numel() == E + 1, "expert_idx must have E+1 entries")
+    n_out = N // 2 if act == L.ACT_SILU_MUL else N
+    if out is None:
+        out = torch.empty(rows, n_out, dtype=x.dtype, device=x.device)
+    wsb = L.lib.b2q_moe_gemm_workspace_bytes(rows, E, N, act)
+    ws = torch.empty(wsb, dtype=torch.uint8, device=x.device)
+    with L.on_device(x):
+        L.check(L.lib.b2q_moe_gemm_fp8(x.data_ptr(), L.dt(x), x.stride(0), L.ptr(row_map), row_div,
+                                        weight.data_ptr(), L.fp8_fmt(weight), scale.data_ptr(), scale_mode,
+                                        expert_offsets.data_ptr(), E, out.data_ptr(), out.stride(0), L.ptr(out_map),
+                                        rows, N, K, act, ws.data_ptr(), wsb, L.stream(x)))
+    return out
+
+
+def moe_forward_int4(x, logits, w13, s13, w2, s2, top_k, num_experts, layout=None):
+    """topk -> route -> gate_up GEMM + SiLU*mul -> down GEMM -> weighted combine (no shared expert).
+
+    The pipeline of moe_prefill_full_int4 (csrc/moe_prefill/moe_prefill_int4.sycl:920-988).  The
+    activations are never materialised in expert order: the up GEMM gathers token rows through
+    expert_tokens and the combine reads the down result through pair_to_perm.
+    """
+    T = x.shape[0]
+    wts, ids = moe_topk(logits, top_k, True, weight_dtype=x.dtype)
+    offsets, tokens, p2p, _ = moe_route(ids, num_experts)
+    rows = T * top_k
+    inter = moe_gemm_int4(x, w13, s13, offsets, rows, row_map=tokens, row_div=top_k, act=L.ACT_SILU_MUL, layout=layout)
+    y = moe_gemm_int4(inter, w2, s2, offsets, rows, layout=layout)
+    return moe_combine(y, wts, p2p, T, top_k)

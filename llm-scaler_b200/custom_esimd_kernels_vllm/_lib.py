@@ -1,0 +1,123 @@
+"""ctypes binding of libb2q.so (the C ABI declared in include/b2q.h).
+
+The library is loaded eagerly and loudly: if libb2q.so is missing or a symbol is
+absent the import fails; there is no CPU or eager-torch fallback anywhere in this
+package.
+"""
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libb2q.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "libb2q.so not found at %s; build it with `python llm-scaler_b200/build.py` "
+        "(needs nvcc; cross-compiles for sm_100a without a GPU)" % LIB_PATH)
+
+lib = C.CDLL(LIB_PATH)
+
+vp, i32, i64, sz = C.c_void_p, C.c_int, C.c_int64, C.c_size_t
+
+_SIGS = {
+    "b2q_strerror": (C.c_char_p, [i32]),
+    "b2q_version": (i32, []),
+    "b2q_device_ok": (i32, []),
+    "b2q_dequant_int4": (i32, [vp, i32, vp, i32, vp, i32, i64, i64, i32, vp]),
+    "b2q_dequant_fp8": (i32, [vp, i32, vp, i32, i32, vp, i32, i64, i64, vp]),
+    "b2q_linear_int4": (i32, [vp, i32, i64, vp, i32, vp, i32, i64, i64, vp, i64, i64, i64, i64, i32, vp]),
+    "b2q_linear_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, i32, vp, i64, i64, i64, i64, vp]),
+    "b2q_act_quant_fp8_1x128": (i32, [vp, i32, i64, vp, vp, i64, i64, vp]),
+    "b2q_gemm_fp8_block_w8a8": (i32, [vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, vp]),
+    "b2q_moe_topk": (i32, [vp, i32, i64, i32, i32, i32, vp, i32, vp, vp]),
+    "b2q_moe_route_workspace_bytes": (sz, [i64, i32]),
+    "b2q_moe_route": (i32, [vp, i64, i32, vp, vp, vp, vp, vp, sz, vp]),
+    "b2q_gather_rows": (i32, [vp, vp, i32, vp, i64, i64, i32, vp]),
+    "b2q_silu_mul": (i32, [vp, vp, i32, i64, i64, vp]),
+    "b2q_moe_combine": (i32, [vp, vp, i32, vp, vp, i32, i64, i32, i64, i32, vp]),
+    "b2q_moe_gemm_workspace_bytes": (sz, [i64, i32, i64, i32]),
+    "b2q_moe_gemm_int4": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
+                                i64, i64, i64, i32, i32, vp, sz, vp]),
+    "b2q_moe_gemm_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
+                               i64, i64, i64, i32, vp, sz, vp]),
+    "b2q_set_force_kernel": (None, [i32]),
+    "b2q_last_kernel": (C.c_char_p, []),
+    "b2q_launch_count": (C.c_uint64, []),
+}
+
+for _name, (_res, _args) in _SIGS.items():
+    _fn = getattr(lib, _name)      # AttributeError here = header / library mismatch
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+EXPORTED = tuple(_SIGS)
+
+BF16, F16, F32 = 0, 1, 2
+W4_NMAJOR, W4_KMAJOR, W4_KMAJOR_MARLIN, W4_NMAJOR_S4 = 0, 1, 2, 3
+E4M3, E5M2 = 0, 1
+SCALE_CHANNEL, SCALE_TENSOR, SCALE_BLOCK128 = 0, 1, 2
+ACT_NONE, ACT_SILU_MUL = 0, 1
+
+_DT = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
+
+
+def dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise RuntimeError("b2q: unsupported dtype %s" % t.dtype) from None
+
+
+def fp8_fmt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float8_e5m2:
+        return E5M2
+    if t.dtype in (torch.float8_e4m3fn, torch.uint8, torch.int8):
+        return E4M3
+    raise RuntimeError("b2q: fp8 weight must be float8_e4m3fn / float8_e5m2 / uint8, got %s" % t.dtype)
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise RuntimeError(lib.b2q_strerror(rc).decode())
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream(t: torch.Tensor):
+    """Raw cudaStream_t of torch's current stream on the tensor's device."""
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def require_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("b2q: tensor must live on a CUDA device (no CPU path exists)")
+
+
+class on_device:
+    """Makes the tensor's device current for the duration of a launch."""
+
+    def __init__(self, t):
+        self.g = torch.cuda.device(t.device)
+
+    def __enter__(self):
+        return self.g.__enter__()
+
+    def __exit__(self, *a):
+        return self.g.__exit__(*a)
+
+
+def launch_count() -> int:
+    return int(lib.b2q_launch_count())
+
+
+def last_kernel() -> str:
+    return lib.b2q_last_kernel().decode()
+
+
+def set_force_kernel(which: int) -> None:
+    lib.b2q_set_force_kernel(int(which))

@@ -1,0 +1,198 @@
+"""Python wrappers with the names, argument order and docstring contracts of the reference package
+(python/custom_esimd_kernels_vllm/ops.py).  Each is a one-line forward to the torch custom op, so a
+caller can use either `custom_esimd_kernels_vllm.esimd_gemv_int4(...)` or
+`torch.ops.custom_esimd_kernels_vllm.esimd_gemv_int4(...)`.
+
+Differences from the reference surface, all widening: activations / outputs may be bf16 as well as
+fp16; INT4 scales may be bf16 / fp16 / fp32; per-channel FP8 scales may be fp16 / bf16 / fp32; every
+dense op accepts any M >= 1 (the reference caps its kernels at M = 1 / 64 / 128).  Device checks
+test for "cuda" where the reference tests for "xpu".
+"""
+import torch
+import torch.nn.functional as F
+
+from . import _register  # noqa: F401  (defines the ops)
+from . import _impl
+
+_ops = torch.ops.custom_esimd_kernels_vllm
+_prefill = torch.ops.moe_int4_prefill_ops
+_moe_int4 = torch.ops.moe_int4_ops
+
+
+# ---- FP8 GEMV / GEMM (ops.py:8-63, 91-143, 799-835 of the reference) ----
+def esimd_gemv_fp8_pern(input, weight, weight_scale, output, N, K):
+    """FP8 weight GEMV with one scale per output row.  input [M, K], weight [N, K] fp8, scale [N], output [M, N]."""
+    return _ops.esimd_gemv_fp8_pern(input, weight, weight_scale, output, N, K)
+
+
+def esimd_gemv_fp8_pern_fused2(input, w0, s0, o0, N0, w1, s1, o1, N1, K):
+    return _ops.esimd_gemv_fp8_pern_fused2(input, w0, s0, o0, N0, w1, s1, o1, N1, K)
+
+
+def esimd_gemv_fp8_pern_fused3(input, w0, s0, o0, N0, w1, s1, o1, N1, w2, s2, o2, N2, K):
+    return _ops.esimd_gemv_fp8_pern_fused3(input, w0, s0, o0, N0, w1, s1, o1, N1, w2, s2, o2, N2, K)
+
+
+def esimd_gemv_fp8_pert(input, weight, weight_scale, output):
+    """FP8 weight GEMV with a per-tensor fp32 scalar scale read on the device."""
+    return _ops.esimd_gemv_fp8_pert(input, weight, weight_scale, output)
+
+
+def esimd_gemv_fp8_pert_bmg(input, weight, weight_scale, output):
+    return _ops.esimd_gemv_fp8_pert_bmg(input, weight, weight_scale, output)
+
+
+def esimd_gemv_fp8_pert_fused2(input, w0, s0, o0, w1, s1, o1):
+    return _ops.esimd_gemv_fp8_pert_fused2(input, w0, s0, o0, w1, s1, o1)
+
+
+def esimd_gemv_fp8_pert_fused3(input, w0, s0, o0, w1, s1, o1, w2, s2, o2):
+    return _ops.esimd_gemv_fp8_pert_fused3(input, w0, s0, o0, w1, s1, o1, w2, s2, o2)
+
+
+def esimd_gemm_fp8_pert(input, weight, weight_scale, output):
+    """FP8 GEMM with per-tensor scale, any M."""
+    return _ops.esimd_gemm_fp8_pert(input, weight, weight_scale, output)
+
+
+def esimd_gemm_fp8_blockscale(input, weight, weight_scale, output, block_n=128, block_k=128):
+    """FP8 128x128 block-scaled GEMM, w8a16: the activation is not quantised."""
+    return _ops.esimd_gemm_fp8_blockscale(input, weight, weight_scale, output, block_n, block_k)
+
+
+def esimd_gemv_fp8_blockscale_fused2(input, w0, s0, o0, w1, s1, o1, block_n=128, block_k=128):
+    return _ops.esimd_gemv_fp8_blockscale_fused2(input, w0, s0, o0, w1, s1, o1, block_n, block_k)
+
+
+# ---- INT4 (ops.py:146-207) ----
+def esimd_gemv_int4(input, weight, weight_scale, output):
+    """Symmetric INT4 (g=128) weight GEMV.  weight uint8 [N, K/2] (low nibble = even k), scale [N, K/128]."""
+    return _ops.esimd_gemv_int4(input, weight, weight_scale, output)
+
+
+def esimd_gemv_int4_fused2(input, w0, s0, o0, w1, s1, o1):
+    return _ops.esimd_gemv_int4_fused2(input, w0, s0, o0, w1, s1, o1)
+
+
+def esimd_gemm_int4_pgrp(input, weight, weight_scale, output):
+    """INT4 GEMM with per-group scale for M >= 2 (no upper bound on M here)."""
+    return _ops.esimd_gemm_int4_pgrp(input, weight, weight_scale, output)
+
+
+# ---- MoE auxiliary ops + FP8 grouped GEMM (ops.py:633-859) ----
+def esimd_moe_topk(router_logits, top_values, top_indices, T):
+    return _ops.esimd_moe_topk(router_logits, top_values, top_indices, T)
+
+
+def esimd_moe_scatter(hidden_states, router_top_value, sorted_token_ids, scattered_hidden, scattered_weights, K, topk,
+                      total_expanded):
+    return _ops.esimd_moe_scatter(hidden_states, router_top_value, sorted_token_ids, scattered_hidden,
+                                  scattered_weights, K, topk, total_expanded)
+
+
+def esimd_moe_scatter_fused(hidden_states, top_values, top_indices, scattered_hidden, scattered_weights, topk_ids,
+                            expert_start, max_tokens_out, K, topk, T, num_experts):
+    return _ops.esimd_moe_scatter_fused(hidden_states, top_values, top_indices, scattered_hidden, scattered_weights,
+                                        topk_ids, expert_start, max_tokens_out, K, topk, T, num_experts)
+
+
+def esimd_moe_silu_mul(input, output, N_gate_up, N_half, total_rows):
+    return _ops.esimd_moe_silu_mul(input, output, N_gate_up, N_half, total_rows)
+
+
+def esimd_moe_gather(moe_output, topk_ids, scattered_weights, final_hidden, K, topk, T):
+    return _ops.esimd_moe_gather(moe_output, topk_ids, scattered_weights, final_hidden, K, topk, T)
+
+
+def esimd_moe_gemm_fp8(input, weight, scale, output, expert_idx, N, K, num_experts, max_tokens_per_expert):
+    """Grouped GEMM, FP8 E5M2 weights [E, N, K] with per-N fp32 scales [E, N]."""
+    return _ops.esimd_moe_gemm_fp8(input, weight, scale, output, expert_idx, N, K, num_experts, max_tokens_per_expert)
+
+
+def esimd_moe_gemm_fp8_pert(input, weight, scale, output, expert_idx, N, K, num_experts, max_tokens_per_expert):
+    return _ops.esimd_moe_gemm_fp8_pert(input, weight, scale, output, expert_idx, N, K, num_experts,
+                                        max_tokens_per_expert)
+
+
+def esimd_moe_gemm_fp8_blockscale(input, weight, weight_scale, output, expert_idx, N, K, num_experts, block_n=128,
+                                  block_k=128):
+    return _ops.esimd_moe_gemm_fp8_blockscale(input, weight, weight_scale, output, expert_idx, N, K, num_experts,
+                                              block_n, block_k)
+
+
+# ---- INT4 MoE (ops.py:1233-1362) ----
+def moe_topk_int4(logits, top_k, n_routed_experts, norm=True):
+    return _moe_int4.moe_topk_int4(logits.contiguous(), top_k, n_routed_experts, norm)
+
+
+def to_cutlass_nmajor_int4(qweight):
+    """int32 [.., N, K/8] -> uint8 [.., N, K/2], low nibble = even k (pure torch, device agnostic)."""
+    if qweight.dtype == torch.uint8:
+        return qweight.contiguous()
+    if qweight.dtype not in (torch.int32, torch.int64):
+        raise TypeError(f"unsupported qweight dtype: {qweight.dtype}")
+    if qweight.dim() not in (2, 3):
+        raise ValueError(f"expected [N,K/8] or [E,N,K/8], got {tuple(qweight.shape)}")
+    u = qweight.to(torch.int64) & 0xFFFFFFFF
+    sh = torch.arange(8, device=qweight.device, dtype=torch.int64) * 4
+    nib = ((u.unsqueeze(-1) >> sh) & 0xF).to(torch.uint8).reshape(*qweight.shape[:-1], qweight.shape[-1] * 8)
+    return (nib[..., 0::2] | (nib[..., 1::2] << 4)).contiguous()
+
+
+def cutlass_nmajor_int4_to_signed(qweight_u4):
+    """uint4 bytes -> two's-complement int4 bytes (value - 8 per nibble); the pure-torch zero-point fold."""
+    if qweight_u4.dtype != torch.uint8:
+        raise TypeError(f"expected uint8 qweight, got {qweight_u4.dtype}")
+    lo = ((qweight_u4 & 0xF).to(torch.int16) - 8) & 0xF
+    hi = (((qweight_u4 >> 4) & 0xF).to(torch.int16) - 8) & 0xF
+    return (lo | (hi << 4)).to(torch.uint8).contiguous()
+
+
+def prepare_cutlass_nmajor_int4_weight(qweight):
+    return cutlass_nmajor_int4_to_signed(to_cutlass_nmajor_int4(qweight))
+
+
+def precompute_moe_route(topk_weights, topk_ids, num_experts):
+    """Sort token routes by expert.  Returns sorted_rows (int64), sorted_weights, rows_per_expert (int32)."""
+    if topk_weights.device.type == "cuda" and topk_ids.device.type == "cuda":
+        return _moe_int4.moe_route_precompute_int4(topk_weights.contiguous(), topk_ids.contiguous(), num_experts)
+    num_rows, top_k = topk_ids.shape
+    flat_experts = topk_ids.reshape(-1).to(torch.int64)
+    flat_rows = torch.arange(num_rows, device=topk_ids.device, dtype=torch.int64).repeat_interleave(top_k)
+    order = torch.argsort(flat_experts, stable=True)
+    rows_per_expert = torch.bincount(flat_experts[order], minlength=num_experts).to(torch.int32)
+    return flat_rows[order].contiguous(), topk_weights.reshape(-1)[order].contiguous(), rows_per_expert.contiguous()
+
+
+def moe_silu_mul_int4(gate_up):
+    if gate_up.device.type == "cuda":
+        return _moe_int4.moe_silu_mul_int4(gate_up.contiguous())
+    inter = gate_up.shape[1] // 2
+    return (F.silu(gate_up[:, :inter].float()) * gate_up[:, inter:].float()).to(gate_up.dtype).contiguous()
+
+
+def moe_route_gather_int4(route_output, sorted_rows, sorted_weights, n_tokens):
+    return _moe_int4.moe_route_gather_int4(route_output.contiguous(), sorted_rows.contiguous(),
+                                           sorted_weights.contiguous(), n_tokens)
+
+
+def moe_gemm_int4_nmajor(x, weight, scale, expert_idx, group_size=128):
+    return _moe_int4.moe_gemm_int4_nmajor(x, weight, scale, expert_idx, group_size)
+
+
+# ---- INT4 MoE prefill pipeline (csrc/moe_prefill/moe_prefill_int4.sycl:992-1013) ----
+def moe_prefill_full_int4(x, router_logits, gate_up_weight, gate_up_scale, down_weight, down_scale, top_k,
+                          n_routed_experts):
+    return _prefill.moe_prefill_full_int4(x, router_logits, gate_up_weight, gate_up_scale, down_weight, down_scale,
+                                          top_k, n_routed_experts)
+
+
+def moe_topk_softmax(router_logits, top_k, num_experts):
+    return _prefill.moe_topk_softmax(router_logits, top_k, num_experts)
+
+
+# ---- additions that have no reference counterpart (needed by BASELINE's W8A8 configuration) ----
+act_quant_fp8_1x128 = _impl.act_quant_fp8_1x128
+gemm_fp8_block_w8a8 = _impl.gemm_fp8_block_w8a8
+dequant_int4 = _impl.dequant_int4
+dequant_fp8 = _impl.dequant_fp8

@@ -1,0 +1,92 @@
+"""MoE pipeline oracle: routing, permutation, grouped GEMM, activation, combine."""
+import torch
+import torch.nn.functional as F
+
+
+def topk_softmax(logits: torch.Tensor, top_k: int, renorm: bool = True, out_dtype=None):
+    """fp32 softmax -> torch.topk -> renormalise -> cast (tests/test_moe_int4_kernel.py:213-216,
+    python/custom_esimd_kernels_vllm/ops.py:1427-1437).  Returns (weights [T,k], ids int32 [T,k])."""
+    probs = F.softmax(logits.float(), dim=-1)
+    w, ids = torch.topk(probs, top_k, dim=-1)
+    if renorm:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w.to(out_dtype or logits.dtype), ids.to(torch.int32)
+
+
+def route(ids: torch.Tensor, num_experts: int):
+    """Stable sort of the T*k (token, slot) pairs by expert (ops.py:1300-1330).
+
+    Returns expert_offsets int32 [E+1], expert_tokens int32 [n_valid] (pair indices),
+    pair_to_perm int32 [T*k] (-1 for ids outside [0, E)), rows_per_expert int32 [E].
+    """
+    flat = ids.reshape(-1).to(torch.int64)
+    valid = (flat >= 0) & (flat < num_experts)
+    key = torch.where(valid, flat, torch.full_like(flat, num_experts))
+    order = torch.argsort(key, stable=True)
+    n_valid = int(valid.sum())
+    order = order[:n_valid]
+    rows = torch.bincount(flat[valid], minlength=num_experts).to(torch.int32)
+    offsets = torch.zeros(num_experts + 1, dtype=torch.int32)
+    offsets[1:] = rows.cumsum(0)
+    p2p = torch.full((flat.numel(),), -1, dtype=torch.int32)
+    p2p[order] = torch.arange(n_valid, dtype=torch.int32)
+    return offsets, order.to(torch.int32), p2p, rows
+
+
+def silu_mul(g: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up in fp32, cast back (ops.py:1333-1342)."""
+    I = g.shape[-1] // 2
+    gf = g[..., :I].float()
+    return ((gf / (1 + torch.exp(-gf))) * g[..., I:].float()).to(g.dtype)
+
+
+def grouped_linear(x_sorted: torch.Tensor, wd: torch.Tensor, offsets: torch.Tensor) -> torch.Tensor:
+    """out[rows of e] = x[rows of e].float() @ wd[e].float().T, fp32 result (wd: [E, N, K] dequantised)."""
+    out = torch.zeros(x_sorted.shape[0], wd.shape[1], dtype=torch.float32)
+    for e in range(wd.shape[0]):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b > a:
+            out[a:b] = x_sorted[a:b].float() @ wd[e].float().T
+    return out
+
+
+def forward(x, logits, w13d, w2d, top_k, round_intermediates=True):
+    """topk -> per expert gate_up -> SiLU*mul -> down -> weighted sum; no shared expert.
+
+    Follows tests/test_moe_int4_kernel.py:198-247 minus the shared expert, evaluated per expert
+    instead of per token.  w13d [E, 2I, H], w2d [E, H, I] are dequantised weights in x.dtype.
+    With round_intermediates the gate_up result, the activation and the down result are rounded
+    to x.dtype between stages, as a pipeline of separate ops with 16-bit tensors between them does.
+    """
+    T, H = x.shape
+    E = w13d.shape[0]
+    wts, ids = topk_softmax(logits, top_k, True, x.dtype)
+    offsets, expert_tokens, p2p, _ = route(ids, E)
+    tok = (expert_tokens // top_k).long()
+    xs = x[tok]
+    g = grouped_linear(xs, w13d, offsets)
+    if round_intermediates:
+        g = g.to(x.dtype)
+    a = silu_mul(g)
+    y = grouped_linear(a, w2d, offsets)
+    if round_intermediates:
+        y = y.to(x.dtype)
+    wflat = wts.reshape(-1).float()
+    yp = y.float()[p2p.long()] * wflat[:, None]
+    return _ordered_sum(yp.reshape(T, top_k, H)).to(x.dtype)
+
+
+def _ordered_sum(v: torch.Tensor) -> torch.Tensor:
+    acc = torch.zeros(v.shape[0], v.shape[2], dtype=torch.float32)
+    for s in range(v.shape[1]):
+        acc += v[:, s]
+    return acc
+
+
+def combine(y: torch.Tensor, wts: torch.Tensor, perm=None) -> torch.Tensor:
+    """out[t] = sum_s w[t,s] * y[perm[t*k+s]] in fp32, slots in order (moe_prefill_int4.sycl:398-454)."""
+    T, k = wts.shape
+    idx = torch.arange(T * k) if perm is None else perm.long()
+    ok = idx >= 0
+    rows = y.float()[idx.clamp(min=0)] * (wts.reshape(-1).float() * ok)[:, None]
+    return _ordered_sum(rows.reshape(T, k, -1)).to(y.dtype)

@@ -1,0 +1,113 @@
+"""The C ABI: the library loads, exports every symbol include/b2q.h declares, and rejects bad
+arguments with error codes before touching a device (no GPU needed)."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def lib(lib_built):
+    return C.CDLL(lib_built)
+
+
+def _declared():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "include", "b2q.h")).read()
+    return sorted(set(re.findall(r"B2Q_API[^;(]*?\b(b2q_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_entry_points():
+    names = _declared()
+    assert len(names) >= 20
+    for must in ("b2q_linear_int4", "b2q_linear_fp8", "b2q_moe_gemm_int4", "b2q_moe_route", "b2q_strerror"):
+        assert must in names
+
+
+def test_every_declared_symbol_is_exported(lib):
+    for name in _declared():
+        assert hasattr(lib, name), name
+
+
+def test_python_binding_covers_the_header(lib_built):
+    from custom_esimd_kernels_vllm import _lib
+    assert sorted(_lib.EXPORTED) == _declared()
+
+
+def test_strerror_and_version(lib):
+    lib.b2q_strerror.restype = C.c_char_p
+    assert lib.b2q_strerror(0) == b"ok"
+    for code in range(-10, 0):
+        assert lib.b2q_strerror(code).startswith(b"b2q:")
+    assert lib.b2q_version() >= 100
+
+
+def test_null_and_shape_errors_need_no_device(lib_built):
+    from custom_esimd_kernels_vllm import _lib as L
+    lib = L.lib
+    assert lib.b2q_linear_int4(None, 0, 128, None, 0, None, 0, 1, 1, None, 16, 1, 16, 128, 128, None) == -1
+    buf = (C.c_uint8 * 4096)()
+    p = C.addressof(buf)
+    p = (p + 255) // 256 * 256
+    # group != 128
+    assert lib.b2q_linear_int4(p, 0, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 64, None) == -2
+    # unknown activation dtype
+    assert lib.b2q_linear_int4(p, 7, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None) == -3
+    # unknown layout
+    assert lib.b2q_linear_int4(p, 0, 128, p, 9, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None) == -5
+    # misaligned activation pointer
+    assert lib.b2q_linear_int4(p + 2, 0, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None) == -4
+    # fp8: K not a multiple of 16, block mode needs fp32 scales
+    assert lib.b2q_linear_fp8(p, 0, 40, p, 0, p, 2, 0, p, 16, 1, 16, 40, None) == -2
+    assert lib.b2q_linear_fp8(p, 0, 128, p, 0, p, 0, 2, p, 16, 1, 16, 128, None) == -3
+    # M == 0 is a successful no-op
+    assert lib.b2q_linear_int4(p, 0, 128, p, 0, p, 0, 1, 1, p, 16, 0, 16, 128, 128, None) == 0
+    # route: workspace too small
+    assert lib.b2q_moe_route(p, 1024, 8, p, p, p, p, p, 16, None) == -8
+    assert lib.b2q_moe_topk(p, 0, 4, 2048, 8, 1, p, 0, p, None) == -10
+
+
+def test_workspace_size_queries(lib_built):
+    from custom_esimd_kernels_vllm import _lib as L
+    assert L.lib.b2q_moe_route_workspace_bytes(32768, 128) == 128 * 128 * 4
+    small = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 0)
+    big = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 1)
+    assert big >= small + 1024 * 256 * 2
+
+
+def test_ops_refuse_cpu_tensors(lib_built):
+    import torch
+    import custom_esimd_kernels_vllm as e
+    x = torch.zeros(1, 128, dtype=torch.bfloat16)
+    w = torch.zeros(16, 64, dtype=torch.uint8)
+    s = torch.zeros(16, 1, dtype=torch.bfloat16)
+    o = torch.zeros(1, 16, dtype=torch.bfloat16)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        e.esimd_gemv_int4(x, w, s, o)
+    with pytest.raises(RuntimeError):
+        e._impl.linear_int4(x, w, s, o)
+
+
+def test_reference_schemas_are_registered(lib_built):
+    import torch
+    import custom_esimd_kernels_vllm  # noqa: F401
+    for ns, names in {
+        "custom_esimd_kernels_vllm": ["esimd_gemv_int4", "esimd_gemv_int4_fused2", "esimd_gemm_int4_pgrp",
+                                      "esimd_gemv_fp8_pern", "esimd_gemv_fp8_pert", "esimd_gemm_fp8_pert",
+                                      "esimd_gemm_fp8_blockscale", "esimd_moe_topk", "esimd_moe_scatter_fused",
+                                      "esimd_moe_silu_mul", "esimd_moe_gather", "esimd_moe_gemm_fp8",
+                                      "esimd_moe_gemm_fp8_pert", "esimd_moe_gemm_fp8_blockscale"],
+        "moe_int4_prefill_ops": ["moe_prefill_full_int4", "moe_prefill_gather_forward_v2", "moe_prefill_up_forward_v2",
+                                 "moe_prefill_down_forward_v2", "moe_prefill_accumulate_forward_v2",
+                                 "moe_prefill_accumulate_permuted_forward_v2", "moe_prefill_silu_mul_forward",
+                                 "moe_prefill_scatter_x_forward", "moe_topk_softmax"],
+        "moe_int4_ops": ["moe_topk_int4", "moe_route_precompute_int4", "moe_silu_mul_int4", "moe_route_gather_int4",
+                         "moe_gemm_int4_nmajor"],
+        "esimd_topk_v2": ["topk_v2"],
+    }.items():
+        for n in names:
+            assert hasattr(getattr(torch.ops, ns), n), (ns, n)
+    s = torch.ops.custom_esimd_kernels_vllm.esimd_gemv_int4.default._schema
+    assert str(s) == ("custom_esimd_kernels_vllm::esimd_gemv_int4(Tensor input, Tensor weight, "
+                      "Tensor weight_scale, Tensor output) -> Tensor")

@@ -1,0 +1,206 @@
+"""GPU parity of the dense ops against the CPU oracle, called through the torch custom ops (which
+bind the C ABI).  Tolerance: max|err| / max|ref| <= 1e-2 for 16-bit outputs of an fp32 accumulation;
+dequantised weights are compared bit for bit."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import DEV, assert_close
+from oracle import configs, fp8, int4
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def e(lib_built):
+    if not torch.cuda.is_available():
+        pytest.fail("GPU test selected but no CUDA device is visible")
+    import custom_esimd_kernels_vllm as pkg
+    assert pkg._lib.lib.b2q_device_ok() == 0, "libb2q.so targets sm_100a only"
+    return pkg
+
+
+def _rand_int4(N, K, dtype, seed, neg_scales=False):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randint(0, 16, (N, K), generator=g, dtype=torch.uint8)
+    s = 0.002 + torch.randn(N, K // 128, generator=g).abs() * 0.01
+    if neg_scales:
+        s = s * torch.where(torch.rand(N, K // 128, generator=g) < 0.5, -1.0, 1.0)
+    return q, s.to(dtype)
+
+
+# ------------------------------------------------------------------ dequant: bit-exact gate
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_dequant_int4_all_layouts_bit_exact(e, dtype):
+    q, s = _rand_int4(80, 384, torch.bfloat16 if dtype != torch.float16 else torch.float16, 3, neg_scales=True)
+    ref = int4.dequant(q, s, dtype)
+    w32 = int4.pack_nmajor_i32(q)
+    L = e._lib
+    out = e.dequant_int4(w32.to(DEV), s.to(DEV), dtype, L.W4_NMAJOR)
+    assert torch.equal(out.cpu(), ref)
+    out = e.dequant_int4(int4.pack_nmajor_u8(q).to(DEV), s.to(DEV), dtype, L.W4_NMAJOR)
+    assert torch.equal(out.cpu(), ref)
+    for marlin, lay in ((False, L.W4_KMAJOR), (True, L.W4_KMAJOR_MARLIN)):
+        wk, sk = int4.to_kmajor(w32, s, marlin)
+        out = e.dequant_int4(wk.to(DEV), sk.to(DEV), dtype, lay)
+        assert torch.equal(out.cpu(), ref), lay
+    s4 = int4.u4_to_s4_bytes(int4.pack_nmajor_u8(q))
+    out = e.dequant_int4(s4.to(DEV), s.to(DEV), dtype, L.W4_NMAJOR_S4)
+    assert torch.equal(out.cpu(), ref)
+
+
+def test_dequant_int4_golden(e, golden):
+    g = golden("int4_ggml")
+    out = e.dequant_int4(torch.from_numpy(g["packed"]).to(DEV), torch.from_numpy(g["scale"]).to(DEV), torch.float16)
+    assert torch.equal(out.cpu(), torch.from_numpy(g["deq"]))
+    g = golden("int4_sym")
+    out = e.dequant_int4(torch.from_numpy(g["ipex_q"][0]).to(DEV), torch.from_numpy(g["ipex_s"][0]).to(DEV),
+                         torch.float16, e._lib.W4_KMAJOR_MARLIN)
+    assert torch.equal(out.cpu(), torch.from_numpy(g["deq"]))
+
+
+def test_dequant_fp8_every_code_exact(e, golden):
+    codes = torch.arange(256, dtype=torch.uint8).repeat(8, 1).contiguous()          # [8, 256]
+    ones = torch.ones(8, dtype=torch.float32)
+    for fmt_dtype, key in ((torch.float8_e4m3fn, "e4m3_codes"), (torch.float8_e5m2, "e5m2_codes")):
+        out = e.dequant_fp8(codes.view(fmt_dtype).to(DEV), ones.to(DEV), e._lib.SCALE_CHANNEL, torch.float32).cpu()
+        ref = torch.from_numpy(golden("fp8_block")[key])
+        fin = torch.isfinite(ref)
+        assert torch.equal(out[0][fin], ref[fin])
+        assert torch.equal(torch.isnan(out[0]), torch.isnan(ref))
+    g = golden("fp8_block")
+    out = e.dequant_fp8(torch.from_numpy(g["wq"]).to(DEV), torch.from_numpy(g["ws"]).to(DEV), e._lib.SCALE_BLOCK128,
+                        torch.float32)
+    assert torch.equal(out.cpu(), torch.from_numpy(g["wd"]))
+
+
+# ------------------------------------------------------------------ INT4 linear
+INT4_SHAPES = [(2560, 2048), (2048, 512), (3072, 2048), (16, 2048), (512, 2048), (128, 7168), (256, 14336), (1024, 128),
+               (1000, 384)]
+
+
+@pytest.mark.parametrize("N,K", INT4_SHAPES)
+@pytest.mark.parametrize("M", [1, 7, 16, 33, 64])
+def test_int4_linear_shapes(e, N, K, M):
+    dtype = torch.bfloat16 if (N + M) % 2 == 0 else torch.float16
+    q, s = _rand_int4(N, K, dtype, N + K + M, neg_scales=True)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(dtype)
+    ref = int4.linear(x, q, s)
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    op = e.esimd_gemv_int4 if M == 1 else e.esimd_gemm_int4_pgrp
+    r = op(x.to(DEV), int4.pack_nmajor_u8(q).to(DEV), s.to(DEV), out)
+    assert r.data_ptr() == out.data_ptr()
+    assert_close(out, ref, what=f"int4 M={M} N={N} K={K}")
+
+
+def test_int4_config1_all_presentations(e):
+    c = configs.c1()
+    ref = int4.linear(c["x"], c["q"], c["scale"])
+    x = c["x"].to(DEV)
+    w32 = c["w_i32"].to(DEV)
+    s = c["scale"].to(DEV)
+    for w, sc in ((w32, s), (w32.view(torch.uint8), s), (w32.t(), s.t().contiguous())):
+        out = torch.empty(16, 4096, dtype=torch.bfloat16, device=DEV)
+        e.esimd_gemm_int4_pgrp(x, w, sc, out)
+        assert_close(out, ref, what="C1")
+
+
+def test_int4_golden_gemv(e, golden):
+    g = golden("int4_ggml")
+    x = torch.from_numpy(g["x"]).to(DEV)
+    out = torch.empty(1, 24, dtype=torch.float16, device=DEV)
+    e.esimd_gemv_int4(x, torch.from_numpy(g["packed"]).to(DEV), torch.from_numpy(g["scale"]).to(DEV), out)
+    assert_close(out, torch.from_numpy(g["y"]), what="golden gemv")
+
+
+def test_int4_fused2_and_s4(e):
+    q0, s0 = _rand_int4(256, 512, torch.bfloat16, 1)
+    q1, s1 = _rand_int4(64, 512, torch.bfloat16, 2)
+    x = torch.randn(1, 512).to(torch.bfloat16)
+    o0 = torch.empty(1, 256, dtype=torch.bfloat16, device=DEV)
+    o1 = torch.empty(1, 64, dtype=torch.bfloat16, device=DEV)
+    r = e.esimd_gemv_int4_fused2(x.to(DEV), int4.pack_nmajor_u8(q0).to(DEV), s0.to(DEV), o0,
+                                 int4.pack_nmajor_u8(q1).to(DEV), s1.to(DEV), o1)
+    assert r.data_ptr() == o0.data_ptr()
+    assert_close(o0, int4.linear(x, q0, s0), what="fused2/0")
+    assert_close(o1, int4.linear(x, q1, s1), what="fused2/1")
+
+
+def test_int4_rejects_bad_arguments(e):
+    x = torch.zeros(2, 256, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(16, 128, dtype=torch.uint8, device=DEV)
+    s = torch.zeros(16, 2, dtype=torch.bfloat16, device=DEV)
+    with pytest.raises(RuntimeError):
+        e.esimd_gemm_int4_pgrp(x, w, s, torch.zeros(2, 8, dtype=torch.bfloat16, device=DEV))      # wrong N
+    with pytest.raises(RuntimeError):
+        e.esimd_gemm_int4_pgrp(x, w, s, torch.zeros(2, 16, dtype=torch.float16, device=DEV))      # dtype mismatch
+    with pytest.raises(RuntimeError):
+        e.esimd_gemm_int4_pgrp(x.float(), w, s, torch.zeros(2, 16, dtype=torch.float32, device=DEV))
+
+
+# ------------------------------------------------------------------ FP8 linear
+@pytest.mark.parametrize("M", [1, 8, 32])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fp8_per_channel(e, M, dtype):
+    c = configs.c2(seed=M, M=M, N=1536, K=5120, dtype=dtype)
+    ref = fp8.linear_channel(c["x"], c["wq"], c["scale"])
+    out = torch.empty(M, 1536, dtype=dtype, device=DEV)
+    for sdt in (torch.float32, torch.float16):
+        e.esimd_gemv_fp8_pern(c["x"].to(DEV), c["wq"].to(DEV), c["scale"].to(sdt).to(DEV), out, 1536, 5120)
+        ref_s = fp8.linear_channel(c["x"], c["wq"], c["scale"].to(sdt))
+        assert_close(out, ref_s, what=f"fp8 pern M={M} {dtype} scale {sdt}")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 5120), (3, 1000, 1056), (64, 512, 2048), (128, 256, 1024)])
+def test_fp8_per_tensor_and_e5m2(e, M, N, K):
+    g = torch.Generator().manual_seed(M + N)
+    w = torch.randn(N, K, generator=g) * 0.05
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    wq, s = fp8.quantize_tensor(w)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    e.esimd_gemm_fp8_pert(x.to(DEV), wq.to(DEV), s.to(DEV), out)
+    assert_close(out, fp8.linear_tensor(x, wq, s), what="fp8 pert e4m3")
+    w5 = (w / s).to(torch.float8_e5m2)
+    e.esimd_gemv_fp8_pert(x.to(DEV), w5.to(DEV), s.to(DEV), out)
+    assert_close(out, fp8.linear_tensor(x, w5, s, e5m2=True), what="fp8 pert e5m2")
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1024, 5120), (1, 5120, 6144), (2, 5120, 5120), (7, 5120, 5120), (9, 5120, 5120),
+                                   (12, 5120, 5120), (33, 5120, 5120), (64, 5120, 5120), (1, 1000, 5120),
+                                   (4, 1000, 5120)])
+def test_fp8_blockscale_w8a16(e, M, N, K):
+    g = torch.Generator().manual_seed(1234 + M * 131 + N + K)
+    w = torch.randn(N, K, generator=g) * 0.3
+    wq, ws = fp8.quantize_block(w)
+    a = (torch.randn(M, K, generator=g) * 0.5).to(torch.float16)
+    out = torch.empty(M, N, dtype=torch.float16, device=DEV)
+    e.esimd_gemm_fp8_blockscale(a.to(DEV), wq.to(DEV), ws.to(DEV), out, 128, 128)
+    assert_close(out, fp8.linear_block_w8a16(a, wq, ws), what=f"fp8 block M={M} N={N} K={K}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fp8_all_finite_codes_through_gemm_are_exact(e, dtype):
+    """Every raw e4m3 code times x = 1 over K = 128: the result is 128 * decode(code), exactly."""
+    raw = torch.arange(256, dtype=torch.uint8).view(256, 1).expand(256, 128).contiguous()
+    reference = torch.from_numpy(fp8.e4m3_table()) * 128
+    finite = torch.isfinite(reference)
+    x = torch.ones(1, 128, dtype=dtype, device=DEV)
+    scale = torch.ones(2, 1, dtype=torch.float32, device=DEV)
+    out = torch.empty(1, 256, dtype=dtype, device=DEV)
+    e.esimd_gemm_fp8_blockscale(x, raw.to(DEV), scale, out, 128, 128)
+    got = out[0].float().cpu()
+    exp = reference.to(dtype).float()
+    assert torch.equal(got[finite], exp[finite])
+    assert got[0x80] == 0.0
+    ones = torch.ones(256, dtype=torch.float32, device=DEV)
+    e.esimd_gemv_fp8_pern(x, raw.to(DEV), ones, out, 256, 128)
+    assert torch.equal(out[0].float().cpu()[finite], exp[finite])
+
+
+def test_act_quant_1x128_bit_exact(e):
+    x = torch.randn(37, 512, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16)
+    x[3, 128:256] = 0
+    xq, xs = e.act_quant_fp8_1x128(x.to(DEV))
+    rq, rs = fp8.quantize_act_1x128(x)
+    assert torch.equal(xs.cpu(), rs)
+    assert torch.equal(xq.cpu().view(torch.uint8), rq.view(torch.uint8))

@@ -1,0 +1,179 @@
+"""GPU parity of the MoE routing / grouped-GEMM ops against the CPU oracle."""
+import pytest
+import torch
+
+from gpu_util import DEV, assert_close
+from oracle import configs, fp8, int4, moe
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def e(lib_built):
+    if not torch.cuda.is_available():
+        pytest.fail("GPU test selected but no CUDA device is visible")
+    import custom_esimd_kernels_vllm as pkg
+    return pkg
+
+
+@pytest.mark.parametrize("T,E,k", [(4096, 128, 8), (33, 256, 8), (7, 128, 10), (5, 64, 2), (1, 8, 8)])
+def test_topk(e, T, E, k):
+    g = torch.Generator().manual_seed(T + E)
+    logits = torch.randn(T, E, generator=g).to(torch.float16)
+    w, ids = e.moe_topk_softmax(logits.to(DEV), k, E)
+    rw, rids = moe.topk_softmax(logits, k, True, torch.float16)
+    assert torch.equal(ids.cpu(), rids)
+    assert torch.allclose(w.cpu().float(), rw.float(), atol=2e-3, rtol=2e-3)
+    tv = torch.empty(T, k, dtype=torch.float16, device=DEV)
+    ti = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    e.esimd_moe_topk(logits.to(DEV), tv, ti, T)
+    assert torch.equal(ti.cpu(), rids)
+    w2, i2 = e.moe_topk_int4(logits.to(DEV), k, E, True)
+    assert torch.equal(i2.cpu(), rids)
+
+
+def test_topk_tie_takes_lowest_index(e):
+    logits = torch.zeros(3, 128, dtype=torch.float16)
+    logits[1, 5] = logits[1, 77] = 2.0
+    w, ids = e.moe_topk_softmax(logits.to(DEV), 4, 128)
+    assert ids[0].tolist() == [0, 1, 2, 3]
+    assert ids[1].tolist() == [5, 77, 0, 1]
+
+
+@pytest.mark.parametrize("T,E,k", [(4096, 128, 8), (130, 4, 1), (3, 1024, 2), (257, 16, 8)])
+def test_route_matches_stable_sort(e, T, E, k):
+    g = torch.Generator().manual_seed(T)
+    ids = torch.randint(0, E, (T, k), generator=g, dtype=torch.int32)
+    if E == 4:
+        ids[ids == 1] = 0                                   # an empty expert
+    off, tok, p2p, rows = e._impl.moe_route(ids.to(DEV), E)
+    roff, rtok, rp2p, rrows = moe.route(ids, E)
+    assert torch.equal(off.cpu(), roff) and torch.equal(tok.cpu(), rtok)
+    assert torch.equal(p2p.cpu(), rp2p) and torch.equal(rows.cpu(), rrows)
+    res = torch.ops.moe_int4_prefill_ops.moe_prefill_gather_forward_v2(ids.to(DEV), E)
+    assert torch.equal(res[0].cpu(), roff[:E]) and torch.equal(res[1].cpu(), rtok)
+    assert torch.equal(res[2].cpu(), rp2p) and torch.equal(res[3].cpu(), rrows)
+
+
+def test_route_drops_ids_outside_the_local_expert_range(e):
+    ids = torch.tensor([[3, 1], [1, 0], [3, 3], [7, 1]], dtype=torch.int32)
+    off, tok, p2p, rows = e._impl.moe_route(ids.to(DEV), 4)
+    assert off.cpu().tolist() == [0, 1, 4, 4, 7]
+    assert tok.cpu().tolist()[:7] == [3, 1, 2, 7, 0, 4, 5]
+    assert p2p.cpu().tolist() == [4, 1, 2, 0, 5, 6, -1, 3]
+
+
+def test_silu_mul_gather_combine(e):
+    g = torch.Generator().manual_seed(9)
+    gu = torch.randn(77, 256, generator=g).to(torch.bfloat16)
+    out = torch.ops.moe_int4_prefill_ops.moe_prefill_silu_mul_forward(gu.to(DEV))
+    assert_close(out, moe.silu_mul(gu).float(), tol=4e-3, what="silu_mul")
+    x = torch.randn(16, 64, generator=g).to(torch.bfloat16)
+    tokens = torch.randperm(64, generator=g).to(torch.int32)
+    xp = torch.ops.moe_int4_prefill_ops.moe_prefill_scatter_x_forward(x.to(DEV), tokens.to(DEV), 4)
+    assert torch.equal(xp.cpu(), x[(tokens // 4).long()])
+    y = torch.randn(64, 128, generator=g).to(torch.bfloat16)
+    w = torch.rand(16, 4, generator=g).to(torch.bfloat16)
+    o = torch.ops.moe_int4_prefill_ops.moe_prefill_accumulate_forward_v2(y.to(DEV), w.to(DEV))
+    assert_close(o, moe.combine(y, w).float(), tol=4e-3, what="accumulate")
+    perm = torch.randperm(64, generator=g).to(torch.int32)
+    o = torch.ops.moe_int4_prefill_ops.moe_prefill_accumulate_permuted_forward_v2(y.to(DEV), w.to(DEV), perm.to(DEV))
+    assert_close(o, moe.combine(y, w, perm).float(), tol=4e-3, what="accumulate permuted")
+
+
+def _experts_int4(E, N, K, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randint(0, 16, (E, N, K), generator=g, dtype=torch.uint8)
+    s = (0.002 + torch.randn(E, N, K // 128, generator=g).abs() * 0.01).to(dtype)
+    return q, s
+
+
+@pytest.mark.parametrize("rows", [[130, 0, 67, 9], [33, 40, 27, 36], [1, 0, 0, 2], [300, 5, 0, 70]])
+def test_grouped_int4_gemm_ragged_and_empty_experts(e, rows):
+    E, N, K = 4, 256, 256
+    q, s = _experts_int4(E, N, K, torch.float16, sum(rows))
+    total = sum(rows)
+    off = torch.tensor([0] + list(torch.tensor(rows).cumsum(0)), dtype=torch.int32)
+    x = (torch.randn(total, K, generator=torch.Generator().manual_seed(1)) * 0.2).half()
+    ref = moe.grouped_linear(x, int4.dequant(q, s, torch.float16), off)
+    out = e.moe_gemm_int4_nmajor(x.to(DEV), int4.pack_nmajor_i32(q).to(DEV), s.to(DEV), off.to(DEV), 128)
+    assert_close(out, ref, what=f"grouped int4 rows={rows}")
+    out = e.moe_gemm_int4_nmajor(x.to(DEV), int4.pack_nmajor_u8(q).to(DEV), s.to(DEV), off.to(DEV), 128)
+    assert_close(out, ref, what=f"grouped int4 u8 rows={rows}")
+
+
+@pytest.mark.parametrize("rows", [[130, 0, 67, 9], [33, 40, 27, 36], [1, 0, 0, 0]])
+def test_grouped_fp8_blockscale(e, rows):
+    E, N, K = 4, 256, 256
+    g = torch.Generator().manual_seed(20260713)
+    total = sum(rows)
+    off = torch.tensor([0] + list(torch.tensor(rows).cumsum(0)), dtype=torch.int32)
+    x = (torch.randn(total, K, generator=g) * 0.2).half()
+    wq, ws = fp8.quantize_block(torch.randn(E, N, K, generator=g) * 0.15)
+    ref = moe.grouped_linear(x, fp8.dequant_block(wq, ws), off)
+    out = torch.empty(total, N, dtype=torch.float16, device=DEV)
+    e.esimd_moe_gemm_fp8_blockscale(x.to(DEV), wq.to(DEV), ws.to(DEV), out, off.to(DEV), N, K, E)
+    assert_close(out, ref, what=f"grouped fp8 block rows={rows}")
+
+
+def test_grouped_fp8_e5m2_per_channel_and_per_expert(e):
+    E, N, K = 3, 128, 256
+    g = torch.Generator().manual_seed(4)
+    rows = [17, 0, 50]
+    off = torch.tensor([0, 17, 17, 67], dtype=torch.int32)
+    x = (torch.randn(67, K, generator=g) * 0.3).half()
+    w = torch.randn(E, N, K, generator=g)
+    w5 = w.to(torch.float8_e5m2)
+    sc = torch.rand(E, N, generator=g) * 0.1 + 0.01
+    wd = fp8.decode(w5, e5m2=True) * sc[:, :, None]
+    out = torch.empty(67, N, dtype=torch.float16, device=DEV)
+    e.esimd_moe_gemm_fp8(x.to(DEV), w5.view(torch.uint8).to(DEV), sc.to(DEV), out, off.to(DEV), N, K, E, 50)
+    assert_close(out, moe.grouped_linear(x, wd, off), what="grouped e5m2 per-N")
+    st = torch.rand(E, generator=g) * 0.1 + 0.01
+    wd = fp8.decode(w5, e5m2=True) * st[:, None, None]
+    e.esimd_moe_gemm_fp8_pert(x.to(DEV), w5.view(torch.uint8).to(DEV), st.to(DEV), out, off.to(DEV), N, K, E, 50)
+    assert_close(out, moe.grouped_linear(x, wd, off), what="grouped e5m2 per-expert")
+
+
+def test_scatter_fused_then_gather_roundtrip(e):
+    T, K, k, E = 40, 128, 4, 16
+    g = torch.Generator().manual_seed(2)
+    h = torch.randn(T, K, generator=g).half()
+    logits = torch.randn(T, E, generator=g).half()
+    tv = torch.empty(T, k, dtype=torch.float16, device=DEV)
+    ti = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    e.esimd_moe_topk(logits.to(DEV), tv, ti, T)
+    sh = torch.empty(T * k, K, dtype=torch.float16, device=DEV)
+    sw = torch.empty(T * k, dtype=torch.float16, device=DEV)
+    ids = torch.empty(T * k, dtype=torch.int32, device=DEV)
+    es = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    mx = torch.empty(1, dtype=torch.int32, device=DEV)
+    e.esimd_moe_scatter_fused(h.to(DEV), tv, ti, sh, sw, ids, es, mx, K, k, T, E)
+    roff, rtok, rp2p, rrows = moe.route(ti.cpu(), E)
+    assert torch.equal(es.cpu(), roff) and int(mx) == int(rrows.max())
+    assert torch.equal(sh.cpu(), h[(rtok // k).long()])
+    fin = torch.empty(T, K, dtype=torch.float16, device=DEV)
+    e.esimd_moe_gather(sh, ids.view(T, k), sw, fin, K, k, T)
+    # identity experts: gather of the scattered rows = sum_s w[t, s] * h[t] = h[t] (weights renormalised)
+    assert_close(fin, h.float() * tv.cpu().float().sum(1, keepdim=True), tol=4e-3, what="scatter/gather")
+
+
+def test_moe_pipeline_golden_and_ops(e, golden):
+    g = golden("moe_int4")
+    x, logits = torch.from_numpy(g["x"]), torch.from_numpy(g["logits"])
+    q13, s13 = torch.from_numpy(g["q13"]), torch.from_numpy(g["s13"])
+    q2, s2 = torch.from_numpy(g["q2"]), torch.from_numpy(g["s2"])
+    k, E = int(g["top_k"]), q13.shape[0]
+    out = e.moe_prefill_full_int4(x.to(DEV), logits.to(DEV), q13.to(DEV), s13.to(DEV), q2.to(DEV), s2.to(DEV), k, E)
+    assert_close(out, torch.from_numpy(g["out"]).float(), what="moe golden")
+
+
+@pytest.mark.parametrize("T", [64, 700])
+def test_moe_pipeline_config4_shape_reduced(e, T):
+    c = configs.c4(seed=T, T=T, E=16, top_k=4, H=512, I=256)
+    d13 = int4.dequant(c["q13"], c["s13"], torch.bfloat16)
+    d2 = int4.dequant(c["q2"], c["s2"], torch.bfloat16)
+    ref = moe.forward(c["x"], c["logits"], d13, d2, 4)
+    out = e.moe_prefill_full_int4(c["x"].to(DEV), c["logits"].to(DEV), int4.pack_nmajor_i32(c["q13"]).to(DEV),
+                                  c["s13"].to(DEV), int4.pack_nmajor_i32(c["q2"]).to(DEV), c["s2"].to(DEV), 4, 16)
+    assert_close(out, ref.float(), what=f"moe T={T}")
