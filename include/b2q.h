@@ -178,7 +178,8 @@ B2Q_API int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int
  * INT4: w is E stacked matrices in w_layout, scales E stacked.
  * Replaces moe_prefill_up/down_forward_v2 (:493-621), moe_gemm_int4_nmajor
  * (csrc/moe_batch/moe_int4.sycl:3373-3552).                                    */
-B2Q_API size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int act);
+/* gather != 0 when a row_map will be passed (the tcgen05 path stages the gathered rows). */
+B2Q_API size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int64_t K, int act, int gather);
 B2Q_API int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx,
                       const int32_t* row_map, int row_div,
                       const void* w, int w_layout, const void* scale, int scale_dtype,
@@ -196,6 +197,10 @@ B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
                      void* out, int64_t ldo, const int32_t* out_map,
                      int64_t rows, int64_t N, int64_t K, int act,
                      void* workspace, size_t workspace_bytes, void* stream);
+
+/* Code of the first bounded device-side wait that expired since the library was loaded
+ * (0 = none).  Synchronises the device; meant for tests and post-mortems.       */
+B2Q_API int b2q_device_status(int* out);
 
 /* Kernel selection override for benchmarking: 0 = automatic,
  * 1 = force the mma.sync streaming kernel, 2 = force the tcgen05 kernel.     */

@@ -235,12 +235,30 @@ int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int32_t* pe
   return moe_combine(y, w, w_dtype, perm, out, dtype, T, top_k, H, w_by_row, (cudaStream_t)stream);
 }
 
-size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int act) {
-  // tile lists for the largest (8-row) tiling of either kernel family, plus the
-  // un-activated [rows, N] intermediate the streaming kernel needs for SiLU*mul.
+size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int64_t K, int act, int gather) {
+  // [tile list for the smallest (8-row) tiling] [gathered activations rows x K] [un-activated rows x N]
   size_t b = tile_list_bytes(rows, E, 8);
+  if (gather) b += align_up((size_t)rows * (size_t)K * 2, 256);
   if (act != B2Q_ACT_NONE) b += align_up((size_t)rows * (size_t)N * 2, 256);
   return b;
+}
+
+int b2q_device_status(int* out) {
+  if (!out) return B2Q_ERR_NULL;
+  return umma_read_status(out);
+}
+
+// Shared tail of the grouped GEMMs once the kernel family is chosen: optional row gather in
+// front of the tcgen05 kernel, optional SiLU*mul behind either kernel.
+struct GroupedPlan {
+  uint8_t* tiles; uint8_t* xg; uint8_t* g;
+};
+static GroupedPlan plan_workspace(void* ws, int64_t rows, int E, int64_t K, bool gather) {
+  GroupedPlan pl;
+  pl.tiles = reinterpret_cast<uint8_t*>(ws);
+  pl.xg = pl.tiles + tile_list_bytes(rows, E, 8);
+  pl.g = pl.xg + (gather ? align_up((size_t)rows * (size_t)K * 2, 256) : 0);
+  return pl;
 }
 
 int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* row_map, int row_div, const void* w,
@@ -252,58 +270,62 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
   if (w_layout < 0 || w_layout > 3) return B2Q_ERR_LAYOUT;
   if (group != 128) return B2Q_ERR_SHAPE;
   if (rows < 0 || N <= 0 || K <= 0 || (K % group) != 0 || E <= 0 || ldx < K) return B2Q_ERR_SHAPE;
-  if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0)) return B2Q_ERR_SHAPE;
   if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL) return B2Q_ERR_UNSUPPORTED;
+  if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0 || ldo != N / 2)) return B2Q_ERR_SHAPE;
+  if (act == B2Q_ACT_NONE && ldo < N) return B2Q_ERR_SHAPE;
   if (E > 1024 || rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if (row_map && row_div <= 0) return B2Q_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(w) || !aligned16(workspace) || ((ldx * 2) & 15)) return B2Q_ERR_ALIGN;
-  if (workspace_bytes < b2q_moe_gemm_workspace_bytes(rows, E, N, act)) return B2Q_ERR_WORKSPACE;
+  if (workspace_bytes < b2q_moe_gemm_workspace_bytes(rows, E, N, K, act, row_map != nullptr)) return B2Q_ERR_WORKSPACE;
   if (rows == 0) return B2Q_OK;
   cudaStream_t st = (cudaStream_t)stream;
   const bool kmajor = (w_layout == B2Q_W4_KMAJOR || w_layout == B2Q_W4_KMAJOR_MARLIN);
+  const bool bf = act_dtype == B2Q_BF16;
   const int force = tls().force_kernel;
-  int32_t* tiles = reinterpret_cast<int32_t*>(workspace);
+  const GroupedPlan pl = plan_workspace(workspace, rows, E, K, row_map != nullptr);
+  int32_t* tiles = reinterpret_cast<int32_t*>(pl.tiles);
+  void* gemm_out = act == B2Q_ACT_NONE ? out : pl.g;
+  const int64_t gemm_ldo = act == B2Q_ACT_NONE ? ldo : N;
+  const int32_t* gemm_out_map = act == B2Q_ACT_NONE ? out_map : nullptr;
+  int rc;
 
   UmmaW4Args ua{};
-  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16);
+  ua.x = x; ua.ldx = ldx; ua.bf16 = bf;
   ua.w = w; ua.layout = w_layout; ua.scale = scale; ua.scale_dtype = scale_dtype;
   ua.s_stride_n = kmajor ? 1 : K / group; ua.s_stride_g = kmajor ? N : 1;
-  ua.out = out; ua.ldo = ldo; ua.M = (int)rows; ua.N = (int)N; ua.K = (int)K;
-  ua.expert_offsets = expert_offsets; ua.E = E; ua.row_map = row_map; ua.row_div = row_div; ua.out_map = out_map;
-  ua.act = act; ua.tiles = tiles;
+  ua.out = gemm_out; ua.ldo = gemm_ldo; ua.M = (int)rows; ua.N = (int)N; ua.K = (int)K;
+  ua.expert_offsets = expert_offsets; ua.E = E; ua.out_map = gemm_out_map; ua.tiles = tiles;
   const int64_t avg = (rows + E - 1) / E;
   const bool want_umma = force == 2 || (force == 0 && (kmajor || avg > 16));
   if (umma_w4_supported(ua) && want_umma) {
+    if (row_map) {
+      rc = gather_rows(x, row_map, row_div, pl.xg, rows, K, 2, st);
+      if (rc) return rc;
+      ua.x = pl.xg; ua.ldx = K;
+    }
     const int tile = umma_w4_token_tile(ua);
-    int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+    rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
     if (rc) return rc;
     ua.tile_cap = (int)((rows + tile - 1) / tile + E);
-    return umma_w4_linear(ua, st);
+    rc = umma_w4_linear(ua, st);
+  } else {
+    if (kmajor) return B2Q_ERR_UNSUPPORTED;
+    const int tile = grouped_tile(rows, E);
+    rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+    if (rc) return rc;
+    SmallMParams p{};
+    p.x = x; p.ldx = ldx;
+    p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K / 2;
+    p.scale = scale; p.scale_dtype = scale_dtype; p.s_stride_n = K / group; p.s_stride_g = 1;
+    p.M = (int)rows; p.N = (int)N; p.K = (int)K;
+    p.xor_mask = (w_layout == B2Q_W4_NMAJOR_S4) ? 0x88888888u : 0u;
+    p.tiles = tiles; p.expert_offsets = expert_offsets; p.row_map = row_map; p.row_div = row_div > 0 ? row_div : 1;
+    p.w_expert_bytes = N * (K / 2); p.s_expert_elems = N * (K / group);
+    p.out = gemm_out; p.ldo = gemm_ldo; p.out_map = gemm_out_map;
+    rc = smallm_int4(p, bf, tile, (int)((rows + tile - 1) / tile + E), st);
   }
-  if (kmajor) return B2Q_ERR_UNSUPPORTED;
-
-  const int tile = grouped_tile(rows, E);
-  int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
-  if (rc) return rc;
-  SmallMParams p{};
-  p.x = x; p.ldx = ldx;
-  p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K / 2;
-  p.scale = scale; p.scale_dtype = scale_dtype; p.s_stride_n = K / group; p.s_stride_g = 1;
-  p.M = (int)rows; p.N = (int)N; p.K = (int)K;
-  p.xor_mask = (w_layout == B2Q_W4_NMAJOR_S4) ? 0x88888888u : 0u;
-  p.tiles = tiles; p.expert_offsets = expert_offsets; p.row_map = row_map; p.row_div = row_div > 0 ? row_div : 1;
-  p.w_expert_bytes = N * (K / 2); p.s_expert_elems = N * (K / group);
-  const int cap = (int)((rows + tile - 1) / tile + E);
-  if (act == B2Q_ACT_NONE) {
-    p.out = out; p.ldo = ldo; p.out_map = out_map;
-    return smallm_int4(p, act_dtype == B2Q_BF16, tile, cap, st);
-  }
-  void* g = reinterpret_cast<uint8_t*>(workspace) + tile_list_bytes(rows, E, 8);
-  p.out = g; p.ldo = N; p.out_map = nullptr;
-  rc = smallm_int4(p, act_dtype == B2Q_BF16, tile, cap, st);
-  if (rc) return rc;
-  if (ldo != N / 2) return B2Q_ERR_SHAPE;
-  return silu_mul(g, out, act_dtype, rows, N / 2, out_map, st);
+  if (rc || act == B2Q_ACT_NONE) return rc;
+  return silu_mul(pl.g, out, act_dtype, rows, N / 2, out_map, st);
 }
 
 int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx, const int32_t* row_map, int row_div, const void* w,
@@ -318,57 +340,61 @@ int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx, const int32_t* r
   if (rows < 0 || N <= 0 || K <= 0 || (K % 16) != 0 || E <= 0 || ldx < K) return B2Q_ERR_SHAPE;
   if (scale_mode == B2Q_SCALE_BLOCK128 && ((K % 128) != 0 || (N % 128) != 0)) return B2Q_ERR_SHAPE;
   if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL) return B2Q_ERR_UNSUPPORTED;
-  if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0)) return B2Q_ERR_SHAPE;
+  if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0 || ldo != N / 2)) return B2Q_ERR_SHAPE;
+  if (act == B2Q_ACT_NONE && ldo < N) return B2Q_ERR_SHAPE;
   if (E > 1024 || rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if (row_map && row_div <= 0) return B2Q_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(w) || !aligned16(workspace) || ((ldx * 2) & 15)) return B2Q_ERR_ALIGN;
-  if (workspace_bytes < b2q_moe_gemm_workspace_bytes(rows, E, N, act)) return B2Q_ERR_WORKSPACE;
+  if (workspace_bytes < b2q_moe_gemm_workspace_bytes(rows, E, N, K, act, row_map != nullptr)) return B2Q_ERR_WORKSPACE;
   if (rows == 0) return B2Q_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  int32_t* tiles = reinterpret_cast<int32_t*>(workspace);
+  const bool bf = act_dtype == B2Q_BF16;
   const int force = tls().force_kernel;
+  const GroupedPlan pl = plan_workspace(workspace, rows, E, K, row_map != nullptr);
+  int32_t* tiles = reinterpret_cast<int32_t*>(pl.tiles);
+  void* gemm_out = act == B2Q_ACT_NONE ? out : pl.g;
+  const int64_t gemm_ldo = act == B2Q_ACT_NONE ? ldo : N;
+  const int32_t* gemm_out_map = act == B2Q_ACT_NONE ? out_map : nullptr;
   const int64_t kblocks = (K + 127) / 128, nblocks = (N + 127) / 128;
   const int64_t s_expert = scale_mode == B2Q_SCALE_CHANNEL ? N : (scale_mode == B2Q_SCALE_TENSOR ? 1 : nblocks * kblocks);
+  int rc;
 
   UmmaW8Args ua{};
-  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16);
+  ua.x = x; ua.ldx = ldx; ua.bf16 = bf;
   ua.w = w; ua.fmt = fp8_format; ua.scale = scale; ua.scale_dtype = B2Q_F32; ua.scale_mode = scale_mode;
-  ua.out = out; ua.ldo = ldo; ua.M = (int)rows; ua.N = (int)N; ua.K = (int)K;
-  ua.expert_offsets = expert_offsets; ua.E = E; ua.row_map = row_map; ua.row_div = row_div; ua.out_map = out_map;
-  ua.act = act; ua.tiles = tiles; ua.s_expert_elems = s_expert;
+  ua.out = gemm_out; ua.ldo = gemm_ldo; ua.M = (int)rows; ua.N = (int)N; ua.K = (int)K;
+  ua.expert_offsets = expert_offsets; ua.E = E; ua.out_map = gemm_out_map; ua.tiles = tiles; ua.s_expert_elems = s_expert;
   const int64_t avg = (rows + E - 1) / E;
   const bool want_umma = force == 2 || (force == 0 && avg > 16);
   if (umma_w8_supported(ua) && want_umma) {
+    if (row_map) {
+      rc = gather_rows(x, row_map, row_div, pl.xg, rows, K, 2, st);
+      if (rc) return rc;
+      ua.x = pl.xg; ua.ldx = K;
+    }
     const int tile = umma_w8_token_tile(ua);
-    int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+    rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
     if (rc) return rc;
     ua.tile_cap = (int)((rows + tile - 1) / tile + E);
-    return umma_w8_linear(ua, st);
+    rc = umma_w8_linear(ua, st);
+  } else {
+    const int tile = grouped_tile(rows, E);
+    rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
+    if (rc) return rc;
+    SmallMParams p{};
+    p.x = x; p.ldx = ldx;
+    p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K;
+    p.scale = scale; p.scale_dtype = B2Q_F32; p.s_stride_n = (scale_mode == B2Q_SCALE_CHANNEL) ? 1 : 0;
+    p.M = (int)rows; p.N = (int)N; p.K = (int)K;
+    p.tiles = tiles; p.expert_offsets = expert_offsets; p.row_map = row_map; p.row_div = row_div > 0 ? row_div : 1;
+    p.w_expert_bytes = N * K; p.s_expert_elems = s_expert;
+    p.out = gemm_out; p.ldo = gemm_ldo; p.out_map = gemm_out_map;
+    const int smode = scale_mode == B2Q_SCALE_BLOCK128 ? SM_BLOCK : SM_POST;
+    const int cap = (int)((rows + tile - 1) / tile + E);
+    rc = bf ? smallm_fp8_bf16(p, fp8_format, smode, tile, cap, st) : smallm_fp8_f16(p, fp8_format, smode, tile, cap, st);
   }
-
-  const int tile = grouped_tile(rows, E);
-  int rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
-  if (rc) return rc;
-  SmallMParams p{};
-  p.x = x; p.ldx = ldx;
-  p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K;
-  p.scale = scale; p.scale_dtype = B2Q_F32; p.s_stride_n = (scale_mode == B2Q_SCALE_CHANNEL) ? 1 : 0;
-  p.M = (int)rows; p.N = (int)N; p.K = (int)K;
-  p.tiles = tiles; p.expert_offsets = expert_offsets; p.row_map = row_map; p.row_div = row_div > 0 ? row_div : 1;
-  p.w_expert_bytes = N * K; p.s_expert_elems = s_expert;
-  const int smode = scale_mode == B2Q_SCALE_BLOCK128 ? SM_BLOCK : SM_POST;
-  const int cap = (int)((rows + tile - 1) / tile + E);
-  const bool bf = act_dtype == B2Q_BF16;
-  if (act == B2Q_ACT_NONE) {
-    p.out = out; p.ldo = ldo; p.out_map = out_map;
-    return bf ? smallm_fp8_bf16(p, fp8_format, smode, tile, cap, st) : smallm_fp8_f16(p, fp8_format, smode, tile, cap, st);
-  }
-  void* g = reinterpret_cast<uint8_t*>(workspace) + tile_list_bytes(rows, E, 8);
-  p.out = g; p.ldo = N; p.out_map = nullptr;
-  rc = bf ? smallm_fp8_bf16(p, fp8_format, smode, tile, cap, st) : smallm_fp8_f16(p, fp8_format, smode, tile, cap, st);
-  if (rc) return rc;
-  if (ldo != N / 2) return B2Q_ERR_SHAPE;
-  return silu_mul(g, out, act_dtype, rows, N / 2, out_map, st);
+  if (rc || act == B2Q_ACT_NONE) return rc;
+  return silu_mul(pl.g, out, act_dtype, rows, N / 2, out_map, st);
 }
 
 }  // extern "C"

@@ -1,11 +1,507 @@
-// placeholder until the tcgen05 kernels land
+// tcgen05 weight-only GEMM: out[tok, n] = sum_k x[tok, k] * dequant(W)[n, k].
+//
+// The 128 weight rows of a CTA's strip are the MMA's M dimension and the tokens its N
+// dimension ("swap-AB"), so one kernel serves decode (16..64 tokens) and prefill (256-token
+// tiles).  Warp roles, one CTA of 7 warps per output tile:
+//   warp 0     TMA producer of raw quantised weight tiles (runs up to RS stages ahead: this
+//              is the HBM stream)
+//   warp 1     tensor-memory owner and the single thread that issues tcgen05.mma
+//   warp 2     TMA producer of activation tiles [TOK x 64] (128-byte swizzle)
+//   warps 3-6  transform: raw int4 / fp8 -> 16-bit values written straight into the
+//              128-byte-swizzled K-major operand layout the MMA reads; afterwards the same
+//              warps drain the fp32 accumulator from tensor memory, apply per-row scales and
+//              store out[tok, n].
+// Every mbarrier wait is bounded; on expiry the CTA records a code in a status word, releases
+// its tensor memory and returns.
+//
+// Reference counterparts: GEMM_int4_pgrp_kernel (csrc/xpu/esimd_kernels/int4_GEMM.h:81-270),
+// FP8_GEMM_DPAS_V9 (fp8_GEMM_pert.h:2940-3150), moe_prefill_up/down_forward_kernel
+// (csrc/moe_prefill/moe_prefill_int4.sycl:121-395), moe_gemm_block_prefill_kernel
+// (fp8_moe_gemm_blockscale.h:187-302).
 #include "umma_gemm.cuh"
+#include "sm100.cuh"
+#include "smallm.cuh"   // nib2_to_act / fp8x2_to_act / lds128
+
 namespace b2q {
-bool umma_w4_supported(const UmmaW4Args&) { return false; }
-int umma_w4_token_tile(const UmmaW4Args&) { return 64; }
-int umma_w4_linear(const UmmaW4Args&, cudaStream_t) { return B2Q_ERR_UNSUPPORTED; }
-bool umma_w8_supported(const UmmaW8Args&) { return false; }
-int umma_w8_token_tile(const UmmaW8Args&) { return 64; }
-int umma_w8_linear(const UmmaW8Args&, cudaStream_t) { return B2Q_ERR_UNSUPPORTED; }
+
+using namespace sm100;
+
+__device__ int g_umma_status = 0;
+
+enum { WK_W4N = 0, WK_W4K = 1, WK_W8 = 2 };
+enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWEMPTY = 105, ST_ACCUM = 106 };
+
+struct UmmaWoParams {
+  const void* scale; int scale_dtype; int scale_mode;      // scale_mode: B2Q_SCALE_* (fp8) ; ignored for int4
+  int64_t s_stride_n, s_stride_g, s_expert_elems;
+  void* out; int64_t ldo;
+  int M, N, K;
+  int marlin; uint32_t xor_mask; int e5m2;
+  const int32_t* tiles; const int32_t* expert_offsets; const int32_t* out_map;
+  int w_rows_per_expert;     // tensor-map rows per expert: N (N-major) or K/8 (K-major)
+  int* status;
+};
+
+template <bool BF16> __device__ __forceinline__ uint32_t pack2f(float a, float b) {
+  uint32_t r;
+  if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+  return r;
+}
+template <bool BF16> __device__ __forceinline__ uint32_t mul2(uint32_t a, uint32_t b) {
+  if constexpr (BF16) {
+    __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  } else {
+    __half2 r = __hmul2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<__half2*>(&b));
+    return *reinterpret_cast<uint32_t*>(&r);
+  }
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
+
+// One int32 of eight nibbles -> eight 16-bit values (q - 8) * s in k order (one 16-byte chunk).
+// FAST: the scale has the activation dtype, so a packed 16-bit multiply rounds exactly like
+// ((q - 8).float() * s.float()).to(dtype).  Otherwise the product is formed in fp32.
+template <bool BF16, bool FAST>
+__device__ __forceinline__ void w4_word(uint32_t w, uint32_t s2, float sf, bool marlin, uint32_t (&o)[4]) {
+  if constexpr (FAST) {
+    uint32_t p0 = mul2<BF16>(nib2_to_act<BF16>(w), s2);
+    uint32_t p1 = mul2<BF16>(nib2_to_act<BF16>(w >> 4), s2);
+    uint32_t p2 = mul2<BF16>(nib2_to_act<BF16>(w >> 8), s2);
+    uint32_t p3 = mul2<BF16>(nib2_to_act<BF16>(w >> 12), s2);
+    if (marlin) { const uint32_t t = p1; p1 = p2; p2 = t; }
+    const uint32_t q0 = __byte_perm(p0, p1, 0x5410), q1 = __byte_perm(p0, p1, 0x7632);
+    const uint32_t q2 = __byte_perm(p2, p3, 0x5410), q3 = __byte_perm(p2, p3, 0x7632);
+    o[0] = q0; o[1] = marlin ? q1 : q2; o[2] = marlin ? q2 : q1; o[3] = q3;
+  } else {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int slot = marlin ? ((j & 3) * 2 + (j >> 2)) : j;
+      v[j] = (float)((int)((w >> (4 * slot)) & 0xFu) - 8) * sf;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[j] = pack2f<BF16>(v[2 * j], v[2 * j + 1]);
+  }
+}
+
+// Four fp8 bytes -> four 16-bit values in k order.  SCALED folds an fp32 scale in (one rounding);
+// otherwise bf16 results carry an exact 2^-112 that the epilogue removes.
+template <bool BF16, bool SCALED>
+__device__ __forceinline__ void w8_word(uint32_t w, bool e5m2, float sf, uint32_t& o0, uint32_t& o1) {
+  if constexpr (!SCALED) {
+    if (e5m2) { o0 = fp8x2_to_act<BF16, true>(w); o1 = fp8x2_to_act<BF16, true>(w >> 16); }
+    else { o0 = fp8x2_to_act<BF16, false>(w); o1 = fp8x2_to_act<BF16, false>(w >> 16); }
+  } else {
+    uint32_t h0, h1;
+    if (e5m2) { h0 = fp8x2_to_act<false, true>(w); h1 = fp8x2_to_act<false, true>(w >> 16); }
+    else { h0 = fp8x2_to_act<false, false>(w); h1 = fp8x2_to_act<false, false>(w >> 16); }
+    const float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h0));
+    const float2 f1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
+    o0 = pack2f<BF16>(f0.x * sf, f0.y * sf);
+    o1 = pack2f<BF16>(f1.x * sf, f1.y * sf);
+  }
+}
+
+template <int TOK> struct UmmaCfg {
+  static constexpr int S = 4;                        // operand stages (64 k each)
+  static constexpr int RS = TOK >= 256 ? 2 : 4;      // raw weight stages (16 KB each)
+  static constexpr int A_BYTES = 128 * 128;          // 128 rows x 64 16-bit values
+  static constexpr int X_BYTES = TOK * 128;
+  static constexpr int RAW_BYTES = 16384;
+  static constexpr int SMEM = S * (A_BYTES + X_BYTES) + RS * RAW_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = TOK < 32 ? 32 : TOK;
+};
+
+template <int WK, bool BF16, int TOK, bool FAST>
+__global__ void __launch_bounds__(224, 1)
+umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const UmmaWoParams p) {
+  using Cfg = UmmaCfg<TOK>;
+  constexpr int S = Cfg::S, RS = Cfg::RS;
+  constexpr int CPR = (WK == WK_W8) ? 2 : 4;          // 64-k chunks per raw stage
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_smem = base;
+  const uint32_t x_smem = a_smem + S * Cfg::A_BYTES;
+  const uint32_t raw_smem = x_smem + S * Cfg::X_BYTES;
+  const uint32_t bar = raw_smem + RS * Cfg::RAW_BYTES;
+  // barrier map (8 bytes each)
+  const uint32_t x_full = bar, a_full = bar + 8 * S, ab_empty = bar + 16 * S;
+  const uint32_t raw_full = bar + 24 * S, raw_empty = raw_full + 8 * RS, accum_full = raw_empty + 8 * RS;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (accum_full + 8 - base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + (accum_full + 16 - base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // ---- which tile ----
+  int tok0 = blockIdx.x * TOK, xrow0 = 0, M = p.M, expert = 0;
+  if (p.tiles) {
+    if ((int)blockIdx.x >= p.tiles[0]) return;
+    const int2 td = reinterpret_cast<const int2*>(p.tiles + 4)[blockIdx.x];
+    expert = td.x; tok0 = td.y;
+    xrow0 = p.expert_offsets[expert];
+    M = p.expert_offsets[expert + 1] - xrow0;
+  }
+  const int n0 = blockIdx.y * 128;
+  const int nk = p.K / 64;
+  const int64_t sbase = (int64_t)expert * p.s_expert_elems;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(a_full + 8 * i, 128); mbar_init(ab_empty + 8 * i, 1); }
+    for (int i = 0; i < RS; ++i) { mbar_init(raw_full + 8 * i, 1); mbar_init(raw_empty + 8 * i, 128); }
+    mbar_init(accum_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- raw weight producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_w);
+      const int nraw = (nk + CPR - 1) / CPR;
+      for (int r = 0; r < nraw; ++r) {
+        const int rs = r % RS;
+        if (r >= RS && !mbar_wait(raw_empty + 8 * rs, ((r / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) break;
+        mbar_expect_tx(raw_full + 8 * rs, Cfg::RAW_BYTES);
+        if constexpr (WK == WK_W4K)
+          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, n0, expert * p.w_rows_per_expert + r * 32, raw_full + 8 * rs);
+        else
+          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, r * 128, expert * p.w_rows_per_expert + n0, raw_full + 8 * rs);
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------- activation producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_x);
+      for (int c = 0; c < nk; ++c) {
+        const int s = c % S;
+        if (c >= S && !mbar_wait(ab_empty + 8 * s, ((c / S) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break;
+        mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
+        tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, c * 64, xrow0 + tok0, x_full + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(BF16 ? 1u : 0u, BF16 ? 1u : 0u, 128, TOK);
+      bool ok = true;
+      for (int c = 0; c < nk && ok; ++c) {
+        const int s = c % S;
+        const uint32_t par = (c / S) & 1;
+        ok = mbar_wait(x_full + 8 * s, par, abort_flag, p.status, ST_XFULL) &&
+             mbar_wait(a_full + 8 * s, par, abort_flag, p.status, ST_AFULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t da = smem_desc_sw128(a_smem + s * Cfg::A_BYTES);
+        const uint64_t db = smem_desc_sw128(x_smem + s * Cfg::X_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          mma_f16(tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (c > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(ab_empty + 8 * s);
+      }
+      if (ok) tc_commit(accum_full);
+    }
+  } else {
+    // ---------------- transform, then epilogue (warps 3..6) ----------------
+    const int t = threadIdx.x - 96;          // 0..127: weight row (N-major / fp8) or column (K-major) in the strip
+    const int nraw = (nk + CPR - 1) / CPR;
+    int nrow = n0 + t; if (nrow >= p.N) nrow = p.N - 1;
+    bool ok = true;
+    for (int r = 0; r < nraw && ok; ++r) {
+      const int rs = r % RS;
+      ok = mbar_wait(raw_full + 8 * rs, (r / RS) & 1, abort_flag, p.status, ST_RAWFULL);
+      if (!ok) break;
+      const uint32_t rawb = raw_smem + rs * Cfg::RAW_BYTES;
+#pragma unroll 1
+      for (int j = 0; j < CPR; ++j) {
+        const int c = r * CPR + j;
+        if (c >= nk) break;
+        const int s = c % S;
+        if (c >= S) { ok = mbar_wait(ab_empty + 8 * s, ((c / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); if (!ok) break; }
+        const uint32_t ab = a_smem + s * Cfg::A_BYTES + t * 128;
+        const int sw = t & 7;
+        if constexpr (WK == WK_W4N || WK == WK_W4K) {
+          const int g = (c * 64) >> 7;
+          uint32_t s2 = 0; float sf = 0.f;
+          const int64_t si = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)g * p.s_stride_g;
+          if constexpr (FAST) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si]; s2 = sv | (sv << 16); }
+          else sf = load_scalar(p.scale, si, p.scale_dtype);
+          if constexpr (WK == WK_W4N) {
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint4 rv = lds128(rawb + t * 128 + (((2 * j + h) ^ sw) << 4));
+              const uint32_t ww[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint32_t o[4];
+                w4_word<BF16, FAST>(ww[i] ^ p.xor_mask, s2, sf, false, o);
+                sts128(ab + (((4 * h + i) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const uint32_t w = lds32(rawb + ((8 * j + i) * 128 + t) * 4);
+              uint32_t o[4];
+              w4_word<BF16, FAST>(w, s2, sf, p.marlin != 0, o);
+              sts128(ab + ((i ^ sw) << 4), o[0], o[1], o[2], o[3]);
+            }
+          }
+        } else {
+          const bool blockscale = (p.scale_mode == B2Q_SCALE_BLOCK128);
+          float sf = 1.f;
+          if (blockscale)
+            sf = reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * ((p.K + 127) >> 7) + ((c * 64) >> 7)];
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            const uint4 rv = lds128(rawb + t * 128 + (((4 * j + c4) ^ sw) << 4));
+            uint32_t o[8];
+            if (blockscale) {
+              w8_word<BF16, true>(rv.x, p.e5m2, sf, o[0], o[1]); w8_word<BF16, true>(rv.y, p.e5m2, sf, o[2], o[3]);
+              w8_word<BF16, true>(rv.z, p.e5m2, sf, o[4], o[5]); w8_word<BF16, true>(rv.w, p.e5m2, sf, o[6], o[7]);
+            } else {
+              w8_word<BF16, false>(rv.x, p.e5m2, sf, o[0], o[1]); w8_word<BF16, false>(rv.y, p.e5m2, sf, o[2], o[3]);
+              w8_word<BF16, false>(rv.z, p.e5m2, sf, o[4], o[5]); w8_word<BF16, false>(rv.w, p.e5m2, sf, o[6], o[7]);
+            }
+            sts128(ab + (((2 * c4) ^ sw) << 4), o[0], o[1], o[2], o[3]);
+            sts128(ab + (((2 * c4 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+          }
+        }
+        fence_proxy_async();
+        mbar_arrive(a_full + 8 * s);
+      }
+      mbar_arrive(raw_empty + 8 * rs);
+    }
+
+    // ---------------- epilogue ----------------
+    if (ok) ok = mbar_wait(accum_full, 0, abort_flag, p.status, ST_ACCUM);
+    if (ok) {
+      tc_fence_after();
+      using A = Act<BF16>;
+      using T = typename A::T;
+      const int quad = warp & 3;                   // tensor-memory lane quadrant this warp may read
+      const int n = n0 + quad * 32 + lane;
+      float post = 1.f;
+      if constexpr (WK == WK_W8) {
+        if (p.scale_mode != B2Q_SCALE_BLOCK128) {
+          post = (BF16 ? 5192296858534827628530496329220096.0f : 1.0f);   // 2^112 undoes the bf16 bit trick
+          const int nn = n < p.N ? n : p.N - 1;
+          post *= load_scalar(p.scale, sbase + (p.scale_mode == B2Q_SCALE_CHANNEL ? nn : 0), p.scale_dtype);
+        }
+      }
+      T* outp = reinterpret_cast<T*>(p.out);
+      constexpr int CB = TOK >= 32 ? 32 : 16;
+#pragma unroll 1
+      for (int cb = 0; cb < TOK; cb += CB) {
+        if (tok0 + cb >= M) break;
+        uint32_t r[32];
+        if constexpr (CB == 32) tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + cb, r);
+        else { uint32_t r16[16]; tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + cb, r16);
+#pragma unroll
+               for (int i = 0; i < 16; ++i) r[i] = r16[i]; }
+        tmem_ld_wait();
+        if (n < p.N) {
+#pragma unroll
+          for (int i = 0; i < CB; ++i) {
+            const int tok = tok0 + cb + i;
+            if (tok < M) {
+              int64_t orow = xrow0 + tok;
+              if (p.out_map) orow = p.out_map[orow];
+              outp[orow * p.ldo + n] = A::from_f(__uint_as_float(r[i]) * post);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, Cfg::TMEM_COLS); }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+PFN_tensorMapEncodeTiled tensor_map_encoder() {
+  static PFN_tensorMapEncodeTiled fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_tensorMapEncodeTiled>(p);
+  }
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows, uint64_t cols,
+                 uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz) {
+  PFN_tensorMapEncodeTiled enc = tensor_map_encoder();
+  if (!enc) return B2Q_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (pitch_bytes & 15u)) return B2Q_ERR_ALIGN;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  (void)elem_bytes;
+  return r == CUDA_SUCCESS ? B2Q_OK : B2Q_ERR_CUDA;
+}
+
+static int* status_ptr() {
+  static thread_local int* ptr[16] = {nullptr};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) return nullptr;
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_umma_status) != cudaSuccess) return nullptr;
+    ptr[dev] = reinterpret_cast<int*>(p);
+  }
+  return ptr[dev];
+}
+
+int umma_read_status(int* out) {
+  int* p = status_ptr();
+  if (!p) return B2Q_ERR_CUDA;
+  return cuda_status(cudaMemcpy(out, p, sizeof(int), cudaMemcpyDeviceToHost));
+}
+
+static int pick_tok(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256))); }
+
+template <int WK, bool BF16, int TOK, bool FAST>
+static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWoParams& p, int token_tiles, cudaStream_t st) {
+  using Cfg = UmmaCfg<TOK>;
+  auto kern = umma_wo_kernel<WK, BF16, TOK, FAST>;
+  static thread_local bool configured[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return B2Q_ERR_CUDA;
+    if (dev < 16) configured[dev] = true;
+  }
+  dim3 grid(token_tiles, (p.N + 127) / 128, 1);
+  kern<<<grid, 224, Cfg::SMEM, st>>>(tw, tx, p);
+  note_launch("umma_wo");
+  return launch_status();
+}
+
+template <int WK, bool BF16, bool FAST>
+static int launch_tok(int tok, const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWoParams& p, int tiles, cudaStream_t st) {
+  switch (tok) {
+    case 16: return launch_one<WK, BF16, 16, FAST>(tw, tx, p, tiles, st);
+    case 32: return launch_one<WK, BF16, 32, FAST>(tw, tx, p, tiles, st);
+    case 64: return launch_one<WK, BF16, 64, FAST>(tw, tx, p, tiles, st);
+    case 128: return launch_one<WK, BF16, 128, FAST>(tw, tx, p, tiles, st);
+    default: return launch_one<WK, BF16, 256, FAST>(tw, tx, p, tiles, st);
+  }
+}
+
+template <int WK>
+static int launch_wk(bool bf16, bool fast, int tok, const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWoParams& p,
+                     int tiles, cudaStream_t st) {
+  if (bf16) return fast ? launch_tok<WK, true, true>(tok, tw, tx, p, tiles, st) : launch_tok<WK, true, false>(tok, tw, tx, p, tiles, st);
+  return fast ? launch_tok<WK, false, true>(tok, tw, tx, p, tiles, st) : launch_tok<WK, false, false>(tok, tw, tx, p, tiles, st);
+}
+
+static int grouped_tok(int rows, int E) {
+  const int avg = E > 0 ? (rows + E - 1) / E : rows;
+  return avg <= 16 ? 16 : (avg <= 32 ? 32 : (avg <= 96 ? 64 : 128));
+}
+
+bool umma_w4_supported(const UmmaW4Args& a) {
+  if (a.K % 128 != 0 || a.K < 64) return false;
+  if (!aligned16(a.x) || !aligned16(a.w) || ((a.ldx * 2) & 15)) return false;
+  const bool kmajor = a.layout == B2Q_W4_KMAJOR || a.layout == B2Q_W4_KMAJOR_MARLIN;
+  if (kmajor && (a.N % 4) != 0) return false;              // tensor-map pitch must be a multiple of 16 bytes
+  if (a.act != B2Q_ACT_NONE) return false;                 // activation is applied by a separate kernel
+  if (a.row_map) return false;                             // rows are gathered by the caller first
+  return tensor_map_encoder() != nullptr && status_ptr() != nullptr;
+}
+int umma_w4_token_tile(const UmmaW4Args& a) { return a.expert_offsets ? grouped_tok(a.M, a.E) : pick_tok(a.M); }
+
+int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
+  const bool kmajor = a.layout == B2Q_W4_KMAJOR || a.layout == B2Q_W4_KMAJOR_MARLIN;
+  const bool grouped = a.expert_offsets != nullptr;
+  const int E = grouped ? a.E : 1;
+  const int tok = umma_w4_token_tile(a);
+  CUtensorMap tw, tx;
+  int rc;
+  if (kmajor)
+    rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, a.w, (uint64_t)E * (a.K / 8), a.N, (uint64_t)a.N * 4, 32, 128,
+                      CU_TENSOR_MAP_SWIZZLE_NONE);
+  else
+    rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)E * a.N, a.K / 2, (uint64_t)a.K / 2, 128, 128,
+                      CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tx, a.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x, a.M, a.K,
+                    (uint64_t)a.ldx * 2, tok, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  UmmaWoParams p{};
+  p.scale = a.scale; p.scale_dtype = a.scale_dtype; p.scale_mode = 0;
+  p.s_stride_n = a.s_stride_n; p.s_stride_g = a.s_stride_g;
+  p.s_expert_elems = (int64_t)a.N * (a.K / 128);
+  p.out = a.out; p.ldo = a.ldo; p.M = a.M; p.N = a.N; p.K = a.K;
+  p.marlin = a.layout == B2Q_W4_KMAJOR_MARLIN; p.xor_mask = a.layout == B2Q_W4_NMAJOR_S4 ? 0x88888888u : 0u;
+  p.tiles = grouped ? a.tiles : nullptr; p.expert_offsets = a.expert_offsets; p.out_map = a.out_map;
+  p.w_rows_per_expert = kmajor ? a.K / 8 : a.N;
+  p.status = status_ptr();
+  const bool fast = (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
+  const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
+  return kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)
+                : launch_wk<WK_W4N>(a.bf16, fast, tok, tw, tx, p, tiles, st);
+}
+
+bool umma_w8_supported(const UmmaW8Args& a) {
+  if (a.K % 64 != 0) return false;
+  if (!aligned16(a.x) || !aligned16(a.w) || ((a.ldx * 2) & 15)) return false;
+  if (a.scale_mode == B2Q_SCALE_BLOCK128 && ((a.N % 128) != 0 || (a.K % 128) != 0) && a.expert_offsets) return false;
+  if (a.act != B2Q_ACT_NONE || a.row_map) return false;
+  return tensor_map_encoder() != nullptr && status_ptr() != nullptr;
+}
+int umma_w8_token_tile(const UmmaW8Args& a) { return a.expert_offsets ? grouped_tok(a.M, a.E) : pick_tok(a.M); }
+
+int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st) {
+  const bool grouped = a.expert_offsets != nullptr;
+  const int E = grouped ? a.E : 1;
+  const int tok = umma_w8_token_tile(a);
+  CUtensorMap tw, tx;
+  int rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, (uint64_t)E * a.N, a.K, (uint64_t)a.K, 128, 128,
+                        CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tx, a.bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.x, a.M, a.K,
+                    (uint64_t)a.ldx * 2, tok, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  UmmaWoParams p{};
+  p.scale = a.scale; p.scale_dtype = a.scale_dtype; p.scale_mode = a.scale_mode;
+  p.s_expert_elems = a.s_expert_elems;
+  p.out = a.out; p.ldo = a.ldo; p.M = a.M; p.N = a.N; p.K = a.K;
+  p.e5m2 = a.fmt == B2Q_E5M2;
+  p.tiles = grouped ? a.tiles : nullptr; p.expert_offsets = a.expert_offsets; p.out_map = a.out_map;
+  p.w_rows_per_expert = a.N;
+  p.status = status_ptr();
+  const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
+  return launch_wk<WK_W8>(a.bf16, true, tok, tw, tx, p, tiles, st);
+}
+
 int umma_w8a8_block(const UmmaW8A8Args&, cudaStream_t) { return B2Q_ERR_UNSUPPORTED; }
+
 }  // namespace b2q

@@ -48,4 +48,7 @@ int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st);
 
 int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st);
 
+// First device-side wait timeout recorded since the library was loaded (0 = none).  Synchronises.
+int umma_read_status(int* out);
+
 }  // namespace b2q

@@ -255,7 +255,7 @@ def moe_gemm_int4(x, weight, scale, expert_offsets, rows, *, row_map=None, row_d
     _chk(expert_offsets.dtype == torch.int32 and expert_offsets.numel() == E + 1, "expert_offsets must be int32 [E+1]")
     n_out = N // 2 if act == L.ACT_SILU_MUL else N
     out = torch.empty(out_rows if out_rows is not None else rows, n_out, dtype=x.dtype, device=x.device)
-    wsb = L.lib.b2q_moe_gemm_workspace_bytes(rows, E, N, act)
+    wsb = L.lib.b2q_moe_gemm_workspace_bytes(rows, E, N, K, act, 1 if row_map is not None else 0)
     ws = torch.empty(wsb, dtype=torch.uint8, device=x.device)
     with L.on_device(x):
         L.check(L.lib.b2q_moe_gemm_int4(x.data_ptr(), L.dt(x), x.stride(0), L.ptr(row_map), row_div,
@@ -278,7 +278,7 @@ def moe_gemm_fp8(x, weight, scale, expert_offsets, rows, scale_mode, *, out=None
     n_out = N // 2 if act == L.ACT_SILU_MUL else N
     if out is None:
         out = torch.empty(rows, n_out, dtype=x.dtype, device=x.device)
-    wsb = L.lib.b2q_moe_gemm_workspace_bytes(rows, E, N, act)
+    wsb = L.lib.b2q_moe_gemm_workspace_bytes(rows, E, N, K, act, 1 if row_map is not None else 0)
     ws = torch.empty(wsb, dtype=torch.uint8, device=x.device)
     with L.on_device(x):
         L.check(L.lib.b2q_moe_gemm_fp8(x.data_ptr(), L.dt(x), x.stride(0), L.ptr(row_map), row_div,

@@ -37,7 +37,8 @@ _SIGS = {
     "b2q_gather_rows": (i32, [vp, vp, i32, vp, i64, i64, i32, vp]),
     "b2q_silu_mul": (i32, [vp, vp, i32, i64, i64, vp]),
     "b2q_moe_combine": (i32, [vp, vp, i32, vp, vp, i32, i64, i32, i64, i32, vp]),
-    "b2q_moe_gemm_workspace_bytes": (sz, [i64, i32, i64, i32]),
+    "b2q_moe_gemm_workspace_bytes": (sz, [i64, i32, i64, i64, i32, i32]),
+    "b2q_device_status": (i32, [vp]),
     "b2q_moe_gemm_int4": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
                                 i64, i64, i64, i32, i32, vp, sz, vp]),
     "b2q_moe_gemm_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
@@ -117,6 +118,13 @@ def launch_count() -> int:
 
 def last_kernel() -> str:
     return lib.b2q_last_kernel().decode()
+
+
+def device_status() -> int:
+    """Code of the first expired device-side wait (0 = none); synchronises."""
+    v = C.c_int(0)
+    check(lib.b2q_device_status(C.addressof(v)))
+    return int(v.value)
 
 
 def set_force_kernel(which: int) -> None:

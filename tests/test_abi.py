@@ -71,9 +71,10 @@ def test_null_and_shape_errors_need_no_device(lib_built):
 def test_workspace_size_queries(lib_built):
     from custom_esimd_kernels_vllm import _lib as L
     assert L.lib.b2q_moe_route_workspace_bytes(32768, 128) == 128 * 128 * 4
-    small = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 0)
-    big = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 1)
+    small = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 512, 0, 0)
+    big = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 512, 1, 0)
     assert big >= small + 1024 * 256 * 2
+    assert L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 512, 0, 1) >= small + 1024 * 512 * 2
 
 
 def test_ops_refuse_cpu_tensors(lib_built):

@@ -165,7 +165,8 @@ def test_moe_pipeline_golden_and_ops(e, golden):
     q2, s2 = torch.from_numpy(g["q2"]), torch.from_numpy(g["s2"])
     k, E = int(g["top_k"]), q13.shape[0]
     out = e.moe_prefill_full_int4(x.to(DEV), logits.to(DEV), q13.to(DEV), s13.to(DEV), q2.to(DEV), s2.to(DEV), k, E)
-    assert_close(out, torch.from_numpy(g["out"]).float(), what="moe golden")
+    # 16-bit roundings between the stages: wider gate for the whole pipeline than for one GEMM
+    assert_close(out, torch.from_numpy(g["out"]).float(), tol=3e-2, what="moe golden")
 
 
 @pytest.mark.parametrize("T", [64, 700])
@@ -176,4 +177,4 @@ def test_moe_pipeline_config4_shape_reduced(e, T):
     ref = moe.forward(c["x"], c["logits"], d13, d2, 4)
     out = e.moe_prefill_full_int4(c["x"].to(DEV), c["logits"].to(DEV), int4.pack_nmajor_i32(c["q13"]).to(DEV),
                                   c["s13"].to(DEV), int4.pack_nmajor_i32(c["q2"]).to(DEV), c["s2"].to(DEV), 4, 16)
-    assert_close(out, ref.float(), what=f"moe T={T}")
+    assert_close(out, ref.float(), tol=3e-2, what=f"moe T={T}")
