@@ -111,12 +111,18 @@ B2Q_API int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx,
  * csrc/xpu/torch_extension_gemm.cc:14-28; kernels fp8_GEMV_v2.h:46-403,
  * fp8_GEMM_pert.h:4030-4075, fp8_GEMM_blockscale.h:64-223).
  * w is [N, K] one byte per element, row-major.  Activation stays 16-bit
- * (w8a16); e4m3 decode is exact including subnormals.  K % 16 == 0.           */
+ * (w8a16); e4m3 decode is exact including subnormals.  K % 16 == 0.
+ * workspace is optional (NULL / 0 allowed).  With at least
+ * b2q_linear_fp8_workspace_bytes() of scratch, bf16 activations are first rewritten
+ * as fp16 times a per-token power of two (exact for every element within 2^-31 of
+ * its row maximum), which makes the in-kernel fp8 decode four times cheaper.        */
+B2Q_API size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t K);
 B2Q_API int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx,
                    const void* w, int fp8_format,
                    const void* scale, int scale_dtype, int scale_mode,
                    void* out, int64_t ldo,
-                   int64_t M, int64_t N, int64_t K, void* stream);
+                   int64_t M, int64_t N, int64_t K,
+                   void* workspace, size_t workspace_bytes, void* stream);
 
 /* Per-token, per-128-column dynamic e4m3 quantisation of activations:
  * xs[m, kb] = max(amax(x[m, 128kb:128kb+128]), 1e-12) / 448 ; xq = e4m3(x / xs).

@@ -40,7 +40,8 @@ def _newest_header():
 
 
 def _compile(nvcc, src, obj, verbose):
-    cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
+    extra = os.environ.get("B2Q_EXTRA_NVCC_FLAGS", "").split()      # e.g. -DB2Q_UMMA_PROF for in-kernel wait timers
+    cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))

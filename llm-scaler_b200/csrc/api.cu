@@ -22,6 +22,7 @@ int gather_rows(const void*, const int32_t*, int, void*, int64_t, int64_t, int, 
 int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t);
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
+int act_to_scaled_f16(const void*, int64_t, void*, float*, int64_t, int, cudaStream_t);
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -116,7 +117,9 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   ua.s_stride_n = s_stride_n; ua.s_stride_g = s_stride_g;
   ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
   const bool umma_ok = umma_w4_supported(ua);
-  const bool want_umma = force == 2 || (force == 0 && (kmajor || M > 32));
+  // measured on B200: the mma.sync streaming kernel wins only for a handful of tokens (its per-token cost is
+  // fragment traffic), the tcgen05 kernel is flat in M up to 64 and the only one for K-major layouts and prefill
+  const bool want_umma = force == 2 || (force == 0 && (kmajor || M > 8));
   if (umma_ok && want_umma) return umma_w4_linear(ua, st);
   if (kmajor) return B2Q_ERR_UNSUPPORTED;
 
@@ -129,9 +132,13 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   return smallm_int4(p, act_dtype == B2Q_BF16, (int)M, 0, st);
 }
 
+size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t K) {
+  return align_up((size_t)M * (size_t)K * 2, 256) + align_up((size_t)M * 4, 256);
+}
+
 int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
                    int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
-                   void* stream) {
+                   void* workspace, size_t workspace_bytes, void* stream) {
   if (!x || !w || !scale || !out) return B2Q_ERR_NULL;
   if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
   if (fp8_format != B2Q_E4M3 && fp8_format != B2Q_E5M2) return B2Q_ERR_DTYPE;
@@ -147,12 +154,23 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
   const int force = tls().force_kernel;
 
   UmmaW8Args ua{};
-  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16);
+  ua.x = x; ua.ldx = ldx; ua.bf16 = (act_dtype == B2Q_BF16); ua.out_bf16 = ua.bf16; ua.tok_scale = nullptr;
   ua.w = w; ua.fmt = fp8_format; ua.scale = scale; ua.scale_dtype = scale_dtype; ua.scale_mode = scale_mode;
   ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
   const bool umma_ok = umma_w8_supported(ua);
-  const bool want_umma = force == 2 || (force == 0 && M > 16);
-  if (umma_ok && want_umma) return umma_w8_linear(ua, st);
+  // bf16 activations + scratch: convert them once to per-token-scaled fp16 so the weight decode is one cvt per pair
+  const bool prep = act_dtype == B2Q_BF16 && workspace && aligned16(workspace) &&
+                    workspace_bytes >= b2q_linear_fp8_workspace_bytes(M, K) && (K % 8) == 0 && force != 3;
+  const bool want_umma = force == 2 || force == 3 || (force == 0 && (M > 4 || prep || act_dtype == B2Q_F16));
+  if (umma_ok && want_umma) {
+    if (prep) {
+      float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * (size_t)K * 2, 256));
+      int rc = act_to_scaled_f16(x, ldx, workspace, inv, M, (int)K, st);
+      if (rc) return rc;
+      ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.out_bf16 = true; ua.tok_scale = inv;
+    }
+    return umma_w8_linear(ua, st);
+  }
 
   SmallMParams p{};
   p.x = x; p.ldx = ldx;

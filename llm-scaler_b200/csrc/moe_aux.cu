@@ -382,3 +382,67 @@ int act_quant_1x128(const void* x, int dtype, int64_t ldx, void* xq, float* xs, 
 }
 
 }  // namespace b2q
+
+namespace b2q {
+
+// ---------------------------------------------------------------------------
+// Activation pre-pass for fp8-weight GEMMs with bf16 activations: rewrites every token row as
+// fp16 times a per-token power of two, x16[m, k] = fp16(x[m, k] * 2^e_m) with 2^e_m chosen so
+// that the row maximum lands in [2^14, 2^15).  A bf16 value has 8 significant bits, fp16 holds 11
+// and reaches down to 2^-24, so every element within 2^-31 of its row maximum converts exactly;
+// smaller ones keep an absolute error below rowmax * 2^-40.  inv_scale[m] = 2^-e_m (exact).
+// The point: e4m3 / e5m2 weights convert to fp16 with one instruction per pair, to bf16 with four.
+__global__ void act_to_scaled_f16_kernel(const __nv_bfloat16* __restrict__ x, int64_t ldx, __half* __restrict__ x16,
+                                         float* __restrict__ inv_scale, int K) {
+  __shared__ float red[32];
+  __shared__ float sc_sh;
+  const int64_t m = blockIdx.x;
+  const __nv_bfloat16* row = x + m * ldx;
+  float amax = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(e[j])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, red[i]);
+    float sc = 1.f;
+    if (a > 0.f && a < INFINITY) {
+      const int ex = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127;      // floor(log2 a) for normal a
+      int sh = 14 - ex;
+      sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+      sc = __uint_as_float((uint32_t)(sh + 127) << 23);
+    }
+    sc_sh = sc;
+    inv_scale[m] = 1.0f / sc;
+  }
+  __syncthreads();
+  const float sc = sc_sh;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+    uint4 o;
+    __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oh[j] = __float2half_rn(__bfloat162float(e[j]) * sc);
+    *reinterpret_cast<uint4*>(x16 + m * (int64_t)K + k) = o;
+  }
+}
+
+int act_to_scaled_f16(const void* x, int64_t ldx, void* x16, float* inv_scale, int64_t M, int K, cudaStream_t st) {
+  if (M == 0) return B2Q_OK;
+  int threads = (K / 8 + 31) / 32 * 32;
+  threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
+  act_to_scaled_f16_kernel<<<(unsigned)M, threads, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), ldx,
+                                                            reinterpret_cast<__half*>(x16), inv_scale, K);
+  note_launch("act_to_scaled_f16");
+  return launch_status();
+}
+
+}  // namespace b2q

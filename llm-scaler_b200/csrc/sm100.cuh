@@ -40,11 +40,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Bounded wait.  `abort_flag` is a shared-memory word every role polls, so one role's
-// timeout releases all the others; `status` is a global word the host can read.
+// timeout releases all the others; `status` is a global word the host can read.  The clock
+// and the abort flag are looked at once every 128 polls so the spin itself stays two
+// instructions long.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
     if (clock64() - t0 > WAIT_LIMIT_TICKS) {
       *abort_flag = 1;
@@ -52,7 +57,19 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       return false;
     }
   }
-  return true;
+}
+
+// Whole-warp wait: lane 0 spins, the other lanes park at the shuffle, then every lane observes
+// the completed phase itself (one try_wait that succeeds at once) so each has its own acquire.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, status, code) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (ok) {
+    int guard = 0;
+    while (!mbar_try_wait(bar, parity) && ++guard < 1024) {}
+  }
+  return ok != 0;
 }
 
 // ---- TMA: 2-D tiled load global -> shared, completion on an mbarrier -------------------
@@ -124,6 +141,31 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Registers -> tensor memory, same shape as tmem_ld32: lane i writes 32 consecutive 32-bit columns of
+// row (lane base + i).  Used to place a dequantised A operand (two 16-bit values per column, lower k
+// in the low half) where tcgen05.mma can read it without a trip through shared memory.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// D[tmem] (+)= A[tmem] * B[smem desc], 16-bit inputs; A is 128 rows x 16 k = 128 lanes x 8 columns.
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 
 // ---- descriptors ----------------------------------------------------------------------------
 // K-major operand tile stored as rows of 128 bytes with the 128-byte swizzle (16-byte chunk c of

@@ -368,8 +368,9 @@ inline int smallm_dispatch(const SmallMParams& p, int m_max, int n_tiles_cap, cu
   // grouped mode: m_max is the token-tile height the tile list was built for (8/16/32/64)
   int nt = m_max <= 8 ? 1 : (m_max <= 16 ? 2 : (m_max <= 32 ? 4 : 8));
   const int64_t strips16 = ((int64_t)p.N + 15) / 16 * (p.tiles ? n_tiles_cap : 1);
-  int rt = strips16 >= 4 * 592 ? 4 : (strips16 >= 2 * 444 ? 2 : 1);
-  if (nt == 8 && rt == 4) rt = 2;
+  // Conversion ALU work, not bytes in flight, limits this kernel, so resident warps matter more
+  // than strip height: 16-row strips give 3 CTAs (12 warps) per SM, 32-row strips 2 CTAs.
+  int rt = (nt >= 4 && strips16 >= 2 * 444) ? 2 : 1;
   if (SMODE == SM_BLOCK && (p.N % 16) != 0) rt = 1;
 #define B2Q_SM_CASE(R, T_) if (rt == R && nt == T_) return smallm_launch_one<WF, SMODE, BF16, R, T_>(p, m_max, n_tiles_cap, st);
   B2Q_SM_CASE(1, 1) B2Q_SM_CASE(1, 2) B2Q_SM_CASE(1, 4) B2Q_SM_CASE(1, 8)

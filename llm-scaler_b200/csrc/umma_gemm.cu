@@ -2,12 +2,12 @@
 //
 // The 128 weight rows of a CTA's strip are the MMA's M dimension and the tokens its N
 // dimension ("swap-AB"), so one kernel serves decode (16..64 tokens) and prefill (256-token
-// tiles).  Warp roles, one CTA of 7 warps per output tile:
+// tiles).  Warp roles, one CTA of 11 warps per output tile:
 //   warp 0     TMA producer of raw quantised weight tiles (runs up to RS stages ahead: this
 //              is the HBM stream)
 //   warp 1     tensor-memory owner and the single thread that issues tcgen05.mma
 //   warp 2     TMA producer of activation tiles [TOK x 64] (128-byte swizzle)
-//   warps 3-6  transform: raw int4 / fp8 -> 16-bit values written straight into the
+//   warps 3-10 transform: raw int4 / fp8 -> 16-bit values written straight into the
 //              128-byte-swizzled K-major operand layout the MMA reads; afterwards the same
 //              warps drain the fp32 accumulator from tensor memory, apply per-row scales and
 //              store out[tok, n].
@@ -27,6 +27,20 @@ namespace b2q {
 using namespace sm100;
 
 __device__ int g_umma_status = 0;
+#ifdef B2Q_UMMA_PROF
+// Wait-time accounting for one CTA, accumulated in registers and flushed once per role so the
+// measurement does not sit on the critical path.
+__device__ long long g_umma_prof[32];
+#define PROF_DECL long long _pa[4] = {0, 0, 0, 0}
+#define PROF_T0 const long long _pt = clock64()
+#define PROF_ADD(i) _pa[(i) & 3] += clock64() - _pt
+#define PROF_FLUSH(base) if (blockIdx.y == 7 && blockIdx.x == 0) { for (int _i = 0; _i < 4; ++_i) g_umma_prof[(base) + _i] += _pa[_i]; }
+#else
+#define PROF_DECL
+#define PROF_T0
+#define PROF_ADD(i)
+#define PROF_FLUSH(base)
+#endif
 
 enum { WK_W4N = 0, WK_W4K = 1, WK_W8 = 2 };
 enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWEMPTY = 105, ST_ACCUM = 106 };
@@ -39,6 +53,8 @@ struct UmmaWoParams {
   int marlin; uint32_t xor_mask; int e5m2;
   const int32_t* tiles; const int32_t* expert_offsets; const int32_t* out_map;
   int w_rows_per_expert;     // tensor-map rows per expert: N (N-major) or K/8 (K-major)
+  const float* tok_scale;    // optional per-token output multiplier (undoes the activation pre-scale)
+  int out_bf16;              // output element type (may differ from the MMA input type)
   int* status;
 };
 
@@ -111,36 +127,59 @@ __device__ __forceinline__ void w8_word(uint32_t w, bool e5m2, float sf, uint32_
 }
 
 template <int TOK> struct UmmaCfg {
-  static constexpr int S = 4;                        // operand stages (64 k each)
-  static constexpr int RS = TOK >= 256 ? 2 : 4;      // raw weight stages (16 KB each)
-  static constexpr int A_BYTES = 128 * 128;          // 128 rows x 64 16-bit values
+  // The dequantised weight operand lives in tensor memory, not shared memory: a 64-k chunk of 128
+  // rows is 128 lanes x 32 columns, written by the transform warps with tcgen05.st and read by the
+  // MMA as its A operand.  Shared memory then carries only the raw quantised stream (written by TMA,
+  // read once by the transform) and the activation tiles, i.e. about twice the HBM traffic instead
+  // of six (fp8) to ten (int4) times, which is what capped the shared-memory variant near 3 TB/s.
+  static constexpr int NG = 2;                                       // transform groups of 4 warps
+  static constexpr int CTAS = TOK <= 64 ? 2 : 1;                     // decode tiles: two CTAs (two MMA issuers) per SM
+  static constexpr int XS = TOK <= 32 ? 6 : 4;                       // activation stages (64 k each)
+  // Issuing tcgen05.mma is a serial job of one thread and costs it several hundred cycles per 64-k
+  // chunk regardless of the tile width; decode tiles therefore use two issuer warps on alternate
+  // chunks, each with its own accumulator (summed in the epilogue).
+  static constexpr int NMMA = TOK <= 64 ? 2 : 1;
+  static constexpr int CW = 2 + NMMA;                                // control warps: raw TMA, X TMA, MMA issuer(s)
+  static constexpr int THREADS = CW * 32 + NG * 128;                 // + transform / epilogue warps
   static constexpr int X_BYTES = TOK * 128;
   static constexpr int RAW_BYTES = 16384;
-  static constexpr int SMEM = S * (A_BYTES + X_BYTES) + RS * RAW_BYTES + 1024 /*align*/ + 256 /*barriers*/;
-  static constexpr int TMEM_COLS = TOK < 32 ? 32 : TOK;
+  static constexpr int SMEM_BUDGET = CTAS == 2 ? 114688 : 230400;    // per CTA, leaving room for the driver's reserve
+  static constexpr int RS_FIT = (SMEM_BUDGET - 1536 - XS * X_BYTES) / RAW_BYTES;
+  static constexpr int RS = RS_FIT > 8 ? 8 : RS_FIT;                 // raw weight stages (16 KB each)
+  static constexpr int SMEM = XS * X_BYTES + RS * RAW_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int ACC_COLS = TOK < 32 ? 32 : TOK;               // fp32 accumulator columns
+  static constexpr int A_COL0 = NMMA * ACC_COLS;                     // first operand column
+  static constexpr int TMEM_COLS = CTAS == 2 ? 256 : 512;            // the SM's 512 columns split over resident CTAs
+  // Operand stages (32 columns each) fill the rest of the allocation: a stage is only reusable once
+  // the MMAs that read it have completed and signalled, a round trip of a couple of microseconds, so
+  // the ring has to be deep for the transform warps to stay busy.
+  static constexpr int S = (TMEM_COLS - A_COL0) / 32 > 12 ? 12 : (TMEM_COLS - A_COL0) / 32;
 };
 
 template <int WK, bool BF16, int TOK, bool FAST>
-__global__ void __launch_bounds__(224, 1)
+__global__ void __launch_bounds__(UmmaCfg<TOK>::THREADS, UmmaCfg<TOK>::CTAS)
 umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const UmmaWoParams p) {
   using Cfg = UmmaCfg<TOK>;
-  constexpr int S = Cfg::S, RS = Cfg::RS;
+  constexpr int S = Cfg::S, RS = Cfg::RS, NG = Cfg::NG, XS = Cfg::XS;
   constexpr int CPR = (WK == WK_W8) ? 2 : 4;          // 64-k chunks per raw stage
+  constexpr int GPR = CPR < NG ? CPR : NG;            // transform groups that touch one raw stage
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t a_smem = base;
-  const uint32_t x_smem = a_smem + S * Cfg::A_BYTES;
-  const uint32_t raw_smem = x_smem + S * Cfg::X_BYTES;
+  const uint32_t x_smem = base;
+  const uint32_t raw_smem = x_smem + XS * Cfg::X_BYTES;
   const uint32_t bar = raw_smem + RS * Cfg::RAW_BYTES;
   // barrier map (8 bytes each)
-  const uint32_t x_full = bar, a_full = bar + 8 * S, ab_empty = bar + 16 * S;
-  const uint32_t raw_full = bar + 24 * S, raw_empty = raw_full + 8 * RS, accum_full = raw_empty + 8 * RS;
+  const uint32_t x_full = bar, x_empty = x_full + 8 * XS, a_full = x_empty + 8 * XS, ab_empty = a_full + 8 * S;
+  const uint32_t raw_full = ab_empty + 8 * S, raw_empty = raw_full + 8 * RS, accum_full = raw_empty + 8 * RS;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (accum_full + 8 - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + (accum_full + 16 - base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef B2Q_UMMA_PROF
+  const long long _kt0 = clock64();
+#endif
 
   // ---- which tile ----
   int tok0 = blockIdx.x * TOK, xrow0 = 0, M = p.M, expert = 0;
@@ -156,9 +195,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   const int64_t sbase = (int64_t)expert * p.s_expert_elems;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(a_full + 8 * i, 128); mbar_init(ab_empty + 8 * i, 1); }
-    for (int i = 0; i < RS; ++i) { mbar_init(raw_full + 8 * i, 1); mbar_init(raw_empty + 8 * i, 128); }
-    mbar_init(accum_full, 1);
+    for (int i = 0; i < S; ++i) { mbar_init(a_full + 8 * i, 128); mbar_init(ab_empty + 8 * i, 1); }
+    for (int i = 0; i < XS; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
+    for (int i = 0; i < RS; ++i) { mbar_init(raw_full + 8 * i, 1); mbar_init(raw_empty + 8 * i, GPR * 128); }
+    mbar_init(accum_full, Cfg::NMMA);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -171,129 +211,178 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   if (warp == 0) {
     // ---------------- raw weight producer ----------------
     if (lane == 0) {
+      PROF_DECL;
       tma_prefetch_desc(&tm_w);
       const int nraw = (nk + CPR - 1) / CPR;
       for (int r = 0; r < nraw; ++r) {
         const int rs = r % RS;
-        if (r >= RS && !mbar_wait(raw_empty + 8 * rs, ((r / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) break;
+        { PROF_T0; if (r >= RS && !mbar_wait(raw_empty + 8 * rs, ((r / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) break; PROF_ADD(0); }
         mbar_expect_tx(raw_full + 8 * rs, Cfg::RAW_BYTES);
         if constexpr (WK == WK_W4K)
           tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, n0, expert * p.w_rows_per_expert + r * 32, raw_full + 8 * rs);
         else
           tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, r * 128, expert * p.w_rows_per_expert + n0, raw_full + 8 * rs);
       }
+      PROF_FLUSH(12);
     }
   } else if (warp == 2) {
     // ---------------- activation producer ----------------
     if (lane == 0) {
+      PROF_DECL;
       tma_prefetch_desc(&tm_x);
       for (int c = 0; c < nk; ++c) {
-        const int s = c % S;
-        if (c >= S && !mbar_wait(ab_empty + 8 * s, ((c / S) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break;
+        const int s = c % XS;
+        { PROF_T0; if (c >= XS && !mbar_wait(x_empty + 8 * s, ((c / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break; PROF_ADD(0); }
         mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
         tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, c * 64, xrow0 + tok0, x_full + 8 * s);
       }
+      PROF_FLUSH(16);
     }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == 1 || (Cfg::NMMA == 2 && warp == 3)) {
+    // ---------------- MMA issuer(s) ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BF16 ? 1u : 0u, BF16 ? 1u : 0u, 128, TOK);
+      const int me = warp == 1 ? 0 : 1;
+      const uint32_t dacc = tmem + me * Cfg::ACC_COLS;
+      const uint64_t db0 = smem_desc_sw128(x_smem);
       bool ok = true;
-      for (int c = 0; c < nk && ok; ++c) {
-        const int s = c % S;
-        const uint32_t par = (c / S) & 1;
-        ok = mbar_wait(x_full + 8 * s, par, abort_flag, p.status, ST_XFULL) &&
-             mbar_wait(a_full + 8 * s, par, abort_flag, p.status, ST_AFULL);
+      PROF_DECL;
+#ifdef B2Q_UMMA_PROF
+      const long long _loop0 = clock64();
+#endif
+#pragma unroll 1
+      for (int c = me; c < nk; c += Cfg::NMMA) {
+        const int s = c % S, xs = c % XS;
+        { PROF_T0; ok = mbar_wait(x_full + 8 * xs, (c / XS) & 1, abort_flag, p.status, ST_XFULL); PROF_ADD(0); }
+        if (ok) { PROF_T0; ok = mbar_wait(a_full + 8 * s, (c / S) & 1, abort_flag, p.status, ST_AFULL); PROF_ADD(1); }
         if (!ok) break;
+        PROF_T0;
         tc_fence_after();
-        const uint64_t da = smem_desc_sw128(a_smem + s * Cfg::A_BYTES);
-        const uint64_t db = smem_desc_sw128(x_smem + s * Cfg::X_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          mma_f16(tmem, da + (uint64_t)(kk * 2), db + (uint64_t)(kk * 2), idesc, (c > 0 || kk > 0) ? 1u : 0u);
+        const uint32_t ta = tmem + Cfg::A_COL0 + 32 * s;
+        const uint64_t db = db0 + (uint64_t)(xs * (Cfg::X_BYTES >> 4));
+        mma_f16_ts(dacc, ta, db, idesc, c >= Cfg::NMMA ? 1u : 0u);
+        mma_f16_ts(dacc, ta + 8, db + 2, idesc, 1u);
+        mma_f16_ts(dacc, ta + 16, db + 4, idesc, 1u);
+        mma_f16_ts(dacc, ta + 24, db + 6, idesc, 1u);
         tc_commit(ab_empty + 8 * s);
+        tc_commit(x_empty + 8 * xs);
+        PROF_ADD(2);
       }
+#ifdef B2Q_UMMA_PROF
+      _pa[3] = clock64() - _loop0;
+      if (me == 0) { PROF_FLUSH(0); }
+#endif
       if (ok) tc_commit(accum_full);
     }
   } else {
-    // ---------------- transform, then epilogue (warps 3..6) ----------------
-    const int t = threadIdx.x - 96;          // 0..127: weight row (N-major / fp8) or column (K-major) in the strip
-    const int nraw = (nk + CPR - 1) / CPR;
+    // ---------------- transform, then epilogue (warps 3..10) ----------------
+    // Two groups of four warps; group g converts the 64-k chunks with (c & 1) == g, one weight row
+    // (N-major / fp8) or column (K-major) per thread, so two chunks are always in flight.
+    const int t = (warp & 3) * 32 + lane;        // row of the strip == tensor-memory lane this thread may write
+    const int grp = (threadIdx.x - Cfg::CW * 32) >> 7;
     int nrow = n0 + t; if (nrow >= p.N) nrow = p.N - 1;
+    const int sw = t & 7;
+    const bool blockscale = (WK == WK_W8) && (p.scale_mode == B2Q_SCALE_BLOCK128);
+    const int kblocks = (p.K + 127) >> 7;
     bool ok = true;
-    for (int r = 0; r < nraw && ok; ++r) {
-      const int rs = r % RS;
-      ok = mbar_wait(raw_full + 8 * rs, (r / RS) & 1, abort_flag, p.status, ST_RAWFULL);
-      if (!ok) break;
-      const uint32_t rawb = raw_smem + rs * Cfg::RAW_BYTES;
+    PROF_DECL;
+#ifdef B2Q_UMMA_PROF
+    const long long _loop0 = clock64();
+#endif
 #pragma unroll 1
-      for (int j = 0; j < CPR; ++j) {
-        const int c = r * CPR + j;
-        if (c >= nk) break;
+    for (int c = grp; c < nk; c += NG) {
+      const int r = c / CPR, j = c % CPR;
+      const int rs = r % RS;
+      { PROF_T0; ok = mbar_wait(raw_full + 8 * rs, (r / RS) & 1, abort_flag, p.status, ST_RAWFULL); PROF_ADD(0); }
+      if (!ok) break;
+      const uint32_t rawrow = raw_smem + rs * Cfg::RAW_BYTES + t * 128;     // N-major / fp8: this thread's row
+      const uint32_t rawcol = raw_smem + rs * Cfg::RAW_BYTES + t * 4;       // K-major: this thread's column
+      {
         const int s = c % S;
-        if (c >= S) { ok = mbar_wait(ab_empty + 8 * s, ((c / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); if (!ok) break; }
-        const uint32_t ab = a_smem + s * Cfg::A_BYTES + t * 128;
-        const int sw = t & 7;
+        if (c >= S) { PROF_T0; ok = mbar_wait(ab_empty + 8 * s, ((c / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); PROF_ADD(1); if (!ok) break; }
+        tc_fence_after();
+        const uint32_t ta = tmem + ((uint32_t)((warp & 3) * 32) << 16) + Cfg::A_COL0 + 32 * s;
+        uint32_t av[32];                         // this row's 64 values of the chunk, two per register, k ascending
+        PROF_T0;
         if constexpr (WK == WK_W4N || WK == WK_W4K) {
-          const int g = (c * 64) >> 7;
           uint32_t s2 = 0; float sf = 0.f;
-          const int64_t si = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)g * p.s_stride_g;
+          const int64_t si = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)(c >> 1) * p.s_stride_g;
           if constexpr (FAST) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si]; s2 = sv | (sv << 16); }
           else sf = load_scalar(p.scale, si, p.scale_dtype);
           if constexpr (WK == WK_W4N) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const uint4 rv = lds128(rawb + t * 128 + (((2 * j + h) ^ sw) << 4));
-              const uint32_t ww[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                uint32_t o[4];
-                w4_word<BF16, FAST>(ww[i] ^ p.xor_mask, s2, sf, false, o);
-                sts128(ab + (((4 * h + i) ^ sw) << 4), o[0], o[1], o[2], o[3]);
-              }
-            }
-          } else {
+            const uint4 r0 = lds128(rawrow + (((2 * j) ^ sw) << 4));
+            const uint4 r1 = lds128(rawrow + (((2 * j + 1) ^ sw) << 4));
+            const uint32_t ww[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const uint32_t w = lds32(rawb + ((8 * j + i) * 128 + t) * 4);
               uint32_t o[4];
-              w4_word<BF16, FAST>(w, s2, sf, p.marlin != 0, o);
-              sts128(ab + ((i ^ sw) << 4), o[0], o[1], o[2], o[3]);
+              w4_word<BF16, FAST>(ww[i] ^ p.xor_mask, s2, sf, false, o);
+              av[4 * i] = o[0]; av[4 * i + 1] = o[1]; av[4 * i + 2] = o[2]; av[4 * i + 3] = o[3];
+            }
+          } else {
+            const bool marlin = p.marlin != 0;
+            uint32_t ww[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ww[i] = lds32(rawcol + (8 * j + i) * 512);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              uint32_t o[4];
+              w4_word<BF16, FAST>(ww[i], s2, sf, marlin, o);
+              av[4 * i] = o[0]; av[4 * i + 1] = o[1]; av[4 * i + 2] = o[2]; av[4 * i + 3] = o[3];
             }
           }
         } else {
-          const bool blockscale = (p.scale_mode == B2Q_SCALE_BLOCK128);
-          float sf = 1.f;
-          if (blockscale)
-            sf = reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * ((p.K + 127) >> 7) + ((c * 64) >> 7)];
+          uint4 rv[4];
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            const uint4 rv = lds128(rawb + t * 128 + (((4 * j + c4) ^ sw) << 4));
-            uint32_t o[8];
-            if (blockscale) {
-              w8_word<BF16, true>(rv.x, p.e5m2, sf, o[0], o[1]); w8_word<BF16, true>(rv.y, p.e5m2, sf, o[2], o[3]);
-              w8_word<BF16, true>(rv.z, p.e5m2, sf, o[4], o[5]); w8_word<BF16, true>(rv.w, p.e5m2, sf, o[6], o[7]);
-            } else {
-              w8_word<BF16, false>(rv.x, p.e5m2, sf, o[0], o[1]); w8_word<BF16, false>(rv.y, p.e5m2, sf, o[2], o[3]);
-              w8_word<BF16, false>(rv.z, p.e5m2, sf, o[4], o[5]); w8_word<BF16, false>(rv.w, p.e5m2, sf, o[6], o[7]);
+          for (int c4 = 0; c4 < 4; ++c4) rv[c4] = lds128(rawrow + (((4 * j + c4) ^ sw) << 4));
+          uint32_t (&o)[32] = av;
+          if (blockscale) {
+            const float sf = reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * kblocks + (c >> 1)];
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              w8_word<BF16, true>(rv[c4].x, p.e5m2, sf, o[8 * c4 + 0], o[8 * c4 + 1]);
+              w8_word<BF16, true>(rv[c4].y, p.e5m2, sf, o[8 * c4 + 2], o[8 * c4 + 3]);
+              w8_word<BF16, true>(rv[c4].z, p.e5m2, sf, o[8 * c4 + 4], o[8 * c4 + 5]);
+              w8_word<BF16, true>(rv[c4].w, p.e5m2, sf, o[8 * c4 + 6], o[8 * c4 + 7]);
             }
-            sts128(ab + (((2 * c4) ^ sw) << 4), o[0], o[1], o[2], o[3]);
-            sts128(ab + (((2 * c4 + 1) ^ sw) << 4), o[4], o[5], o[6], o[7]);
+          } else if (p.e5m2) {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              o[8 * c4 + 0] = fp8x2_to_act<BF16, true>(rv[c4].x); o[8 * c4 + 1] = fp8x2_to_act<BF16, true>(rv[c4].x >> 16);
+              o[8 * c4 + 2] = fp8x2_to_act<BF16, true>(rv[c4].y); o[8 * c4 + 3] = fp8x2_to_act<BF16, true>(rv[c4].y >> 16);
+              o[8 * c4 + 4] = fp8x2_to_act<BF16, true>(rv[c4].z); o[8 * c4 + 5] = fp8x2_to_act<BF16, true>(rv[c4].z >> 16);
+              o[8 * c4 + 6] = fp8x2_to_act<BF16, true>(rv[c4].w); o[8 * c4 + 7] = fp8x2_to_act<BF16, true>(rv[c4].w >> 16);
+            }
+          } else {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              o[8 * c4 + 0] = fp8x2_to_act<BF16, false>(rv[c4].x); o[8 * c4 + 1] = fp8x2_to_act<BF16, false>(rv[c4].x >> 16);
+              o[8 * c4 + 2] = fp8x2_to_act<BF16, false>(rv[c4].y); o[8 * c4 + 3] = fp8x2_to_act<BF16, false>(rv[c4].y >> 16);
+              o[8 * c4 + 4] = fp8x2_to_act<BF16, false>(rv[c4].z); o[8 * c4 + 5] = fp8x2_to_act<BF16, false>(rv[c4].z >> 16);
+              o[8 * c4 + 6] = fp8x2_to_act<BF16, false>(rv[c4].w); o[8 * c4 + 7] = fp8x2_to_act<BF16, false>(rv[c4].w >> 16);
+            }
           }
         }
-        fence_proxy_async();
+        tmem_st32(ta, av);
+        tmem_st_wait();
+        tc_fence_before();
         mbar_arrive(a_full + 8 * s);
+        PROF_ADD(2);
       }
-      mbar_arrive(raw_empty + 8 * rs);
+      // release the raw stage once this group's last chunk in it is converted
+      if (c + NG >= nk || (c + NG) / CPR != r) mbar_arrive(raw_empty + 8 * rs);
     }
 
+#ifdef B2Q_UMMA_PROF
+    _pa[3] = clock64() - _loop0;
+    if (threadIdx.x == Cfg::CW * 32) { PROF_FLUSH(4); }
+#endif
     // ---------------- epilogue ----------------
     if (ok) ok = mbar_wait(accum_full, 0, abort_flag, p.status, ST_ACCUM);
     if (ok) {
       tc_fence_after();
-      using A = Act<BF16>;
-      using T = typename A::T;
       const int quad = warp & 3;                   // tensor-memory lane quadrant this warp may read
+      const int cgrp = (warp - Cfg::CW) >> 2;            // the NG warps of a quadrant take column blocks in turn
       const int n = n0 + quad * 32 + lane;
       float post = 1.f;
       if constexpr (WK == WK_W8) {
@@ -303,10 +392,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           post *= load_scalar(p.scale, sbase + (p.scale_mode == B2Q_SCALE_CHANNEL ? nn : 0), p.scale_dtype);
         }
       }
-      T* outp = reinterpret_cast<T*>(p.out);
+      uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
       constexpr int CB = TOK >= 32 ? 32 : 16;
 #pragma unroll 1
-      for (int cb = 0; cb < TOK; cb += CB) {
+      for (int cb = cgrp * CB; cb < TOK; cb += NG * CB) {
         if (tok0 + cb >= M) break;
         uint32_t r[32];
         if constexpr (CB == 32) tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + cb, r);
@@ -314,6 +403,16 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 #pragma unroll
                for (int i = 0; i < 16; ++i) r[i] = r16[i]; }
         tmem_ld_wait();
+        if (Cfg::NMMA == 2 && nk >= 2) {
+          uint32_t q[32];
+          if constexpr (CB == 32) tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + Cfg::ACC_COLS + cb, q);
+          else { uint32_t q16[16]; tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + Cfg::ACC_COLS + cb, q16);
+#pragma unroll
+                 for (int i = 0; i < 16; ++i) q[i] = q16[i]; }
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
+        }
         if (n < p.N) {
 #pragma unroll
           for (int i = 0; i < CB; ++i) {
@@ -321,7 +420,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
             if (tok < M) {
               int64_t orow = xrow0 + tok;
               if (p.out_map) orow = p.out_map[orow];
-              outp[orow * p.ldo + n] = A::from_f(__uint_as_float(r[i]) * post);
+              float v = __uint_as_float(r[i]) * post;
+              if (p.tok_scale) v *= p.tok_scale[xrow0 + tok];
+              outp[orow * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                                  : __half_as_ushort(__float2half_rn(v));
             }
           }
         }
@@ -332,6 +434,9 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, Cfg::TMEM_COLS); }
+#ifdef B2Q_UMMA_PROF
+  if (threadIdx.x == 0 && blockIdx.y == 7 && blockIdx.x == 0) { g_umma_prof[8] += clock64() - _kt0; g_umma_prof[9] += 1; }
+#endif
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -385,6 +490,15 @@ int umma_read_status(int* out) {
   return cuda_status(cudaMemcpy(out, p, sizeof(int), cudaMemcpyDeviceToHost));
 }
 
+#ifdef B2Q_UMMA_PROF
+extern "C" __attribute__((visibility("default"))) int b2q_debug_prof(long long* out, int reset) {
+  cudaDeviceSynchronize();
+  if (out && cudaMemcpyFromSymbol(out, g_umma_prof, sizeof(long long) * 32) != cudaSuccess) return -1;
+  if (reset) { long long z[32] = {0}; cudaMemcpyToSymbol(g_umma_prof, z, sizeof(z)); }
+  return 0;
+}
+#endif
+
 static int pick_tok(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256))); }
 
 template <int WK, bool BF16, int TOK, bool FAST>
@@ -399,7 +513,7 @@ static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWo
     if (dev < 16) configured[dev] = true;
   }
   dim3 grid(token_tiles, (p.N + 127) / 128, 1);
-  kern<<<grid, 224, Cfg::SMEM, st>>>(tw, tx, p);
+  kern<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(tw, tx, p);
   note_launch("umma_wo");
   return launch_status();
 }
@@ -463,6 +577,7 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.marlin = a.layout == B2Q_W4_KMAJOR_MARLIN; p.xor_mask = a.layout == B2Q_W4_NMAJOR_S4 ? 0x88888888u : 0u;
   p.tiles = grouped ? a.tiles : nullptr; p.expert_offsets = a.expert_offsets; p.out_map = a.out_map;
   p.w_rows_per_expert = kmajor ? a.K / 8 : a.N;
+  p.tok_scale = nullptr; p.out_bf16 = a.bf16 ? 1 : 0;
   p.status = status_ptr();
   const bool fast = (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
@@ -497,6 +612,7 @@ int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st) {
   p.e5m2 = a.fmt == B2Q_E5M2;
   p.tiles = grouped ? a.tiles : nullptr; p.expert_offsets = a.expert_offsets; p.out_map = a.out_map;
   p.w_rows_per_expert = a.N;
+  p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0;
   p.status = status_ptr();
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
   return launch_wk<WK_W8>(a.bf16, true, tok, tw, tx, p, tiles, st);

@@ -25,7 +25,8 @@ struct UmmaW4Args : UmmaGroupArgs {
 };
 
 struct UmmaW8Args : UmmaGroupArgs {
-  const void* x; int64_t ldx; bool bf16;
+  const void* x; int64_t ldx; bool bf16;      // bf16: element type of x (the MMA input type)
+  bool out_bf16; const float* tok_scale;      // output type; optional per-token multiplier
   const void* w; int fmt;
   const void* scale; int scale_dtype; int scale_mode;
   void* out; int64_t ldo;

@@ -114,10 +114,15 @@ def linear_fp8(input, weight, weight_scale, output, scale_mode, N=None, K=None):
         _chk(weight_scale.dtype == torch.float32 and weight_scale.is_contiguous(), "block scale must be fp32")
         _chk(tuple(weight_scale.shape) == ((wn + 127) // 128, (wk + 127) // 128), "block scale shape mismatch")
     with L.on_device(input):
+        ws, wsb = None, 0
+        if input.dtype == torch.bfloat16:
+            # scratch for the activation pre-pass (torch's caching allocator: no cudaMalloc in steady state)
+            wsb = L.lib.b2q_linear_fp8_workspace_bytes(M, wk)
+            ws = torch.empty(wsb, dtype=torch.uint8, device=input.device)
         L.check(L.lib.b2q_linear_fp8(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else wk,
                                       weight.data_ptr(), L.fp8_fmt(weight), weight_scale.data_ptr(),
                                       L.dt(weight_scale), scale_mode, output.data_ptr(),
-                                      output.stride(0) if M > 1 else wn, M, wn, wk, L.stream(input)))
+                                      output.stride(0) if M > 1 else wn, M, wn, wk, L.ptr(ws), wsb, L.stream(input)))
     return output
 
 

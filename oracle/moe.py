@@ -7,7 +7,11 @@ def topk_softmax(logits: torch.Tensor, top_k: int, renorm: bool = True, out_dtyp
     """fp32 softmax -> torch.topk -> renormalise -> cast (tests/test_moe_int4_kernel.py:213-216,
     python/custom_esimd_kernels_vllm/ops.py:1427-1437).  Returns (weights [T,k], ids int32 [T,k])."""
     probs = F.softmax(logits.float(), dim=-1)
-    w, ids = torch.topk(probs, top_k, dim=-1)
+    # torch.topk with the tie rule of the reference kernel made explicit: among bit-equal
+    # probabilities the lowest expert index is taken first (csrc/xpu/esimd_kernels/moe_ops.h:77-104).
+    # A stable descending sort does exactly that; without ties it equals torch.topk.
+    sp, si = torch.sort(probs, dim=-1, descending=True, stable=True)
+    w, ids = sp[..., :top_k], si[..., :top_k]
     if renorm:
         w = w / w.sum(dim=-1, keepdim=True)
     return w.to(out_dtype or logits.dtype), ids.to(torch.int32)

@@ -59,8 +59,8 @@ def test_null_and_shape_errors_need_no_device(lib_built):
     # misaligned activation pointer
     assert lib.b2q_linear_int4(p + 2, 0, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None) == -4
     # fp8: K not a multiple of 16, block mode needs fp32 scales
-    assert lib.b2q_linear_fp8(p, 0, 40, p, 0, p, 2, 0, p, 16, 1, 16, 40, None) == -2
-    assert lib.b2q_linear_fp8(p, 0, 128, p, 0, p, 0, 2, p, 16, 1, 16, 128, None) == -3
+    assert lib.b2q_linear_fp8(p, 0, 40, p, 0, p, 2, 0, p, 16, 1, 16, 40, None, 0, None) == -2
+    assert lib.b2q_linear_fp8(p, 0, 128, p, 0, p, 0, 2, p, 16, 1, 16, 128, None, 0, None) == -3
     # M == 0 is a successful no-op
     assert lib.b2q_linear_int4(p, 0, 128, p, 0, p, 0, 1, 1, p, 16, 0, 16, 128, 128, None) == 0
     # route: workspace too small

@@ -61,9 +61,10 @@ def test_int4_kmajor(e, marlin, M, N, K):
         e.esimd_gemm_int4_pgrp(x.to(DEV), wk.to(DEV), sk.to(DEV), out)       # classified K-major from the scale shape
     else:
         L = e._lib
+        xd, wd, sd = x.to(DEV), wk.to(DEV), sk.to(DEV)
         with L.on_device(out):
-            L.check(L.lib.b2q_linear_int4(x.to(DEV).data_ptr(), L.BF16, K, wk.to(DEV).data_ptr(), L.W4_KMAJOR_MARLIN,
-                                          sk.to(DEV).data_ptr(), L.BF16, 1, N, out.data_ptr(), N, M, N, K, 128, None))
+            L.check(L.lib.b2q_linear_int4(xd.data_ptr(), L.BF16, K, wd.data_ptr(), L.W4_KMAJOR_MARLIN,
+                                          sd.data_ptr(), L.BF16, 1, N, out.data_ptr(), N, M, N, K, 128, None))
         torch.cuda.synchronize()
     assert_close(out, ref, what=f"umma int4 kmajor marlin={marlin}")
 
