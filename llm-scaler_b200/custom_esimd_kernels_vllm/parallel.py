@@ -1,0 +1,161 @@
+"""Tensor-parallel and expert-parallel use of the quantized-linear path, one process per GPU over
+`torch.distributed` (NCCL on GPUs; the same code runs over gloo in the CPU tests with a stand-in
+compute backend).
+
+What the reference does around the ops (vLLM side, `vllm/patches/vllm_for_multi_arc.patch`):
+  * column-parallel QKV / gate_up: the N dimension is split, no communication;
+  * row-parallel o_proj / down: K is split in multiples of the 128-wide quantisation group, each rank
+    produces a full-width partial result and the ranks all-reduce it (`:10185`, `:10199`, `:8006-8010`);
+  * expert parallelism: experts are split contiguously over ranks (`:3356-3365`) and tokens are exchanged.
+The reference has no fused kernel under EP and emulates all-to-all with all-gather + reduce-scatter
+(`:1559-1563`); here tokens really travel by all-to-all with a counts exchange in front.
+
+Only sharding arithmetic and collectives live here; all compute goes through a small backend object so
+that the CUDA ops (default) and a CPU oracle (tests) can both drive the same schedule.
+"""
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+GROUP = 128
+
+
+# ----------------------------------------------------------------------------- sharding of INT4 N-major weights
+def shard_column(w: torch.Tensor, scale: torch.Tensor, rank: int, world: int, fused_halves: int = 1):
+    """Split output rows.  w [N, K/8] (or [N, K/2]) and scale [N, K/g] are sliced the same way.
+
+    fused_halves = 2 for gate_up: the gate rows and the up rows are each split so that a rank owns matching
+    slices ([gate_r ; up_r]); 1 for a plain split (QKV is split by heads by the caller choosing N)."""
+    N = w.shape[0]
+    assert N % (world * fused_halves) == 0, "N must divide evenly over ranks"
+    part = N // fused_halves
+    sl = part // world
+    rows = torch.cat([torch.arange(h * part + rank * sl, h * part + (rank + 1) * sl) for h in range(fused_halves)])
+    rows = rows.to(w.device)
+    return w.index_select(0, rows).contiguous(), scale.index_select(0, rows).contiguous()
+
+
+def shard_row(w: torch.Tensor, scale: torch.Tensor, rank: int, world: int, k_per_word: int = 8):
+    """Split the reduction dimension in multiples of the 128-wide group.  w [N, K/k_per_word], scale [N, K/128]."""
+    G = scale.shape[1]
+    assert G % world == 0, "K/128 must divide evenly over ranks"
+    g = G // world
+    wcols = g * GROUP // k_per_word
+    return (w[:, rank * wcols:(rank + 1) * wcols].contiguous(), scale[:, rank * g:(rank + 1) * g].contiguous())
+
+
+# ----------------------------------------------------------------------------- compute backends
+class CudaBackend:
+    """The product path: torch ops of this package (C ABI underneath)."""
+
+    def __init__(self):
+        from . import _impl, _lib
+        self.I, self.L = _impl, _lib
+
+    def linear_int4(self, x, w, s):
+        out = torch.empty(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+        return self.I.linear_int4(x, w, s, out)
+
+    def silu_mul(self, g):
+        return self.I.silu_mul(g)
+
+    def topk(self, logits, k, dtype):
+        return self.I.moe_topk(logits, k, True, weight_dtype=dtype)
+
+    def route(self, ids, E):
+        return self.I.moe_route(ids, E)
+
+    def gather_rows(self, src, idx, div):
+        return self.I.gather_rows(src, idx, div)
+
+    def expert_mlp(self, x, w13, s13, w2, s2, offsets, tokens, rows):
+        """rows of x (in arrival order) -> y in arrival order, through the experts given by the route."""
+        inter = self.I.moe_gemm_int4(x, w13, s13, offsets, rows, row_map=tokens, row_div=1, act=self.L.ACT_SILU_MUL)
+        return self.I.moe_gemm_int4(inter, w2, s2, offsets, rows, out_map=tokens, out_rows=x.shape[0])
+
+    def combine(self, y, weights, perm, T, k):
+        return self.I.moe_combine(y, weights, perm, T, k)
+
+
+# ----------------------------------------------------------------------------- tensor parallel
+@dataclass
+class TPLayer:
+    """One decoder layer's four INT4 linears, already sharded for this rank."""
+    qkv: tuple
+    o: tuple
+    gate_up: tuple
+    down: tuple
+
+
+def all_reduce(t: torch.Tensor, group=None) -> torch.Tensor:
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.SUM, group=group)
+    return t
+
+
+def tp_layer_forward(x: torch.Tensor, layer: TPLayer, backend, group=None) -> torch.Tensor:
+    """x [M, hidden] (replicated) -> [M, hidden] (replicated).
+
+    QKV (column) -> the rank's q slice stands in for the attention output -> o_proj (row, all-reduce)
+    -> gate_up (column) -> SiLU*mul -> down (row, all-reduce).  Attention itself is outside this path."""
+    qkv = backend.linear_int4(x, *layer.qkv)
+    k_local = layer.o[1].shape[1] * GROUP
+    attn = qkv[:, :k_local].contiguous()
+    h = all_reduce(backend.linear_int4(attn, *layer.o), group)
+    gu = backend.linear_int4(h, *layer.gate_up)
+    act = backend.silu_mul(gu)
+    return all_reduce(backend.linear_int4(act, *layer.down), group)
+
+
+# ----------------------------------------------------------------------------- expert parallel
+def ep_plan(ids: torch.Tensor, experts_per_rank: int, world: int, backend):
+    """Sort this rank's (token, slot) pairs by destination rank.
+
+    Returns send_counts [world] (host list), send_order int32 [n_pairs] (pair indices grouped by destination,
+    stable), pair_to_send int32 [n_pairs] (inverse), local_expert int32 [n_pairs] in send order."""
+    dest = torch.div(ids, experts_per_rank, rounding_mode="floor").to(torch.int32).contiguous()
+    offsets, order, p2s, rows = backend.route(dest, world)
+    local_e = (ids.reshape(-1) % experts_per_rank).to(torch.int32)[order.long()].contiguous()
+    return rows.tolist(), order, p2s, local_e
+
+
+def ep_moe_forward(x, logits, w13, s13, w2, s2, top_k: int, num_experts: int, backend, group=None):
+    """Expert-parallel MoE forward for this rank's tokens.
+
+    x [T_local, H], logits [T_local, E]; w13 / s13 / w2 / s2 hold this rank's experts
+    [E/world, ...].  Steps: top-k -> plan by destination rank -> exchange counts -> all-to-all rows and
+    local expert ids -> route + grouped up GEMM + SiLU*mul + grouped down GEMM on the owner -> all-to-all back
+    -> weighted combine at the source.  Returns [T_local, H]."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    T, H = x.shape
+    e_local = num_experts // world
+    wts, ids = backend.topk(logits, top_k, x.dtype)
+    send_counts, order, p2s, local_e = ep_plan(ids, e_local, world, backend)
+    send_rows = backend.gather_rows(x, order, top_k)                       # [n_pairs, H] grouped by destination
+
+    if world > 1:
+        sc = torch.tensor(send_counts, dtype=torch.int64, device=x.device)
+        rc = torch.empty_like(sc)
+        dist.all_to_all_single(rc, sc, group=group)
+        recv_counts = rc.tolist()
+        n_recv = int(sum(recv_counts))
+        recv_rows = torch.empty(n_recv, H, dtype=x.dtype, device=x.device)
+        recv_e = torch.empty(n_recv, dtype=torch.int32, device=x.device)
+        dist.all_to_all_single(recv_rows, send_rows, recv_counts, send_counts, group=group)
+        dist.all_to_all_single(recv_e, local_e, recv_counts, send_counts, group=group)
+    else:
+        recv_counts, n_recv, recv_rows, recv_e = send_counts, send_rows.shape[0], send_rows, local_e
+
+    if n_recv > 0:
+        offsets, tokens, _, _ = backend.route(recv_e.reshape(-1, 1), e_local)
+        y_recv = backend.expert_mlp(recv_rows, w13, s13, w2, s2, offsets, tokens, n_recv)
+    else:
+        y_recv = torch.empty(0, H, dtype=x.dtype, device=x.device)
+
+    if world > 1:
+        y_send = torch.empty(send_rows.shape[0], H, dtype=x.dtype, device=x.device)
+        dist.all_to_all_single(y_send, y_recv, send_counts, recv_counts, group=group)
+    else:
+        y_send = y_recv
+    return backend.combine(y_send, wts, p2s, T, top_k)
