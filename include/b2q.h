@@ -159,6 +159,21 @@ B2Q_API int b2q_moe_route(const int32_t* ids, int64_t n_pairs, int E,
                   int32_t* pair_to_perm, int32_t* rows_per_expert,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same sort, same outputs, no workspace argument.  This entry point has no counterpart in
+ * the reference.  It is for callers that must not allocate device memory around the call:
+ * code running inside a stream capture (where cudaMalloc is not allowed), runtimes that plan
+ * all device memory in advance, hosts without a pooled allocator.  The scratch table lives in
+ * a fixed array inside the library (256 KB per GPU that loads it, held until exit), so
+ *   - n_pairs <= 65536 and E <= 256, otherwise B2Q_ERR_LIMIT;
+ *   - the first call on each device looks up the array's device address (with that device
+ *     current); make that first call outside any stream capture;
+ *   - every call on a device uses the same array: calls whose kernels may overlap on the GPU
+ *     (different streams) race on it.  Nothing needs clearing between calls.
+ * It calls no allocation routine of any kind.                                               */
+B2Q_API int b2q_moe_route_static(const int32_t* ids, int64_t n_pairs, int E,
+                  int32_t* expert_offsets, int32_t* expert_tokens,
+                  int32_t* pair_to_perm, int32_t* rows_per_expert, void* stream);
+
 /* dst[r, :] = src[idx[r] / div, :] for r < rows (row gather; div = top_k maps
  * pair index -> token).  Replaces moe_prefill_scatter_x_forward (:818-859).   */
 B2Q_API int b2q_gather_rows(const void* src, const int32_t* idx, int div, void* dst,

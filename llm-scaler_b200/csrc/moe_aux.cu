@@ -446,3 +446,61 @@ int act_to_scaled_f16(const void* x, int64_t ldx, void* x16, float* inv_scale, i
 }
 
 }  // namespace b2q
+
+// ---------------------------------------------------------------------------
+// Routing without a caller-provided workspace.
+//
+// b2q_moe_route() needs a small scratch table (per-chunk expert histograms) that the caller has to
+// allocate.  Some callers cannot: code that runs while a CUDA stream is being captured (cudaMalloc is
+// illegal there), serving runtimes that plan all device memory up front and hand the kernels no
+// allocator, and plain C hosts that have no pooled allocator and do not want a cudaMalloc/cudaFree
+// pair on the decode path.  For them the same three kernels run on a table that lives in the
+// library image itself.  The table is a fixed-size device array, so the problem size is capped, every
+// GPU that loads the library carries the array until the process exits, and all calls share it.
+// ---------------------------------------------------------------------------
+namespace b2q {
+
+constexpr int64_t ROUTE_STATIC_MAX_PAIRS = 65536;   // token * top_k pairs
+constexpr int ROUTE_STATIC_MAX_EXPERTS = 256;
+constexpr int64_t ROUTE_STATIC_WORDS = (ROUTE_STATIC_MAX_PAIRS / ROUTE_CHUNK) * ROUTE_STATIC_MAX_EXPERTS;  // 65536 int32 = 256 KB
+
+static __device__ __align__(256) int32_t g_route_scratch[ROUTE_STATIC_WORDS];
+
+// In host code `g_route_scratch` is only a handle for the runtime, not something a kernel can
+// dereference; the device address has to be asked for, per device, with that device current.
+static int route_scratch_address(int32_t** out) {
+  static int32_t* cached[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B2Q_ERR_CUDA;
+  int32_t* p = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+  if (!p) {
+    void* sym = nullptr;
+    if (cudaGetSymbolAddress(&sym, g_route_scratch) != cudaSuccess || !sym) return B2Q_ERR_CUDA;
+    p = reinterpret_cast<int32_t*>(sym);
+    __atomic_store_n(&cached[dev], p, __ATOMIC_RELEASE);   // racing first calls store the same value
+  }
+  *out = p;
+  return B2Q_OK;
+}
+
+int moe_route_static(const int32_t* ids, int64_t n_pairs, int E, int32_t* expert_offsets, int32_t* expert_tokens,
+                     int32_t* pair_to_perm, int32_t* rows_per_expert, cudaStream_t st) {
+  if (n_pairs > ROUTE_STATIC_MAX_PAIRS || E > ROUTE_STATIC_MAX_EXPERTS) return B2Q_ERR_LIMIT;
+  int32_t* scratch = nullptr;
+  const int rc = route_scratch_address(&scratch);
+  if (rc) return rc;
+  // Nothing in the table has to start at zero: the histogram kernel overwrites every (chunk, expert)
+  // slot that the two later kernels read for this problem size.
+  return moe_route(ids, n_pairs, E, expert_offsets, expert_tokens, pair_to_perm, rows_per_expert, scratch, st);
+}
+
+}  // namespace b2q
+
+extern "C" B2Q_API int b2q_moe_route_static(const int32_t* ids, int64_t n_pairs, int E, int32_t* expert_offsets,
+                                            int32_t* expert_tokens, int32_t* pair_to_perm, int32_t* rows_per_expert,
+                                            void* stream) {
+  if (!ids || !expert_offsets || !expert_tokens) return B2Q_ERR_NULL;
+  if (n_pairs < 0 || E <= 0) return B2Q_ERR_SHAPE;
+  return b2q::moe_route_static(ids, n_pairs, E, expert_offsets, expert_tokens, pair_to_perm, rows_per_expert,
+                               (cudaStream_t)stream);
+}

@@ -35,6 +35,7 @@ _SIGS = {
     "b2q_moe_topk": (i32, [vp, i32, i64, i32, i32, i32, vp, i32, vp, vp]),
     "b2q_moe_route_workspace_bytes": (sz, [i64, i32]),
     "b2q_moe_route": (i32, [vp, i64, i32, vp, vp, vp, vp, vp, sz, vp]),
+    "b2q_moe_route_static": (i32, [vp, i64, i32, vp, vp, vp, vp, vp]),
     "b2q_gather_rows": (i32, [vp, vp, i32, vp, i64, i64, i32, vp]),
     "b2q_silu_mul": (i32, [vp, vp, i32, i64, i64, vp]),
     "b2q_moe_combine": (i32, [vp, vp, i32, vp, vp, i32, i64, i32, i64, i32, vp]),
