@@ -104,14 +104,20 @@ def require_cuda(*ts):
 class on_device:
     """Makes the tensor's device current for the duration of a launch."""
 
+    __slots__ = ("g",)
+
     def __init__(self, t):
-        self.g = torch.cuda.device(t.device)
+        # the common case (tensor on the current device) costs one integer compare, not a context switch
+        idx = t.device.index
+        self.g = None if idx is None or idx == torch.cuda.current_device() else torch.cuda.device(idx)
 
     def __enter__(self):
-        return self.g.__enter__()
+        if self.g is not None:
+            self.g.__enter__()
 
     def __exit__(self, *a):
-        return self.g.__exit__(*a)
+        if self.g is not None:
+            self.g.__exit__(*a)
 
 
 def launch_count() -> int:

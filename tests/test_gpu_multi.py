@@ -1,0 +1,102 @@
+"""Tensor-parallel and expert-parallel schedules on two GPUs over NCCL, CUDA kernels underneath, against the
+unsharded CPU oracle.  Skipped when fewer than two GPUs are visible."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import configs, int4, moe
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, what, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from custom_esimd_kernels_vllm import parallel as P
+        be = P.CudaBackend()
+        if what == "tp":
+            full = configs.c5_layer(seed=3, M=40, tp=1, rank=0, scale=1 / 16)
+            packed = {n: (int4.pack_nmajor_i32(full[n][0]), full[n][1]) for n in ("qkv", "o", "gate_up", "down")}
+            hidden = full["x"].shape[1]
+            qw, qs = packed["qkv"]
+            rest = qw.shape[0] - hidden
+            rows = torch.cat([torch.arange(rank * hidden // world, (rank + 1) * hidden // world),
+                              hidden + torch.arange(rank * rest // world, (rank + 1) * rest // world)])
+            to = lambda pair: (pair[0].to(dev), pair[1].to(dev))
+            layer = P.TPLayer(qkv=to((qw[rows].contiguous(), qs[rows].contiguous())),
+                              o=to(P.shard_row(*packed["o"], rank, world)),
+                              gate_up=to(P.shard_column(*packed["gate_up"], rank, world, fused_halves=2)),
+                              down=to(P.shard_row(*packed["down"], rank, world)))
+            out = P.tp_layer_forward(full["x"].to(dev), layer, be)
+        else:
+            c = configs.c4(seed=5, T=256, E=8, top_k=2, H=256, I=128)
+            T = c["x"].shape[0] // world
+            el = 8 // world
+            sl, es = slice(rank * T, (rank + 1) * T), slice(rank * el, (rank + 1) * el)
+            out = P.ep_moe_forward(c["x"][sl].contiguous().to(dev), c["logits"][sl].contiguous().to(dev),
+                                   int4.pack_nmajor_i32(c["q13"][es]).to(dev), c["s13"][es].contiguous().to(dev),
+                                   int4.pack_nmajor_i32(c["q2"][es]).to(dev), c["s2"][es].contiguous().to(dev), 2, 8, be)
+        torch.cuda.synchronize()
+        q.put((rank, out.cpu()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(what):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, what, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    outs = dict(q.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    return outs
+
+
+@pytest.fixture(scope="module")
+def two_gpus(lib_built):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+
+
+def _err(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max())
+
+
+@pytest.mark.timeout(600)
+def test_tensor_parallel_layer_two_gpus(two_gpus):
+    outs = _run("tp")
+    assert torch.equal(outs[0], outs[1])
+    full = configs.c5_layer(seed=3, M=40, tp=1, rank=0, scale=1 / 16)
+    x = full["x"]
+    lin = lambda t, name: int4.linear(t, *full[name]).to(x.dtype)
+    h = lin(lin(x, "qkv")[:, :x.shape[1]].contiguous(), "o")
+    ref = lin(moe.silu_mul(lin(h, "gate_up")), "down")
+    assert _err(outs[0], ref) < 3e-2          # four chained GEMMs with 16-bit tensors between them
+
+
+@pytest.mark.timeout(600)
+def test_expert_parallel_two_gpus(two_gpus):
+    outs = _run("ep")
+    c = configs.c4(seed=5, T=256, E=8, top_k=2, H=256, I=128)
+    ref = moe.forward(c["x"], c["logits"], int4.dequant(c["q13"], c["s13"], torch.bfloat16),
+                      int4.dequant(c["q2"], c["s2"], torch.bfloat16), 2)
+    assert _err(torch.cat([outs[0], outs[1]]), ref) < 3e-2
