@@ -99,12 +99,19 @@ B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, in
  *  kernels csrc/xpu/esimd_kernels/int4_GEMV.h:165-304, int4_GEMM.h:81-320).
  * Any M >= 1.  K % group == 0, group == 128, K % 8 == 0.
  * scale strides are in elements: scale(n, kg) = scale[n*s_stride_n + kg*s_stride_g].
- * ldx / ldo are row pitches of x / out in elements.                           */
+ * ldx / ldo are row pitches of x / out in elements.
+ * workspace is optional (NULL / 0 allowed).  With at least b2q_linear_workspace_bytes() of
+ * scratch the tensor-core kernel first rewrites the activations as fp16 times a per-token power
+ * of two in the element order its nibble decode produces; the dequantised weight is then
+ * (q - 8) * scale rounded once to fp16 (11 significant bits) instead of to the activation type.
+ * Without scratch the weight is rounded exactly as the torch reference rounds it.              */
+B2Q_API size_t b2q_linear_workspace_bytes(int64_t M, int64_t K);
 B2Q_API int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx,
                     const void* w, int w_layout,
                     const void* scale, int scale_dtype, int64_t s_stride_n, int64_t s_stride_g,
                     void* out, int64_t ldo,
-                    int64_t M, int64_t N, int64_t K, int group, void* stream);
+                    int64_t M, int64_t N, int64_t K, int group,
+                    void* workspace, size_t workspace_bytes, void* stream);
 
 /* Replaces esimd_gemv_fp8_pern / esimd_gemv_fp8_pert / esimd_gemm_fp8_pert /
  * esimd_gemm_fp8_blockscale (csrc/xpu/torch_extension.cc:9-37,
@@ -199,7 +206,7 @@ B2Q_API int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int
  * INT4: w is E stacked matrices in w_layout, scales E stacked.
  * Replaces moe_prefill_up/down_forward_v2 (:493-621), moe_gemm_int4_nmajor
  * (csrc/moe_batch/moe_int4.sycl:3373-3552).                                    */
-/* gather != 0 when a row_map will be passed (the tcgen05 path stages the gathered rows). */
+/* gather is ignored (kept for call compatibility): the pre-passed activations are always staged. */
 B2Q_API size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int64_t K, int act, int gather);
 B2Q_API int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx,
                       const int32_t* row_map, int row_div,

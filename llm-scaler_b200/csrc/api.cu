@@ -22,7 +22,7 @@ int gather_rows(const void*, const int32_t*, int, void*, int64_t, int64_t, int, 
 int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t);
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
-int act_to_scaled_f16(const void*, int64_t, void*, float*, int64_t, int, cudaStream_t);
+int act_prep(const void*, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -97,7 +97,7 @@ int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, int scale_
 
 int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, int w_layout, const void* scale,
                     int scale_dtype, int64_t s_stride_n, int64_t s_stride_g, void* out, int64_t ldo, int64_t M,
-                    int64_t N, int64_t K, int group, void* stream) {
+                    int64_t N, int64_t K, int group, void* workspace, size_t workspace_bytes, void* stream) {
   if (!x || !w || !scale || !out) return B2Q_ERR_NULL;
   if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
   if (scale_dtype < 0 || scale_dtype > 2) return B2Q_ERR_DTYPE;
@@ -119,8 +119,22 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   const bool umma_ok = umma_w4_supported(ua);
   // measured on B200: the mma.sync streaming kernel wins only for a handful of tokens (its per-token cost is
   // fragment traffic), the tcgen05 kernel is flat in M up to 64 and the only one for K-major layouts and prefill
-  const bool want_umma = force == 2 || (force == 0 && (kmajor || M > 8));
-  if (umma_ok && want_umma) return umma_w4_linear(ua, st);
+  const bool want_umma = force == 2 || force == 3 || (force == 0 && (kmajor || M > 8));
+  if (umma_ok && want_umma) {
+    // With scratch, activations go through the pre-pass (fp16, per-token power-of-two scale, pair order of
+    // the magic-number transform) and the transform's integer work drops from 12 to 5 operations per word.
+    const bool prep = workspace && aligned16(workspace) && workspace_bytes >= b2q_linear_workspace_bytes(M, K) &&
+                      force != 3;
+    ua.out_bf16 = ua.bf16;
+    if (prep) {
+      float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * (size_t)K * 2, 256));
+      const int perm = w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1;
+      int rc = act_prep(x, act_dtype == B2Q_BF16, ldx, nullptr, 1, workspace, inv, M, (int)K, perm, st);
+      if (rc) return rc;
+      ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.tok_scale = inv; ua.magic = true;
+    }
+    return umma_w4_linear(ua, st);
+  }
   if (kmajor) return B2Q_ERR_UNSUPPORTED;
 
   SmallMParams p{};
@@ -132,9 +146,10 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   return smallm_int4(p, act_dtype == B2Q_BF16, (int)M, 0, st);
 }
 
-size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t K) {
+size_t b2q_linear_workspace_bytes(int64_t M, int64_t K) {
   return align_up((size_t)M * (size_t)K * 2, 256) + align_up((size_t)M * 4, 256);
 }
+size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t K) { return b2q_linear_workspace_bytes(M, K); }
 
 int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
                    int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
@@ -165,7 +180,7 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
   if (umma_ok && want_umma) {
     if (prep) {
       float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * (size_t)K * 2, 256));
-      int rc = act_to_scaled_f16(x, ldx, workspace, inv, M, (int)K, st);
+      int rc = act_prep(x, true, ldx, nullptr, 1, workspace, inv, M, (int)K, 0, st);
       if (rc) return rc;
       ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.out_bf16 = true; ua.tok_scale = inv;
     }
@@ -255,8 +270,10 @@ int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int32_t* pe
 
 size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int64_t K, int act, int gather) {
   // [tile list for the smallest (8-row) tiling] [gathered activations rows x K] [un-activated rows x N]
+  // [tile list] [pre-passed activations rows x K fp16] [per-row scales] [un-activated rows x N]
+  (void)gather;
   size_t b = tile_list_bytes(rows, E, 8);
-  if (gather) b += align_up((size_t)rows * (size_t)K * 2, 256);
+  b += align_up((size_t)rows * (size_t)K * 2, 256) + align_up((size_t)rows * 4, 256);
   if (act != B2Q_ACT_NONE) b += align_up((size_t)rows * (size_t)N * 2, 256);
   return b;
 }
@@ -269,13 +286,14 @@ int b2q_device_status(int* out) {
 // Shared tail of the grouped GEMMs once the kernel family is chosen: optional row gather in
 // front of the tcgen05 kernel, optional SiLU*mul behind either kernel.
 struct GroupedPlan {
-  uint8_t* tiles; uint8_t* xg; uint8_t* g;
+  uint8_t* tiles; uint8_t* xg; float* inv; uint8_t* g;
 };
-static GroupedPlan plan_workspace(void* ws, int64_t rows, int E, int64_t K, bool gather) {
+static GroupedPlan plan_workspace(void* ws, int64_t rows, int E, int64_t K, bool) {
   GroupedPlan pl;
   pl.tiles = reinterpret_cast<uint8_t*>(ws);
   pl.xg = pl.tiles + tile_list_bytes(rows, E, 8);
-  pl.g = pl.xg + (gather ? align_up((size_t)rows * (size_t)K * 2, 256) : 0);
+  pl.inv = reinterpret_cast<float*>(pl.xg + align_up((size_t)rows * (size_t)K * 2, 256));
+  pl.g = reinterpret_cast<uint8_t*>(pl.inv) + align_up((size_t)rows * 4, 256);
   return pl;
 }
 
@@ -315,12 +333,12 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
   ua.expert_offsets = expert_offsets; ua.E = E; ua.out_map = gemm_out_map; ua.tiles = tiles;
   const int64_t avg = (rows + E - 1) / E;
   const bool want_umma = force == 2 || (force == 0 && (kmajor || avg > 16));
+  ua.out_bf16 = bf;
   if (umma_w4_supported(ua) && want_umma) {
-    if (row_map) {
-      rc = gather_rows(x, row_map, row_div, pl.xg, rows, K, 2, st);
-      if (rc) return rc;
-      ua.x = pl.xg; ua.ldx = K;
-    }
+    // gather (if any), fp16 re-scaling and pair permutation in one pre-pass over the rows
+    rc = act_prep(x, bf, ldx, row_map, row_div, pl.xg, pl.inv, rows, (int)K, w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1, st);
+    if (rc) return rc;
+    ua.x = pl.xg; ua.ldx = K; ua.bf16 = false; ua.tok_scale = pl.inv; ua.magic = true;
     const int tile = umma_w4_token_tile(ua);
     rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
     if (rc) return rc;

@@ -504,3 +504,93 @@ extern "C" B2Q_API int b2q_moe_route_static(const int32_t* ids, int64_t n_pairs,
   return b2q::moe_route_static(ids, n_pairs, E, expert_offsets, expert_tokens, pair_to_perm, rows_per_expert,
                                (cudaStream_t)stream);
 }
+
+namespace b2q {
+
+// ---------------------------------------------------------------------------
+// General activation pre-pass in front of the tcgen05 GEMM: optional row gather, per-token
+// power-of-two scaling into fp16 (see act_to_scaled_f16_kernel for why that is exact in practice)
+// and an optional permutation inside every group of eight k so that the INT4 transform can emit
+// its nibble pairs in the order the bit tricks produce them instead of re-sorting them:
+//   perm 0: identity      perm 1: (0,4,1,5,2,6,3,7)  nibble i at bits 4i (GGML / N-major, plain K-major)
+//                         perm 2: (0,2,4,6,1,3,5,7)  marlin-shuffled words
+// dst row r = f(src row (idx ? idx[r] / div : r)); fp16 input keeps scale 1.
+template <bool IN_BF16>
+__global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const int32_t* __restrict__ idx, int div,
+                                __half* __restrict__ x16, float* __restrict__ inv_scale, int K, int perm) {
+  __shared__ float red[32];
+  __shared__ float sc_sh;
+  const int64_t r = blockIdx.x;
+  const int64_t srow = idx ? (int64_t)(idx[r] / div) : r;
+  const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + srow * ldx;
+  float sc = 1.f;
+  if constexpr (IN_BF16) {
+    float amax = 0.f;
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+      const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(e[j])));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float a = 0.f;
+      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, red[i]);
+      float s = 1.f;
+      if (a > 0.f && a < INFINITY) {
+        const int ex = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127;
+        int sh = 14 - ex;
+        sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+        s = __uint_as_float((uint32_t)(sh + 127) << 23);
+      }
+      sc_sh = s;
+      inv_scale[r] = 1.0f / s;
+    }
+    __syncthreads();
+    sc = sc_sh;
+  } else {
+    if (threadIdx.x == 0) inv_scale[r] = 1.0f;
+  }
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    __half h[8];
+    if constexpr (IN_BF16) {
+      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(__bfloat162float(e[j]) * sc);
+    } else {
+      const __half* e = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = e[j];
+    }
+    uint4 o;
+    __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      // position j of the stored group holds source element src(j)
+      const int src = perm == 1 ? ((j & 1) * 4 + (j >> 1)) : (perm == 2 ? ((j & 3) * 2 + (j >> 2)) : j);
+      oh[j] = h[src];
+    }
+    *reinterpret_cast<uint4*>(x16 + r * (int64_t)K + k) = o;
+  }
+}
+
+int act_prep(const void* x, bool in_bf16, int64_t ldx, const int32_t* idx, int div, void* x16, float* inv_scale,
+             int64_t rows, int K, int perm, cudaStream_t st) {
+  if (rows == 0) return B2Q_OK;
+  int threads = (K / 8 + 31) / 32 * 32;
+  threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
+  if (in_bf16)
+    act_prep_kernel<true><<<(unsigned)rows, threads, 0, st>>>(x, ldx, idx, div > 0 ? div : 1, reinterpret_cast<__half*>(x16),
+                                                              inv_scale, K, perm);
+  else
+    act_prep_kernel<false><<<(unsigned)rows, threads, 0, st>>>(x, ldx, idx, div > 0 ? div : 1, reinterpret_cast<__half*>(x16),
+                                                               inv_scale, K, perm);
+  note_launch("act_prep");
+  return launch_status();
+}
+
+}  // namespace b2q

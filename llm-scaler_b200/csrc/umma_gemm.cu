@@ -51,6 +51,7 @@ struct UmmaWoParams {
   void* out; int64_t ldo;
   int M, N, K;
   int marlin; uint32_t xor_mask; int e5m2;
+  int magic;                 // INT4: fp16 magic-number transform; x was permuted / scaled by the pre-pass
   const int32_t* tiles; const int32_t* expert_offsets; const int32_t* out_map;
   int w_rows_per_expert;     // tensor-map rows per expert: N (N-major) or K/8 (K-major)
   const float* tok_scale;    // optional per-token output multiplier (undoes the activation pre-scale)
@@ -105,6 +106,27 @@ __device__ __forceinline__ void w4_word(uint32_t w, uint32_t s2, float sf, bool 
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) o[j] = pack2f<BF16>(v[2 * j], v[2 * j + 1]);
+  }
+}
+
+// fp16 magic-number variant: 0x6400 | q is 1024 + q and 0x6400 | (q << 4) is 1024 + 16 q, so the nibbles at
+// bits 0-3 / 4-7 of each half-word need no shift; one shift by 8 reaches the other four.  The result
+// (q - 8) * s is rounded to fp16 once.  Output pair order: (n0,n4) (n1,n5) (n2,n6) (n3,n7) where n_i is the
+// nibble at bits 4i; the activation pre-pass stores x in the matching order.  Integer work per word: one
+// shift and four LOP3 (the ALU pipe, not the FP pipes, is what bounds the int4 transform).
+__device__ __forceinline__ void w4_word_magic(uint32_t w, uint32_t s2, uint32_t (&o)[4]) {
+  const uint32_t c1032 = 0x64086408u, r16 = 0x2C002C00u, m72 = 0xD480D480u;
+  const uint32_t w8 = w >> 8;
+  uint32_t v[4] = {(w & 0x000F000Fu) | 0x64006400u, (w & 0x00F000F0u) | 0x64006400u,
+                   (w8 & 0x000F000Fu) | 0x64006400u, (w8 & 0x00F000F0u) | 0x64006400u};
+  const __half2 sc = *reinterpret_cast<const __half2*>(&s2);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 h = *reinterpret_cast<__half2*>(&v[i]);
+    if (i & 1) h = __hfma2(h, *reinterpret_cast<const __half2*>(&r16), *reinterpret_cast<const __half2*>(&m72));
+    else h = __hsub2(h, *reinterpret_cast<const __half2*>(&c1032));
+    h = __hmul2(h, sc);
+    o[i] = *reinterpret_cast<uint32_t*>(&h);
   }
 }
 
@@ -307,23 +329,37 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         if constexpr (WK == WK_W4N || WK == WK_W4K) {
           uint32_t s2 = 0; float sf = 0.f;
           const int64_t si = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)(c >> 1) * p.s_stride_g;
-          if constexpr (FAST) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si]; s2 = sv | (sv << 16); }
+          if constexpr (FAST) { if (!p.magic) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si]; s2 = sv | (sv << 16); } }
           else sf = load_scalar(p.scale, si, p.scale_dtype);
+          uint32_t ww[8];
+          bool marlin = false;
           if constexpr (WK == WK_W4N) {
             const uint4 r0 = lds128(rawrow + (((2 * j) ^ sw) << 4));
             const uint4 r1 = lds128(rawrow + (((2 * j + 1) ^ sw) << 4));
-            const uint32_t ww[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              uint32_t o[4];
-              w4_word<BF16, FAST>(ww[i] ^ p.xor_mask, s2, sf, false, o);
-              av[4 * i] = o[0]; av[4 * i + 1] = o[1]; av[4 * i + 2] = o[2]; av[4 * i + 3] = o[3];
-            }
+            ww[0] = r0.x ^ p.xor_mask; ww[1] = r0.y ^ p.xor_mask; ww[2] = r0.z ^ p.xor_mask; ww[3] = r0.w ^ p.xor_mask;
+            ww[4] = r1.x ^ p.xor_mask; ww[5] = r1.y ^ p.xor_mask; ww[6] = r1.z ^ p.xor_mask; ww[7] = r1.w ^ p.xor_mask;
           } else {
-            const bool marlin = p.marlin != 0;
-            uint32_t ww[8];
+            marlin = p.marlin != 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) ww[i] = lds32(rawcol + (8 * j + i) * 512);
+          }
+          bool done = false;
+          if constexpr (!BF16 && FAST) {
+            if (p.magic) {
+              // fp16 magic-number path: the activation pre-pass stored x in the pair order this produces
+              const __half hs = __float2half_rn(load_scalar(p.scale, si, p.scale_dtype));
+              const uint32_t hv = __half_as_ushort(hs);
+              const uint32_t m2 = hv | (hv << 16);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                uint32_t o[4];
+                w4_word_magic(ww[i], m2, o);
+                av[4 * i] = o[0]; av[4 * i + 1] = o[1]; av[4 * i + 2] = o[2]; av[4 * i + 3] = o[3];
+              }
+              done = true;
+            }
+          }
+          if (!done) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               uint32_t o[4];
@@ -577,9 +613,9 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.marlin = a.layout == B2Q_W4_KMAJOR_MARLIN; p.xor_mask = a.layout == B2Q_W4_NMAJOR_S4 ? 0x88888888u : 0u;
   p.tiles = grouped ? a.tiles : nullptr; p.expert_offsets = a.expert_offsets; p.out_map = a.out_map;
   p.w_rows_per_expert = kmajor ? a.K / 8 : a.N;
-  p.tok_scale = nullptr; p.out_bf16 = a.bf16 ? 1 : 0;
+  p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0; p.magic = a.magic ? 1 : 0;
   p.status = status_ptr();
-  const bool fast = (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
+  const bool fast = a.magic || (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
   return kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)
                 : launch_wk<WK_W4N>(a.bf16, fast, tok, tw, tx, p, tiles, st);

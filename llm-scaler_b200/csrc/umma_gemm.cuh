@@ -17,7 +17,9 @@ struct UmmaGroupArgs {
 };
 
 struct UmmaW4Args : UmmaGroupArgs {
-  const void* x; int64_t ldx; bool bf16;
+  const void* x; int64_t ldx; bool bf16;      // bf16: element type of x (the MMA input type)
+  bool out_bf16; const float* tok_scale;      // output type; optional per-token multiplier
+  bool magic;                                 // x is the pre-pass output (fp16, scaled, pair-permuted)
   const void* w; int layout;
   const void* scale; int scale_dtype; int64_t s_stride_n, s_stride_g;
   void* out; int64_t ldo;

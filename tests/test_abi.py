@@ -46,23 +46,23 @@ def test_strerror_and_version(lib):
 def test_null_and_shape_errors_need_no_device(lib_built):
     from custom_esimd_kernels_vllm import _lib as L
     lib = L.lib
-    assert lib.b2q_linear_int4(None, 0, 128, None, 0, None, 0, 1, 1, None, 16, 1, 16, 128, 128, None) == -1
+    assert lib.b2q_linear_int4(None, 0, 128, None, 0, None, 0, 1, 1, None, 16, 1, 16, 128, 128, None, 0, None) == -1
     buf = (C.c_uint8 * 4096)()
     p = C.addressof(buf)
     p = (p + 255) // 256 * 256
     # group != 128
-    assert lib.b2q_linear_int4(p, 0, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 64, None) == -2
+    assert lib.b2q_linear_int4(p, 0, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 64, None, 0, None) == -2
     # unknown activation dtype
-    assert lib.b2q_linear_int4(p, 7, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None) == -3
+    assert lib.b2q_linear_int4(p, 7, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None, 0, None) == -3
     # unknown layout
-    assert lib.b2q_linear_int4(p, 0, 128, p, 9, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None) == -5
+    assert lib.b2q_linear_int4(p, 0, 128, p, 9, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None, 0, None) == -5
     # misaligned activation pointer
-    assert lib.b2q_linear_int4(p + 2, 0, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None) == -4
+    assert lib.b2q_linear_int4(p + 2, 0, 128, p, 0, p, 0, 1, 1, p, 16, 1, 16, 128, 128, None, 0, None) == -4
     # fp8: K not a multiple of 16, block mode needs fp32 scales
     assert lib.b2q_linear_fp8(p, 0, 40, p, 0, p, 2, 0, p, 16, 1, 16, 40, None, 0, None) == -2
     assert lib.b2q_linear_fp8(p, 0, 128, p, 0, p, 0, 2, p, 16, 1, 16, 128, None, 0, None) == -3
     # M == 0 is a successful no-op
-    assert lib.b2q_linear_int4(p, 0, 128, p, 0, p, 0, 1, 1, p, 16, 0, 16, 128, 128, None) == 0
+    assert lib.b2q_linear_int4(p, 0, 128, p, 0, p, 0, 1, 1, p, 16, 0, 16, 128, 128, None, 0, None) == 0
     # route: workspace too small
     assert lib.b2q_moe_route(p, 1024, 8, p, p, p, p, p, 16, None) == -8
     assert lib.b2q_moe_topk(p, 0, 4, 2048, 8, 1, p, 0, p, None) == -10
@@ -74,7 +74,8 @@ def test_workspace_size_queries(lib_built):
     small = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 512, 0, 0)
     big = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 512, 1, 0)
     assert big >= small + 1024 * 256 * 2
-    assert L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 512, 0, 1) >= small + 1024 * 512 * 2
+    assert small >= 1024 * 512 * 2 + 1024 * 4          # staged activations + per-row scales are always there
+    assert L.lib.b2q_linear_workspace_bytes(64, 8192) >= 64 * 8192 * 2 + 64 * 4
 
 
 def test_ops_refuse_cpu_tensors(lib_built):

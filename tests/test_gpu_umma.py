@@ -64,7 +64,7 @@ def test_int4_kmajor(e, marlin, M, N, K):
         xd, wd, sd = x.to(DEV), wk.to(DEV), sk.to(DEV)
         with L.on_device(out):
             L.check(L.lib.b2q_linear_int4(xd.data_ptr(), L.BF16, K, wd.data_ptr(), L.W4_KMAJOR_MARLIN,
-                                          sd.data_ptr(), L.BF16, 1, N, out.data_ptr(), N, M, N, K, 128, None))
+                                          sd.data_ptr(), L.BF16, 1, N, out.data_ptr(), N, M, N, K, 128, None, 0, None))
         torch.cuda.synchronize()
     assert_close(out, ref, what=f"umma int4 kmajor marlin={marlin}")
 
@@ -77,7 +77,7 @@ def test_int4_s4(e):
     xd, sd = x.to(DEV), s.to(DEV)
     out = torch.empty(20, 256, dtype=torch.float16, device=DEV)
     L.check(L.lib.b2q_linear_int4(xd.data_ptr(), L.F16, 256, s4.data_ptr(), L.W4_NMAJOR_S4, sd.data_ptr(), L.F16, 2, 1,
-                                  out.data_ptr(), 256, 20, 256, 256, 128, None))
+                                  out.data_ptr(), 256, 20, 256, 256, 128, None, 0, None))
     torch.cuda.synchronize()
     assert_close(out, int4.linear(x, q, s), what="umma s4")
 
