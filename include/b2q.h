@@ -104,8 +104,10 @@ B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, in
  * scratch the tensor-core kernel first rewrites the activations as fp16 times a per-token power
  * of two in the element order its nibble decode produces; the dequantised weight is then
  * (q - 8) * scale rounded once to fp16 (11 significant bits) instead of to the activation type.
- * Without scratch the weight is rounded exactly as the torch reference rounds it.              */
-B2Q_API size_t b2q_linear_workspace_bytes(int64_t M, int64_t K);
+ * Without scratch the weight is rounded exactly as the torch reference rounds it.  For M <= 64
+ * the scratch also holds an fp32 [M, N] accumulator: K is then split over several CTAs per strip of
+ * output rows so that layers with few output rows still occupy every SM.                        */
+B2Q_API size_t b2q_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 B2Q_API int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx,
                     const void* w, int w_layout,
                     const void* scale, int scale_dtype, int64_t s_stride_n, int64_t s_stride_g,
@@ -123,7 +125,7 @@ B2Q_API int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx,
  * b2q_linear_fp8_workspace_bytes() of scratch, bf16 activations are first rewritten
  * as fp16 times a per-token power of two (exact for every element within 2^-31 of
  * its row maximum), which makes the in-kernel fp8 decode four times cheaper.        */
-B2Q_API size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t K);
+B2Q_API size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K);
 B2Q_API int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx,
                    const void* w, int fp8_format,
                    const void* scale, int scale_dtype, int scale_mode,

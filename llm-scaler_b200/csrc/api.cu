@@ -35,6 +35,24 @@ static inline size_t tile_list_bytes(int64_t rows, int E, int tile) {
   return align_up(16 + 8 * (size_t)((rows + tile - 1) / tile + E), 256);
 }
 
+// [pre-passed activations M x K fp16] [per-token scales] [fp32 split-K accumulator M x N, decode shapes only]
+static inline size_t ws_prep_bytes(int64_t M, int64_t K) {
+  return align_up((size_t)M * (size_t)K * 2, 256) + align_up((size_t)M * 4, 256);
+}
+
+// Decode shapes: split K so that strips x splits fills the machine; the fp32 accumulator is zeroed here.
+template <class Args>
+static int plan_split(Args& ua, void* workspace, int64_t M, int64_t N, int64_t K, int chunks_per_raw, cudaStream_t st) {
+  if (M > 64) return B2Q_OK;
+  int cps = 0;
+  const int sk = umma_plan_split_k((int)N, (int)K, chunks_per_raw, &cps);
+  if (sk <= 1) return B2Q_OK;
+  float* acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + ws_prep_bytes(M, K));
+  if (cudaMemsetAsync(acc, 0, (size_t)M * (size_t)N * 4, st) != cudaSuccess) return B2Q_ERR_CUDA;
+  ua.split_k = sk; ua.chunks_per_split = cps; ua.split_acc = acc;
+  return B2Q_OK;
+}
+
 }  // namespace b2q
 
 using namespace b2q;
@@ -119,11 +137,13 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   const bool umma_ok = umma_w4_supported(ua);
   // measured on B200: the mma.sync streaming kernel wins only for a handful of tokens (its per-token cost is
   // fragment traffic), the tcgen05 kernel is flat in M up to 64 and the only one for K-major layouts and prefill
-  const bool want_umma = force == 2 || force == 3 || (force == 0 && (kmajor || M > 8));
+  // small weights at small M: one launch of the streaming kernel beats pre-pass + GEMM (+ split-K finalize)
+  const bool tiny = M <= 32 && N * K <= (int64_t)1 << 25;
+  const bool want_umma = force == 2 || force == 3 || (force == 0 && (kmajor || (M > 8 && !tiny)));
   if (umma_ok && want_umma) {
     // With scratch, activations go through the pre-pass (fp16, per-token power-of-two scale, pair order of
     // the magic-number transform) and the transform's integer work drops from 12 to 5 operations per word.
-    const bool prep = workspace && aligned16(workspace) && workspace_bytes >= b2q_linear_workspace_bytes(M, K) &&
+    const bool prep = workspace && aligned16(workspace) && workspace_bytes >= b2q_linear_workspace_bytes(M, N, K) &&
                       force != 3;
     ua.out_bf16 = ua.bf16;
     if (prep) {
@@ -132,6 +152,8 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
       int rc = act_prep(x, act_dtype == B2Q_BF16, ldx, nullptr, 1, workspace, inv, M, (int)K, perm, st);
       if (rc) return rc;
       ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.tok_scale = inv; ua.magic = true;
+      rc = plan_split(ua, workspace, M, N, K, 4, st);
+      if (rc) return rc;
     }
     return umma_w4_linear(ua, st);
   }
@@ -146,10 +168,10 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   return smallm_int4(p, act_dtype == B2Q_BF16, (int)M, 0, st);
 }
 
-size_t b2q_linear_workspace_bytes(int64_t M, int64_t K) {
-  return align_up((size_t)M * (size_t)K * 2, 256) + align_up((size_t)M * 4, 256);
+size_t b2q_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  return ws_prep_bytes(M, K) + (M <= 64 ? align_up((size_t)M * (size_t)N * 4, 256) : 0);
 }
-size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t K) { return b2q_linear_workspace_bytes(M, K); }
+size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K) { return b2q_linear_workspace_bytes(M, N, K); }
 
 int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
                    int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
@@ -174,8 +196,9 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
   ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
   const bool umma_ok = umma_w8_supported(ua);
   // bf16 activations + scratch: convert them once to per-token-scaled fp16 so the weight decode is one cvt per pair
-  const bool prep = act_dtype == B2Q_BF16 && workspace && aligned16(workspace) &&
-                    workspace_bytes >= b2q_linear_fp8_workspace_bytes(M, K) && (K % 8) == 0 && force != 3;
+  const bool have_ws = workspace && aligned16(workspace) && workspace_bytes >= b2q_linear_workspace_bytes(M, N, K) &&
+                       force != 3;
+  const bool prep = act_dtype == B2Q_BF16 && have_ws && (K % 8) == 0;
   const bool want_umma = force == 2 || force == 3 || (force == 0 && (M > 4 || prep || act_dtype == B2Q_F16));
   if (umma_ok && want_umma) {
     if (prep) {
@@ -183,6 +206,10 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
       int rc = act_prep(x, true, ldx, nullptr, 1, workspace, inv, M, (int)K, 0, st);
       if (rc) return rc;
       ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.out_bf16 = true; ua.tok_scale = inv;
+    }
+    if (have_ws) {
+      const int rc = plan_split(ua, workspace, M, N, K, 2, st);
+      if (rc) return rc;
     }
     return umma_w8_linear(ua, st);
   }

@@ -51,6 +51,8 @@ struct UmmaWoParams {
   void* out; int64_t ldo;
   int M, N, K;
   int marlin; uint32_t xor_mask; int e5m2;
+  int split_k, chunks_per_split;   // split-K over blockIdx.z (dense decode only)
+  float* split_acc;          // fp32 [M, N] accumulation buffer for split-K (zeroed by the host side)
   int magic;                 // INT4: fp16 magic-number transform; x was permuted / scaled by the pre-pass
   const int32_t* tiles; const int32_t* expert_offsets; const int32_t* out_map;
   int w_rows_per_expert;     // tensor-map rows per expert: N (N-major) or K/8 (K-major)
@@ -213,7 +215,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     M = p.expert_offsets[expert + 1] - xrow0;
   }
   const int n0 = blockIdx.y * 128;
-  const int nk = p.K / 64;
+  // split-K: blockIdx.z owns a contiguous range of 64-k chunks (a multiple of the raw stage size)
+  const int c_begin = p.split_k > 1 ? (int)blockIdx.z * p.chunks_per_split : 0;
+  const int c_stop = p.split_k > 1 ? min(p.K / 64, c_begin + p.chunks_per_split) : p.K / 64;
+  const int nk = c_stop - c_begin;
   const int64_t sbase = (int64_t)expert * p.s_expert_elems;
 
   if (threadIdx.x == 0) {
@@ -241,9 +246,9 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         { PROF_T0; if (r >= RS && !mbar_wait(raw_empty + 8 * rs, ((r / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) break; PROF_ADD(0); }
         mbar_expect_tx(raw_full + 8 * rs, Cfg::RAW_BYTES);
         if constexpr (WK == WK_W4K)
-          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, n0, expert * p.w_rows_per_expert + r * 32, raw_full + 8 * rs);
+          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, n0, expert * p.w_rows_per_expert + (c_begin / CPR + r) * 32, raw_full + 8 * rs);
         else
-          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, r * 128, expert * p.w_rows_per_expert + n0, raw_full + 8 * rs);
+          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, (c_begin / CPR + r) * 128, expert * p.w_rows_per_expert + n0, raw_full + 8 * rs);
       }
       PROF_FLUSH(12);
     }
@@ -256,7 +261,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int s = c % XS;
         { PROF_T0; if (c >= XS && !mbar_wait(x_empty + 8 * s, ((c / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break; PROF_ADD(0); }
         mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
-        tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, c * 64, xrow0 + tok0, x_full + 8 * s);
+        tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, (c_begin + c) * 64, xrow0 + tok0, x_full + 8 * s);
       }
       PROF_FLUSH(16);
     }
@@ -328,7 +333,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         PROF_T0;
         if constexpr (WK == WK_W4N || WK == WK_W4K) {
           uint32_t s2 = 0; float sf = 0.f;
-          const int64_t si = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)(c >> 1) * p.s_stride_g;
+          const int64_t si = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)((c_begin + c) >> 1) * p.s_stride_g;
           if constexpr (FAST) { if (!p.magic) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si]; s2 = sv | (sv << 16); } }
           else sf = load_scalar(p.scale, si, p.scale_dtype);
           uint32_t ww[8];
@@ -373,7 +378,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           for (int c4 = 0; c4 < 4; ++c4) rv[c4] = lds128(rawrow + (((4 * j + c4) ^ sw) << 4));
           uint32_t (&o)[32] = av;
           if (blockscale) {
-            const float sf = reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * kblocks + (c >> 1)];
+            const float sf = reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * kblocks + ((c_begin + c) >> 1)];
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
               w8_word<BF16, true>(rv[c4].x, p.e5m2, sf, o[8 * c4 + 0], o[8 * c4 + 1]);
@@ -458,6 +463,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               if (p.out_map) orow = p.out_map[orow];
               float v = __uint_as_float(r[i]) * post;
               if (p.tok_scale) v *= p.tok_scale[xrow0 + tok];
+              if (p.split_acc) { atomicAdd(p.split_acc + (int64_t)(xrow0 + tok) * p.N + n, v); continue; }
               outp[orow * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
                                                   : __half_as_ushort(__float2half_rn(v));
             }
@@ -535,6 +541,44 @@ extern "C" __attribute__((visibility("default"))) int b2q_debug_prof(long long* 
 }
 #endif
 
+// out[m, n] = round(acc[m, n]) after a split-K launch
+__global__ void splitk_finalize_kernel(const float* __restrict__ acc, uint16_t* __restrict__ out, int64_t ldo, int M, int N,
+                                       int out_bf16) {
+  const int64_t total = (int64_t)M * N;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / N, n = i % N;
+    const float v = acc[i];
+    out[m * ldo + n] = out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+  }
+}
+
+// Picks the number of K splits for a decode-shaped launch so that (strips x splits) fills whole waves of
+// the two-CTAs-per-SM grid; returns 1 when splitting does not pay.  cps_out = chunks per split.
+int umma_plan_split_k(int N, int K, int chunks_per_raw, int* cps_out) {
+  static thread_local int sms = 0;
+  if (!sms) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms <= 0) sms = 148;
+  }
+  const int slots = 2 * sms, strips = (N + 127) / 128, nk = K / 64;
+  int best = 1, best_cps = nk;
+  double best_eff = (double)strips / ((double)((strips + slots - 1) / slots) * slots);
+  // every extra CTA pays a pipeline fill and an atomic epilogue: split only when most of the machine would idle
+  if (best_eff >= 0.6) { *cps_out = nk; return 1; }
+  for (int sk = 2; sk <= 16; ++sk) {
+    int cps = (nk + sk - 1) / sk;
+    cps = (cps + chunks_per_raw - 1) / chunks_per_raw * chunks_per_raw;
+    if (cps < 8 || (sk - 1) * cps >= nk) continue;
+    const int items = strips * sk;
+    const double eff = (double)items / ((double)((items + slots - 1) / slots) * slots);
+    if (eff > best_eff + 0.04) { best_eff = eff; best = sk; best_cps = cps; }
+  }
+  *cps_out = best_cps;
+  return best;
+}
+
 static int pick_tok(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256))); }
 
 template <int WK, bool BF16, int TOK, bool FAST>
@@ -548,7 +592,7 @@ static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWo
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return B2Q_ERR_CUDA;
     if (dev < 16) configured[dev] = true;
   }
-  dim3 grid(token_tiles, (p.N + 127) / 128, 1);
+  dim3 grid(token_tiles, (p.N + 127) / 128, p.split_k > 1 ? p.split_k : 1);
   kern<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(tw, tx, p);
   note_launch("umma_wo");
   return launch_status();
@@ -575,6 +619,15 @@ static int launch_wk(bool bf16, bool fast, int tok, const CUtensorMap& tw, const
 static int grouped_tok(int rows, int E) {
   const int avg = E > 0 ? (rows + E - 1) / E : rows;
   return avg <= 16 ? 16 : (avg <= 32 ? 32 : (avg <= 96 ? 64 : 128));
+}
+
+static int splitk_finalize(const float* acc, void* out, int64_t ldo, int M, int N, bool out_bf16, cudaStream_t st) {
+  const int64_t total = (int64_t)M * N;
+  int64_t g = (total + 255) / 256;
+  if (g > 148 * 8) g = 148 * 8;
+  splitk_finalize_kernel<<<(int)g, 256, 0, st>>>(acc, reinterpret_cast<uint16_t*>(out), ldo, M, N, out_bf16 ? 1 : 0);
+  note_launch("splitk_finalize");
+  return launch_status();
 }
 
 bool umma_w4_supported(const UmmaW4Args& a) {
@@ -615,10 +668,13 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.w_rows_per_expert = kmajor ? a.K / 8 : a.N;
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0; p.magic = a.magic ? 1 : 0;
   p.status = status_ptr();
+  p.split_k = a.split_k; p.chunks_per_split = a.chunks_per_split; p.split_acc = a.split_k > 1 ? a.split_acc : nullptr;
   const bool fast = a.magic || (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
-  return kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)
-                : launch_wk<WK_W4N>(a.bf16, fast, tok, tw, tx, p, tiles, st);
+  rc = kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)
+              : launch_wk<WK_W4N>(a.bf16, fast, tok, tw, tx, p, tiles, st);
+  if (rc || !p.split_acc) return rc;
+  return splitk_finalize(p.split_acc, a.out, a.ldo, a.M, a.N, a.out_bf16, st);
 }
 
 bool umma_w8_supported(const UmmaW8Args& a) {
@@ -650,8 +706,11 @@ int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st) {
   p.w_rows_per_expert = a.N;
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0;
   p.status = status_ptr();
+  p.split_k = a.split_k; p.chunks_per_split = a.chunks_per_split; p.split_acc = a.split_k > 1 ? a.split_acc : nullptr;
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
-  return launch_wk<WK_W8>(a.bf16, true, tok, tw, tx, p, tiles, st);
+  rc = launch_wk<WK_W8>(a.bf16, true, tok, tw, tx, p, tiles, st);
+  if (rc || !p.split_acc) return rc;
+  return splitk_finalize(p.split_acc, a.out, a.ldo, a.M, a.N, a.out_bf16, st);
 }
 
 int umma_w8a8_block(const UmmaW8A8Args&, cudaStream_t) { return B2Q_ERR_UNSUPPORTED; }

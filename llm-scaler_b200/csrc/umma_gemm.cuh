@@ -14,6 +14,9 @@ struct UmmaGroupArgs {
   const int32_t* tiles = nullptr;           // device tile list {n, pad3, int2...}
   int tile_cap = 0;
   int64_t s_expert_elems = 0;
+  // split-K (dense decode shapes only): fp32 [M, N] buffer zeroed by the caller, see umma_plan_split_k
+  int split_k = 1, chunks_per_split = 0;
+  float* split_acc = nullptr;
 };
 
 struct UmmaW4Args : UmmaGroupArgs {
@@ -50,6 +53,8 @@ int umma_w8_token_tile(const UmmaW8Args& a);
 int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st);
 
 int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st);
+
+int umma_plan_split_k(int N, int K, int chunks_per_raw, int* cps_out);
 
 // First device-side wait timeout recorded since the library was loaded (0 = none).  Synchronises.
 int umma_read_status(int* out);

@@ -70,7 +70,7 @@ def linear_int4(input, weight, weight_scale, output):
         ws, wsb = None, 0
         if M > 8 or layout != L.W4_NMAJOR:
             # scratch for the activation pre-pass of the tensor-core kernel (caching allocator, no cudaMalloc)
-            wsb = L.lib.b2q_linear_workspace_bytes(M, K)
+            wsb = L.lib.b2q_linear_workspace_bytes(M, N, K)
             ws = torch.empty(wsb, dtype=torch.uint8, device=input.device)
         L.check(L.lib.b2q_linear_int4(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else K,
                                        wt.data_ptr(), layout, weight_scale.data_ptr(), L.dt(weight_scale), sn, sg,
@@ -120,9 +120,9 @@ def linear_fp8(input, weight, weight_scale, output, scale_mode, N=None, K=None):
         _chk(tuple(weight_scale.shape) == ((wn + 127) // 128, (wk + 127) // 128), "block scale shape mismatch")
     with L.on_device(input):
         ws, wsb = None, 0
-        if input.dtype == torch.bfloat16:
-            # scratch for the activation pre-pass (torch's caching allocator: no cudaMalloc in steady state)
-            wsb = L.lib.b2q_linear_fp8_workspace_bytes(M, wk)
+        if input.dtype == torch.bfloat16 or M <= 64:
+            # scratch for the activation pre-pass / split-K accumulator (torch's caching allocator: no cudaMalloc in steady state)
+            wsb = L.lib.b2q_linear_workspace_bytes(M, wn, wk)
             ws = torch.empty(wsb, dtype=torch.uint8, device=input.device)
         L.check(L.lib.b2q_linear_fp8(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else wk,
                                       weight.data_ptr(), L.fp8_fmt(weight), weight_scale.data_ptr(),

@@ -75,7 +75,7 @@ def test_workspace_size_queries(lib_built):
     big = L.lib.b2q_moe_gemm_workspace_bytes(1024, 8, 256, 512, 1, 0)
     assert big >= small + 1024 * 256 * 2
     assert small >= 1024 * 512 * 2 + 1024 * 4          # staged activations + per-row scales are always there
-    assert L.lib.b2q_linear_workspace_bytes(64, 8192) >= 64 * 8192 * 2 + 64 * 4
+    assert L.lib.b2q_linear_workspace_bytes(64, 1024, 8192) >= 64 * 8192 * 2 + 64 * 4 + 64 * 1024 * 4
 
 
 def test_ops_refuse_cpu_tensors(lib_built):

@@ -37,7 +37,7 @@ def test_int4_nmajor(e, M, N, K, dtype):
     ref = int4.linear(x, q, s)
     out = torch.empty(M, N, dtype=dtype, device=DEV)
     e.esimd_gemm_int4_pgrp(x.to(DEV), int4.pack_nmajor_i32(q).to(DEV), s.to(DEV), out)
-    assert e.last_kernel() == "umma_wo"
+    assert e.last_kernel() in ("umma_wo", "splitk_finalize")
     assert_close(out, ref, what=f"umma int4 M={M} N={N} K={K}")
 
 
@@ -91,7 +91,7 @@ def test_fp8_channel_tensor(e, M, N, K, dtype):
     wq, s = fp8.quantize_channel(w)
     out = torch.empty(M, N, dtype=dtype, device=DEV)
     e.esimd_gemv_fp8_pern(x.to(DEV), wq.to(DEV), s.to(DEV), out, N, K)
-    assert e.last_kernel() == "umma_wo"
+    assert e.last_kernel() in ("umma_wo", "splitk_finalize")
     assert_close(out, fp8.linear_channel(x, wq, s), what="umma fp8 channel")
     wq, st = fp8.quantize_tensor(w)
     e.esimd_gemm_fp8_pert(x.to(DEV), wq.to(DEV), st.to(DEV), out)
@@ -132,7 +132,7 @@ def test_grouped_int4_and_fp8(e, rows):
     q = torch.randint(0, 16, (E, N, K), generator=g, dtype=torch.uint8)
     s = (0.002 + torch.randn(E, N, K // 128, generator=g).abs() * 0.01).half()
     out = e.moe_gemm_int4_nmajor(x.to(DEV), int4.pack_nmajor_i32(q).to(DEV), s.to(DEV), off.to(DEV), 128)
-    assert e.last_kernel() == "umma_wo"
+    assert e.last_kernel() in ("umma_wo", "splitk_finalize")
     assert_close(out, moe.grouped_linear(x, int4.dequant(q, s, torch.float16), off), what="umma grouped int4")
     wq, ws = fp8.quantize_block(torch.randn(E, N, K, generator=g) * 0.15)
     o8 = torch.empty(total, N, dtype=torch.float16, device=DEV)
