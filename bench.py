@@ -131,18 +131,21 @@ def run_b200(args):
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    # clocks / throttle reasons are sampled from here to the end of the end-to-end loop: the timed region
+    # itself lasts a few milliseconds, too short for nvidia-smi, and everything in this window is the same load
+    cs = ClockSampler(torch.cuda.current_device())
+    cs.__enter__()
     for i in range(max(args.warmup, 3)):
         step(i)
     barrier()
     launches0 = e.launch_count()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(torch.cuda.current_device()) as cs:
-        barrier()
-        ev0.record()
-        for i in range(args.steps):
-            step(i)
-        ev1.record()
-        barrier()
+    barrier()
+    ev0.record()
+    for i in range(args.steps):
+        step(i)
+    ev1.record()
+    barrier()
     ms = ev0.elapsed_time(ev1)
     launches = e.launch_count() - launches0
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
@@ -192,6 +195,14 @@ def run_b200(args):
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     e2e_value = world * step_bytes * args.steps / float(t.item()) / 1e9
+    # keep the GPU under the same load for a moment so that the sampler sees it, then stop sampling
+    t_end = time.perf_counter() + 1.0
+    i = 0
+    while time.perf_counter() < t_end:
+        step(i)
+        i += 1
+    torch.cuda.synchronize()
+    cs.__exit__(None, None, None)
 
     peaks, peak_kind = measured_peaks()
     achieved = step_bytes * args.steps / (ms * 1e-3) / 1e9      # this rank's kernels only

@@ -526,10 +526,14 @@ static int* status_ptr() {
   return ptr[dev];
 }
 
+int w8a8_read_status(int* out);
+
 int umma_read_status(int* out) {
   int* p = status_ptr();
   if (!p) return B2Q_ERR_CUDA;
-  return cuda_status(cudaMemcpy(out, p, sizeof(int), cudaMemcpyDeviceToHost));
+  int rc = cuda_status(cudaMemcpy(out, p, sizeof(int), cudaMemcpyDeviceToHost));
+  if (rc || *out) return rc;
+  return w8a8_read_status(out);
 }
 
 #ifdef B2Q_UMMA_PROF
@@ -713,6 +717,5 @@ int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st) {
   return splitk_finalize(p.split_acc, a.out, a.ldo, a.M, a.N, a.out_bf16, st);
 }
 
-int umma_w8a8_block(const UmmaW8A8Args&, cudaStream_t) { return B2Q_ERR_UNSUPPORTED; }
 
 }  // namespace b2q

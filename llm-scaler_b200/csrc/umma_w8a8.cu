@@ -1,0 +1,199 @@
+// W8A8 block-scaled FP8 GEMM on tcgen05:  out[tok, n] = sum_kb xs[tok, kb] * ws[n/128, kb] * (xq[tok, kb-block] . wq[n, kb-block]).
+//
+// Both operands are e4m3 and go from TMA straight into the tensor core (kind::f8f6f4, K = 32 per
+// instruction); nothing is dequantised in shared memory.  The hardware block-scaling MMA only takes
+// power-of-two scales, while these scales are arbitrary fp32 (amax / 448), so every 128-deep K block is
+// accumulated into its own tensor-memory buffer and promoted by the epilogue warps:
+// acc[n, tok] += partial[n, tok] * xs[tok, kb] * ws[n/128, kb] in fp32 registers, while the MMA already
+// works on the next K blocks (four accumulator buffers rotate through the 512 TMEM columns).
+// The 128 weight rows of a strip are the MMA's M dimension, a 128-token tile its N dimension, so
+// ws is one scalar per (CTA, kb) and the scale varies only along the columns a thread owns.
+//
+// Reference counterpart: the block-scaled linear of vllm/patches/vllm_for_multi_arc.patch:2651-2691 with the
+// (1,128) dynamic activation quantisation its capability key asks for (:2628-2634); the reference itself
+// keeps the activation in 16 bit, which b2q_linear_fp8 reproduces.
+#include "umma_gemm.cuh"
+#include "sm100.cuh"
+
+namespace b2q {
+
+using namespace sm100;
+
+__device__ int g_w8a8_status = 0;
+
+namespace w8a8 {
+constexpr int TOK = 128;            // token tile (MMA N)
+constexpr int S = 4;                // operand stages: one K block of W (16 KB) + one of X (16 KB) each
+constexpr int NBUF = 4;             // accumulator buffers of TOK columns
+constexpr int THREADS = 64 + 256;   // TMA warp, MMA warp, 8 promotion / epilogue warps
+constexpr int STAGE_BYTES = 2 * 16384;
+constexpr int MAX_KB = 128;         // K <= 16384
+enum { ST_FULL = 201, ST_EMPTY = 202, ST_ACCFULL = 203, ST_ACCEMPTY = 204 };
+}  // namespace w8a8
+
+struct W8A8Params {
+  const float* xs; const float* ws;     // [M, K/128], [ceil(N/128), K/128]
+  void* out; int64_t ldo; int out_bf16;
+  int M, N, K;
+  int* status;
+};
+
+__global__ void __launch_bounds__(w8a8::THREADS, 1)
+umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const W8A8Params p) {
+  using namespace w8a8;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
+  const int nkb = p.K >> 7;
+  // layout: [S stages of (W tile, X tile)] [scale table nkb x TOK fp32] [barriers]
+  const uint32_t sc_off = S * STAGE_BYTES;
+  float* sc = reinterpret_cast<float*>(gen + sc_off);
+  const uint32_t bar = base + sc_off + MAX_KB * TOK * 4;
+  const uint32_t full = bar, empty = bar + 8 * S, acc_full = bar + 16 * S, acc_empty = acc_full + 8 * NBUF;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (acc_empty + 8 * NBUF - base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + (acc_empty + 8 * NBUF + 8 - base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tok0 = blockIdx.x * TOK, n0 = blockIdx.y * 128;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) { mbar_init(full + 8 * i, 1); mbar_init(empty + 8 * i, 1); }
+    for (int i = 0; i < NBUF; ++i) { mbar_init(acc_full + 8 * i, 1); mbar_init(acc_empty + 8 * i, 256); }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512); tmem_relinquish(); }
+  // combined scale table: sc[kb][t] = xs[tok0 + t, kb] * ws[n0 / 128, kb]
+  for (int i = threadIdx.x; i < nkb * TOK; i += THREADS) {
+    const int t = i % TOK, kb = i / TOK;        // kb-major in smem
+    const int tok = tok0 + t;
+    sc[i] = tok < p.M ? p.xs[(int64_t)tok * nkb + kb] * p.ws[(int64_t)(n0 >> 7) * nkb + kb] : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_w);
+      tma_prefetch_desc(&tm_x);
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % S;
+        if (kb >= S && !mbar_wait(empty + 8 * s, ((kb / S) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break;
+        mbar_expect_tx(full + 8 * s, STAGE_BYTES);
+        tma_load_2d(base + s * STAGE_BYTES, &tm_w, kb * 128, n0, full + 8 * s);
+        tma_load_2d(base + s * STAGE_BYTES + 16384, &tm_x, kb * 128, tok0, full + 8 * s);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc(0u, 0u, 128, TOK);       // e4m3 x e4m3 -> fp32
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % S, b = kb % NBUF;
+        if (!mbar_wait(full + 8 * s, (kb / S) & 1, abort_flag, p.status, ST_FULL)) break;
+        if (kb >= NBUF && !mbar_wait(acc_empty + 8 * b, ((kb / NBUF) - 1) & 1, abort_flag, p.status, ST_ACCEMPTY)) break;
+        tc_fence_after();
+        const uint64_t da = smem_desc_sw128(base + s * STAGE_BYTES);
+        const uint64_t db = smem_desc_sw128(base + s * STAGE_BYTES + 16384);
+        const uint32_t d = tmem + b * TOK;
+        mma_f8(d, da, db, idesc, 0u);
+        mma_f8(d, da + 2, db + 2, idesc, 1u);
+        mma_f8(d, da + 4, db + 4, idesc, 1u);
+        mma_f8(d, da + 6, db + 6, idesc, 1u);
+        tc_commit(empty + 8 * s);
+        tc_commit(acc_full + 8 * b);
+      }
+    }
+  } else {
+    // ---- promotion + epilogue: 8 warps, quadrant = warp & 3, column half = (warp - 2) >> 2 ----
+    const int quad = warp & 3, half = (warp - 2) >> 2;
+    const int col0 = half * 64;
+    float acc[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    bool ok = true;
+#pragma unroll 1
+    for (int kb = 0; kb < nkb; ++kb) {
+      const int b = kb % NBUF;
+      ok = mbar_wait(acc_full + 8 * b, (kb / NBUF) & 1, abort_flag, p.status, ST_ACCFULL);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      const uint32_t ta = tmem + ((uint32_t)(quad * 32) << 16) + b * TOK + col0;
+      tmem_ld32(ta, r0);
+      tmem_ld32(ta + 32, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(acc_empty + 8 * b);           // the buffer may be overwritten while the FMAs run
+      const float4* s4 = reinterpret_cast<const float4*>(sc + kb * TOK + col0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 v = s4[i];
+        acc[4 * i + 0] = fmaf(__uint_as_float(r0[4 * i + 0]), v.x, acc[4 * i + 0]);
+        acc[4 * i + 1] = fmaf(__uint_as_float(r0[4 * i + 1]), v.y, acc[4 * i + 1]);
+        acc[4 * i + 2] = fmaf(__uint_as_float(r0[4 * i + 2]), v.z, acc[4 * i + 2]);
+        acc[4 * i + 3] = fmaf(__uint_as_float(r0[4 * i + 3]), v.w, acc[4 * i + 3]);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float4 v = s4[8 + i];
+        acc[32 + 4 * i + 0] = fmaf(__uint_as_float(r1[4 * i + 0]), v.x, acc[32 + 4 * i + 0]);
+        acc[32 + 4 * i + 1] = fmaf(__uint_as_float(r1[4 * i + 1]), v.y, acc[32 + 4 * i + 1]);
+        acc[32 + 4 * i + 2] = fmaf(__uint_as_float(r1[4 * i + 2]), v.z, acc[32 + 4 * i + 2]);
+        acc[32 + 4 * i + 3] = fmaf(__uint_as_float(r1[4 * i + 3]), v.w, acc[32 + 4 * i + 3]);
+      }
+    }
+    if (ok) {
+      const int n = n0 + quad * 32 + lane;
+      if (n < p.N) {
+        uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int tok = tok0 + col0 + i;
+          if (tok < p.M)
+            outp[(int64_t)tok * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(acc[i]))
+                                                        : __half_as_ushort(__float2half_rn(acc[i]));
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
+}
+
+int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st) {
+  using namespace w8a8;
+  if ((a.K % 128) != 0 || a.K / 128 > MAX_KB) return B2Q_ERR_SHAPE;
+  if (!tensor_map_encoder()) return B2Q_ERR_CUDA;
+  CUtensorMap tw, tx;
+  int rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, a.N, a.K, (uint64_t)a.K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, a.M, a.K, (uint64_t)a.K, TOK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
+  W8A8Params p{};
+  p.xs = a.xs; p.ws = a.ws; p.out = a.out; p.ldo = a.ldo; p.out_bf16 = a.bf16 ? 1 : 0;
+  p.M = a.M; p.N = a.N; p.K = a.K;
+  void* sym = nullptr;
+  if (cudaGetSymbolAddress(&sym, g_w8a8_status) != cudaSuccess) return B2Q_ERR_CUDA;
+  p.status = reinterpret_cast<int*>(sym);
+  constexpr int SMEM = S * STAGE_BYTES + MAX_KB * TOK * 4 + 1024 + 256;
+  static thread_local bool configured[16] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || !configured[dev]) {
+    if (cudaFuncSetAttribute(umma_w8a8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return B2Q_ERR_CUDA;
+    if (dev < 16) configured[dev] = true;
+  }
+  dim3 grid((a.M + TOK - 1) / TOK, (a.N + 127) / 128, 1);
+  umma_w8a8_kernel<<<grid, THREADS, SMEM, st>>>(tw, tx, p);
+  note_launch("umma_w8a8");
+  return launch_status();
+}
+
+int w8a8_read_status(int* out) {
+  return cuda_status(cudaMemcpyFromSymbol(out, g_w8a8_status, sizeof(int)));
+}
+
+}  // namespace b2q

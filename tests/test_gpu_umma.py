@@ -152,3 +152,19 @@ def test_moe_prefill_ops_with_ipex_kmajor_marlin_weights(e):
     out = e.moe_prefill_full_int4(c["x"].to(DEV), c["logits"].to(DEV), w13.to(DEV), s13.to(DEV), w2.to(DEV), s2.to(DEV), 2, 8)
     # three 16-bit roundings sit between the stages, hence the wider gate for the whole pipeline
     assert_close(out, ref.float(), tol=3e-2, what="moe kmajor marlin")
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 384, 512), (1000, 1000, 1024), (64, 256, 5120)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_fp8_block_w8a8(e, M, N, K, dtype):
+    """e4m3 x e4m3 tensor cores with per-128-block fp32 promotion, against dq(Aq, As) @ dq(Wq, Ws).T."""
+    g = torch.Generator().manual_seed(M + N + K)
+    wq, ws = fp8.quantize_block(torch.randn(N, K, generator=g) * 0.02)
+    x = torch.randn(M, K, generator=g).to(dtype)
+    xq, xs = e.act_quant_fp8_1x128(x.to(DEV))
+    rq, rs = fp8.quantize_act_1x128(x)
+    assert torch.equal(xq.cpu().view(torch.uint8), rq.view(torch.uint8)) and torch.equal(xs.cpu(), rs)
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    e.gemm_fp8_block_w8a8(xq, xs, wq.to(DEV), ws.to(DEV), out)
+    assert e.last_kernel() == "umma_w8a8"
+    assert_close(out, fp8.linear_block_w8a8(rq, rs, wq, ws), what=f"w8a8 M={M} N={N} K={K}")
