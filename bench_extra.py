@@ -1,9 +1,11 @@
-"""Device-timed figures for the benchmark configurations other than the headline one (bench.py --extra).
+"""Device-timed figures for the benchmark configurations other than the headline one.
 
-Each entry reports the quantity the configuration is judged on: weight GB/s for decode shapes,
-TFLOP/s for prefill shapes, tokens/s for the MoE pipeline and the decoder stack, with the measured
-roofline fraction beside it.  Synthetic seeded data; weights rotate over copies larger than L2 where
-one copy would fit in it.
+    python bench.py --extra            all cases, appended to the bench line under "extra"
+    python bench.py --case c5_m64      one case alone (small enough to profile), printed as one JSON line
+
+Each case reports the quantity its configuration is judged on: weight GB/s for decode shapes, TFLOP/s for
+prefill shapes, tokens/s for the MoE pipeline and the decoder layer, with the measured roofline fraction
+beside it.  Synthetic seeded data; weights rotate over copies larger than L2 where one copy would fit in it.
 """
 import json
 import os
@@ -34,78 +36,91 @@ def _time(fn, reps, warm=3):
 
 
 def _int4(N, K, dev, g, copies=1, lead=()):
-    ws = [torch.randint(-2 ** 31, 2 ** 31 - 1, (*lead, N, K // 8), generator=g, device=dev, dtype=torch.int32) for _ in range(copies)]
+    ws = [torch.randint(-2 ** 31, 2 ** 31 - 1, (*lead, N, K // 8), generator=g, device=dev, dtype=torch.int32)
+          for _ in range(copies)]
     s = (0.002 + torch.randn(*lead, N, K // 128, generator=g, device=dev).abs() * 0.01).to(torch.bfloat16)
     return ws, s
 
 
-def run(e, dev):
-    pk = _peaks()
-    hbm, tf = pk["hbm_gbs"], pk["bf16_tflops"]
-    g = torch.Generator(device=dev).manual_seed(7)
-    out = {}
+def case_c1(e, dev, g, pk):
+    """C1: INT4 linear M=16, K=N=4096 (8.9 MB per launch: launch-latency dominated)."""
     op4 = torch.ops.custom_esimd_kernels_vllm.esimd_gemm_int4_pgrp
-
-    # ---- C1: INT4 linear M=16, K=N=4096 (8.9 MB per launch: launch-latency dominated) ----
     N = K = 4096
     ws, s = _int4(N, K, dev, g, copies=32)                       # 32 x 8.4 MB > 2 x L2
     x = torch.randn(16, K, generator=g, device=dev).to(torch.bfloat16)
     o = torch.empty(16, N, dtype=torch.bfloat16, device=dev)
     us = _time(lambda i: op4(x, ws[i % 32], s, o), 64)
     byts = N * K // 2 + N * (K // 128) * 2 + 16 * K * 2 + 16 * N * 2
-    out["c1_int4_m16_4096"] = {"us": round(us, 2), "GBps": round(byts / us / 1e3, 1), "hbm_frac": round(byts / us / 1e3 / hbm, 3),
-                               "kernel": e.last_kernel()}
-    del ws
+    return {"us": round(us, 2), "GBps": round(byts / us / 1e3, 1), "hbm_frac": round(byts / us / 1e3 / pk["hbm_gbs"], 3),
+            "kernel": e.last_kernel()}
 
-    # ---- C3: FP8 128x128 block GEMM, M=4096, N=17408, K=5120, reference semantics (activation stays 16 bit) ----
-    M, N, K = 4096, 17408, 5120
+
+def _c3_weights(dev, g, M, N, K):
     w = (torch.randn(N, K, generator=g, device=dev) * 0.02)
     blk = w.reshape(N // 128, 128, K // 128, 128)
     wsc = (blk.abs().amax(dim=(1, 3)).clamp(min=1e-12) / 448.0).float().contiguous()
     wq = (blk / wsc[:, None, :, None]).reshape(N, K).to(torch.float8_e4m3fn).contiguous()
-    del w, blk
     x = torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16)
+    return wq, wsc, x
+
+
+def case_c3_w8a16(e, dev, g, pk):
+    """C3 with the reference's semantics: 128x128 block-scaled e4m3 weights, activation kept in 16 bit."""
+    M, N, K = 4096, 17408, 5120
+    wq, wsc, x = _c3_weights(dev, g, M, N, K)
     o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     us = _time(lambda i: torch.ops.custom_esimd_kernels_vllm.esimd_gemm_fp8_blockscale(x, wq, wsc, o, 128, 128), 5, warm=2)
     fl = 2.0 * M * N * K
-    out["c3_fp8_block_m4096"] = {"us": round(us, 1), "TFLOPs": round(fl / us / 1e6, 1), "bf16_peak_frac": round(fl / us / 1e6 / tf, 3),
-                                 "semantics": "w8a16: the reference path keeps the activation in 16 bit", "kernel": e.last_kernel()}
-    # the configuration as BASELINE states it: activations quantised per token per 128 columns, e4m3 x e4m3 MMA
+    return {"us": round(us, 1), "TFLOPs": round(fl / us / 1e6, 1), "bf16_peak_frac": round(fl / us / 1e6 / pk["bf16_tflops"], 3),
+            "kernel": e.last_kernel()}
+
+
+def case_c3_w8a8(e, dev, g, pk):
+    """C3 as BASELINE states it: activations quantised per token per 128 columns, e4m3 x e4m3 MMA."""
+    M, N, K = 4096, 17408, 5120
+    wq, wsc, x = _c3_weights(dev, g, M, N, K)
+    o = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
     xq, xsc = e.act_quant_fp8_1x128(x)
+    fl = 2.0 * M * N * K
     us8 = _time(lambda i: e.gemm_fp8_block_w8a8(xq, xsc, wq, wsc, o), 5, warm=2)
     usq = _time(lambda i: e.gemm_fp8_block_w8a8(*e.act_quant_fp8_1x128(x), wq, wsc, o), 5, warm=2)
-    out["c3_fp8_block_w8a8_m4096"] = {"us_gemm": round(us8, 1), "TFLOPs_gemm": round(fl / us8 / 1e6, 1),
-                                      "us_with_act_quant": round(usq, 1), "TFLOPs_with_act_quant": round(fl / usq / 1e6, 1),
-                                      "fp8_peak_frac_vs_2x_bf16": round(fl / us8 / 1e6 / (2 * tf), 3), "kernel": e.last_kernel()}
-    del wq, x, o, xq, xsc
+    return {"us_gemm": round(us8, 1), "TFLOPs_gemm": round(fl / us8 / 1e6, 1), "us_with_act_quant": round(usq, 1),
+            "TFLOPs_with_act_quant": round(fl / usq / 1e6, 1),
+            "fp8_peak_frac": round(fl / us8 / 1e6 / (2 * pk["bf16_tflops"]), 3),
+            "fp8_peak": "2 x measured bf16 burst peak (no measured fp8 entry in MEASURED_PEAKS.json)", "kernel": e.last_kernel()}
 
-    # ---- C5: Llama-70B-shape layer, INT4, single GPU, decode M=64 and prefill M=2048 ----
-    shapes = {"qkv": (10240, 8192), "o": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}
-    layer = {n: _int4(N_, K_, dev, g, copies=1) for n, (N_, K_) in shapes.items()}
-    wbytes = sum(N_ * K_ // 2 + N_ * (K_ // 128) * 2 for N_, K_ in shapes.values())
-    params = sum(N_ * K_ for N_, K_ in shapes.values())
-    for M in (64, 2048):
-        x = torch.randn(M, 8192, generator=g, device=dev).to(torch.bfloat16)
-        bufs = {n: torch.empty(M, N_, dtype=torch.bfloat16, device=dev) for n, (N_, _) in shapes.items()}
 
-        def layer_fwd(i):
-            op4(x, layer["qkv"][0][0], layer["qkv"][1], bufs["qkv"])
-            attn = bufs["qkv"][:, :8192]
-            op4(attn, layer["o"][0][0], layer["o"][1], bufs["o"])
-            op4(bufs["o"], layer["gate_up"][0][0], layer["gate_up"][1], bufs["gate_up"])
-            act = e._impl.silu_mul(bufs["gate_up"])
-            op4(act, layer["down"][0][0], layer["down"][1], bufs["down"])
+C5_SHAPES = {"qkv": (10240, 8192), "o": (8192, 8192), "gate_up": (57344, 8192), "down": (8192, 28672)}
 
-        us = _time(layer_fwd, 5 if M > 64 else 20, warm=2)        # 428 MB of weights per pass: no L2 residency
-        rec = {"us_per_layer": round(us, 1), "tokens_per_s_80_layers": round(M / (us * 80) * 1e6, 1)}
-        if M == 64:
-            rec.update(GBps=round(wbytes / us / 1e3, 1), hbm_frac=round(wbytes / us / 1e3 / hbm, 3))
-        else:
-            rec.update(TFLOPs=round(2.0 * M * params / us / 1e6, 1), bf16_peak_frac=round(2.0 * M * params / us / 1e6 / tf, 3))
-        out["c5_layer_int4_m%d" % M] = rec
-    del layer
 
-    # ---- C4: INT4 MoE, 128 experts, top-8, H=2048, I=768, T=4096 ----
+def _case_c5(e, dev, g, pk, M):
+    """C5: one Llama-70B-shape decoder layer of INT4 linears on one GPU (attention replaced by the q slice)."""
+    op4 = torch.ops.custom_esimd_kernels_vllm.esimd_gemm_int4_pgrp
+    layer = {n: _int4(N_, K_, dev, g, copies=1) for n, (N_, K_) in C5_SHAPES.items()}
+    wbytes = sum(N_ * K_ // 2 + N_ * (K_ // 128) * 2 for N_, K_ in C5_SHAPES.values())
+    params = sum(N_ * K_ for N_, K_ in C5_SHAPES.values())
+    x = torch.randn(M, 8192, generator=g, device=dev).to(torch.bfloat16)
+    bufs = {n: torch.empty(M, N_, dtype=torch.bfloat16, device=dev) for n, (N_, _) in C5_SHAPES.items()}
+
+    def layer_fwd(i):
+        op4(x, layer["qkv"][0][0], layer["qkv"][1], bufs["qkv"])
+        op4(bufs["qkv"][:, :8192], layer["o"][0][0], layer["o"][1], bufs["o"])
+        op4(bufs["o"], layer["gate_up"][0][0], layer["gate_up"][1], bufs["gate_up"])
+        act = e._impl.silu_mul(bufs["gate_up"])
+        op4(act, layer["down"][0][0], layer["down"][1], bufs["down"])
+
+    us = _time(layer_fwd, 5 if M > 64 else 20, warm=2)            # 428 MB of weights per pass: no L2 residency
+    rec = {"us_per_layer": round(us, 1), "tokens_per_s_80_layers": round(M / (us * 80) * 1e6, 1)}
+    if M <= 64:
+        rec.update(GBps=round(wbytes / us / 1e3, 1), hbm_frac=round(wbytes / us / 1e3 / pk["hbm_gbs"], 3))
+    else:
+        tfl = 2.0 * M * params / us / 1e6
+        rec.update(TFLOPs=round(tfl, 1), bf16_peak_frac=round(tfl / pk["bf16_tflops"], 3))
+    return rec
+
+
+def case_c4(e, dev, g, pk):
+    """C4: INT4 MoE pipeline, 128 experts, top-8, H=2048, I=768, T=4096."""
     T, E, H, I, k = 4096, 128, 2048, 768, 8
     (w13,), s13 = _int4(2 * I, H, dev, g, lead=(E,))
     (w2,), s2 = _int4(H, I, dev, g, lead=(E,))
@@ -113,6 +128,27 @@ def run(e, dev):
     logits = torch.randn(T, E, generator=g, device=dev).to(torch.bfloat16)
     us = _time(lambda i: e.moe_prefill_full_int4(x, logits, w13, s13, w2, s2, k, E), 5, warm=2)
     fl = T * k * (2.0 * H * 2 * I + 2.0 * I * H)
-    out["c4_moe_int4_t4096"] = {"us": round(us, 1), "tokens_per_s": round(T / us * 1e6, 0), "TFLOPs": round(fl / us / 1e6, 1),
-                                "bf16_peak_frac": round(fl / us / 1e6 / tf, 3)}
+    return {"us": round(us, 1), "tokens_per_s": round(T / us * 1e6, 0), "TFLOPs": round(fl / us / 1e6, 1),
+            "bf16_peak_frac": round(fl / us / 1e6 / pk["bf16_tflops"], 3)}
+
+
+CASES = {
+    "c1_int4_m16_4096": case_c1,
+    "c3_fp8_block_w8a16_m4096": case_c3_w8a16,
+    "c3_fp8_block_w8a8_m4096": case_c3_w8a8,
+    "c5_m64": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 64),
+    "c5_m2048": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 2048),
+    "c4_moe_int4_t4096": case_c4,
+}
+
+
+def run(e, dev, only=None):
+    pk = _peaks()
+    out = {}
+    for name, fn in CASES.items():
+        if only is not None and name != only:
+            continue
+        g = torch.Generator(device=dev).manual_seed(7)
+        out[name] = fn(e, dev, g, pk)
+        torch.cuda.empty_cache()
     return out

@@ -235,6 +235,15 @@ B2Q_API int b2q_device_status(int* out);
 /* Kernel selection override for benchmarking: 0 = automatic,
  * 1 = force the mma.sync streaming kernel, 2 = force the tcgen05 kernel.     */
 B2Q_API void b2q_set_force_kernel(int which);
+/* Overlap of consecutive kernels on a stream (programmatic dependent launch), per calling thread:
+ *   0  off: every kernel starts after the one before it has completed.
+ *   1  (default) the activation pre-pass and the GEMM of one call overlap: the GEMM streams and
+ *      converts weights while the pre-pass runs, and waits for it before it reads activations.
+ *   2  additionally declares the weight and scale tensors static: no kernel that precedes a b2q
+ *      call on its stream writes them.  A GEMM may then start streaming weights while the kernels
+ *      before it (the previous layer) are still draining.  Activations, outputs and scratch stay
+ *      fully ordered in every mode.                                             */
+B2Q_API void b2q_set_overlap_mode(int mode);
 /* Name of the kernel family the last b2q_linear_* / b2q_moe_gemm_* call on this
  * thread launched ("smallm", "umma", ...).                                    */
 B2Q_API const char* b2q_last_kernel(void);

@@ -86,6 +86,7 @@ int b2q_device_ok(void) {
 }
 
 void b2q_set_force_kernel(int which) { tls().force_kernel = which; }
+void b2q_set_overlap_mode(int mode) { tls().overlap_mode = mode < 0 ? 0 : (mode > 2 ? 2 : mode); }
 const char* b2q_last_kernel(void) { return tls().last_kernel; }
 uint64_t b2q_launch_count(void) { return tls().launches; }
 
@@ -151,7 +152,7 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
       const int perm = w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1;
       int rc = act_prep(x, act_dtype == B2Q_BF16, ldx, nullptr, 1, workspace, inv, M, (int)K, perm, st);
       if (rc) return rc;
-      ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.tok_scale = inv; ua.magic = true;
+      ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.tok_scale = inv; ua.magic = true; ua.after_prep = true;
       rc = plan_split(ua, workspace, M, N, K, 4, st);
       if (rc) return rc;
     }
@@ -205,7 +206,7 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
       float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * (size_t)K * 2, 256));
       int rc = act_prep(x, true, ldx, nullptr, 1, workspace, inv, M, (int)K, 0, st);
       if (rc) return rc;
-      ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.out_bf16 = true; ua.tok_scale = inv;
+      ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.out_bf16 = true; ua.tok_scale = inv; ua.after_prep = true;
     }
     if (have_ws) {
       const int rc = plan_split(ua, workspace, M, N, K, 2, st);

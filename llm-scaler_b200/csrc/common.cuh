@@ -14,6 +14,7 @@ struct ThreadState {
   uint64_t launches = 0;
   const char* last_kernel = "none";
   int force_kernel = 0;
+  int overlap_mode = 1;      // programmatic dependent launch: 0 off, 1 on, 2 on + weights declared static
 };
 ThreadState& tls();
 
@@ -25,6 +26,26 @@ inline void note_launch(const char* name, int n = 1) {
 
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? B2Q_OK : B2Q_ERR_CUDA; }
 inline int launch_status() { return cuda_status(cudaGetLastError()); }
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// A kernel launched through launch_overlapped may begin while the kernel before it on the stream is
+// still running; it must execute grid_dep_wait() before it touches anything an earlier kernel may have
+// written (and before it writes anything an earlier kernel may still read).  grid_dep_release() lets
+// the next kernel on the stream begin.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool overlap,
+                                     Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int dtype_bytes(int dt) { return dt == B2Q_F32 ? 4 : 2; }

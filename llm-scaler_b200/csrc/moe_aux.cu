@@ -517,9 +517,15 @@ namespace b2q {
 // dst row r = f(src row (idx ? idx[r] / div : r)); fp16 input keeps scale 1.
 template <bool IN_BF16>
 __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const int32_t* __restrict__ idx, int div,
-                                __half* __restrict__ x16, float* __restrict__ inv_scale, int K, int perm) {
+                                __half* __restrict__ x16, float* __restrict__ inv_scale, int K, int perm, int release_early) {
   __shared__ float red[32];
   __shared__ float sc_sh;
+  // The GEMM that follows may start streaming its weights as soon as this kernel lets it.  With static
+  // weights that is at once; otherwise only after everything before this kernel has completed, because the
+  // kernel before might be the one that writes those weights.
+  if (release_early) grid_dep_release();
+  grid_dep_wait();
+  if (!release_early) grid_dep_release();
   const int64_t r = blockIdx.x;
   const int64_t srow = idx ? (int64_t)(idx[r] / div) : r;
   const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + srow * ldx;
@@ -583,14 +589,16 @@ int act_prep(const void* x, bool in_bf16, int64_t ldx, const int32_t* idx, int d
   if (rows == 0) return B2Q_OK;
   int threads = (K / 8 + 31) / 32 * 32;
   threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
+  const int mode = tls().overlap_mode;
+  cudaError_t e;
   if (in_bf16)
-    act_prep_kernel<true><<<(unsigned)rows, threads, 0, st>>>(x, ldx, idx, div > 0 ? div : 1, reinterpret_cast<__half*>(x16),
-                                                              inv_scale, K, perm);
+    e = launch_overlapped(act_prep_kernel<true>, dim3((unsigned)rows), dim3(threads), 0, st, mode > 0, x, ldx, idx,
+                          div > 0 ? div : 1, reinterpret_cast<__half*>(x16), inv_scale, K, perm, mode == 2 ? 1 : 0);
   else
-    act_prep_kernel<false><<<(unsigned)rows, threads, 0, st>>>(x, ldx, idx, div > 0 ? div : 1, reinterpret_cast<__half*>(x16),
-                                                               inv_scale, K, perm);
+    e = launch_overlapped(act_prep_kernel<false>, dim3((unsigned)rows), dim3(threads), 0, st, mode > 0, x, ldx, idx,
+                          div > 0 ? div : 1, reinterpret_cast<__half*>(x16), inv_scale, K, perm, mode == 2 ? 1 : 0);
   note_launch("act_prep");
-  return launch_status();
+  return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
 }
 
 }  // namespace b2q

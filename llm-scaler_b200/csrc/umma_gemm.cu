@@ -58,6 +58,7 @@ struct UmmaWoParams {
   int w_rows_per_expert;     // tensor-map rows per expert: N (N-major) or K/8 (K-major)
   const float* tok_scale;    // optional per-token output multiplier (undoes the activation pre-scale)
   int out_bf16;              // output element type (may differ from the MMA input type)
+  int overlap_ok;            // host side only: launch with programmatic stream serialization
   int* status;
 };
 
@@ -206,8 +207,14 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 #endif
 
   // ---- which tile ----
+  // Dense launches let the next kernel of the stream begin at once and themselves wait for the kernels
+  // before them only where they first touch activations (the X producer below): the weight stream, the
+  // conversion into tensor memory and all set-up overlap the tail of whatever ran before.
+  // Grouped launches read a tile list the previous kernel built, so they wait here.
+  grid_dep_release();
   int tok0 = blockIdx.x * TOK, xrow0 = 0, M = p.M, expert = 0;
   if (p.tiles) {
+    grid_dep_wait();
     if ((int)blockIdx.x >= p.tiles[0]) return;
     const int2 td = reinterpret_cast<const int2*>(p.tiles + 4)[blockIdx.x];
     expert = td.x; tok0 = td.y;
@@ -257,6 +264,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       PROF_DECL;
       tma_prefetch_desc(&tm_x);
+      if (!p.tiles) grid_dep_wait();
       for (int c = 0; c < nk; ++c) {
         const int s = c % XS;
         { PROF_T0; if (c >= XS && !mbar_wait(x_empty + 8 * s, ((c / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break; PROF_ADD(0); }
@@ -597,7 +605,8 @@ static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWo
     if (dev < 16) configured[dev] = true;
   }
   dim3 grid(token_tiles, (p.N + 127) / 128, p.split_k > 1 ? p.split_k : 1);
-  kern<<<grid, Cfg::THREADS, Cfg::SMEM, st>>>(tw, tx, p);
+  const bool overlap = tls().overlap_mode > 0 && p.overlap_ok;
+  if (launch_overlapped(kern, grid, dim3(Cfg::THREADS), Cfg::SMEM, st, overlap, tw, tx, p) != cudaSuccess) return B2Q_ERR_CUDA;
   note_launch("umma_wo");
   return launch_status();
 }
@@ -672,6 +681,7 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.w_rows_per_expert = kmajor ? a.K / 8 : a.N;
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0; p.magic = a.magic ? 1 : 0;
   p.status = status_ptr();
+  p.overlap_ok = (a.after_prep || tls().overlap_mode == 2) ? 1 : 0;
   p.split_k = a.split_k; p.chunks_per_split = a.chunks_per_split; p.split_acc = a.split_k > 1 ? a.split_acc : nullptr;
   const bool fast = a.magic || (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
@@ -710,6 +720,7 @@ int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st) {
   p.w_rows_per_expert = a.N;
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0;
   p.status = status_ptr();
+  p.overlap_ok = (a.after_prep || tls().overlap_mode == 2) ? 1 : 0;
   p.split_k = a.split_k; p.chunks_per_split = a.chunks_per_split; p.split_acc = a.split_k > 1 ? a.split_acc : nullptr;
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
   rc = launch_wk<WK_W8>(a.bf16, true, tok, tw, tx, p, tiles, st);

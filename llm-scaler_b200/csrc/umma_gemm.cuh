@@ -17,6 +17,9 @@ struct UmmaGroupArgs {
   // split-K (dense decode shapes only): fp32 [M, N] buffer zeroed by the caller, see umma_plan_split_k
   int split_k = 1, chunks_per_split = 0;
   float* split_acc = nullptr;
+  // the activation pre-pass of the same call was launched directly before this GEMM: everything older on the
+  // stream is then known to be complete, so the weight stream may start before the pre-pass has finished
+  bool after_prep = false;
 };
 
 struct UmmaW4Args : UmmaGroupArgs {

@@ -25,7 +25,7 @@ namespace w8a8 {
 constexpr int TOK = 128;            // token tile (MMA N)
 constexpr int S = 4;                // operand stages: one K block of W (16 KB) + one of X (16 KB) each
 constexpr int NBUF = 4;             // accumulator buffers of TOK columns
-constexpr int THREADS = 64 + 256;   // TMA warp, MMA warp, 8 promotion / epilogue warps
+constexpr int THREADS = 64 + 512;   // TMA warp, MMA warp, 16 promotion / epilogue warps (4 quadrants x 4 column quarters)
 constexpr int STAGE_BYTES = 2 * 16384;
 constexpr int MAX_KB = 128;         // K <= 16384
 enum { ST_FULL = 201, ST_EMPTY = 202, ST_ACCFULL = 203, ST_ACCEMPTY = 204 };
@@ -58,7 +58,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(full + 8 * i, 1); mbar_init(empty + 8 * i, 1); }
-    for (int i = 0; i < NBUF; ++i) { mbar_init(acc_full + 8 * i, 1); mbar_init(acc_empty + 8 * i, 256); }
+    for (int i = 0; i < NBUF; ++i) { mbar_init(acc_full + 8 * i, 1); mbar_init(acc_empty + 8 * i, 512); }
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -106,12 +106,14 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       }
     }
   } else {
-    // ---- promotion + epilogue: 8 warps, quadrant = warp & 3, column half = (warp - 2) >> 2 ----
-    const int quad = warp & 3, half = (warp - 2) >> 2;
-    const int col0 = half * 64;
-    float acc[64];
+    // ---- promotion + epilogue: 16 warps, quadrant = warp & 3, column quarter = (warp - 2) >> 2 ----
+    // A thread owns one weight row and 32 token columns; the per-K-block chain (wait, tcgen05.ld, 32 FMAs) is
+    // short enough that the sixteen warps keep up with the MMA that refills the rotating buffers.
+    const int quad = warp & 3, quarter = (warp - 2) >> 2;
+    const int col0 = quarter * 32;
+    float acc[32];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) acc[i] = 0.f;
+    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
     bool ok = true;
 #pragma unroll 1
     for (int kb = 0; kb < nkb; ++kb) {
@@ -119,10 +121,8 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       ok = mbar_wait(acc_full + 8 * b, (kb / NBUF) & 1, abort_flag, p.status, ST_ACCFULL);
       if (!ok) break;
       tc_fence_after();
-      uint32_t r0[32], r1[32];
-      const uint32_t ta = tmem + ((uint32_t)(quad * 32) << 16) + b * TOK + col0;
-      tmem_ld32(ta, r0);
-      tmem_ld32(ta + 32, r1);
+      uint32_t r0[32];
+      tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * TOK + col0, r0);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(acc_empty + 8 * b);           // the buffer may be overwritten while the FMAs run
@@ -135,21 +135,13 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         acc[4 * i + 2] = fmaf(__uint_as_float(r0[4 * i + 2]), v.z, acc[4 * i + 2]);
         acc[4 * i + 3] = fmaf(__uint_as_float(r0[4 * i + 3]), v.w, acc[4 * i + 3]);
       }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 v = s4[8 + i];
-        acc[32 + 4 * i + 0] = fmaf(__uint_as_float(r1[4 * i + 0]), v.x, acc[32 + 4 * i + 0]);
-        acc[32 + 4 * i + 1] = fmaf(__uint_as_float(r1[4 * i + 1]), v.y, acc[32 + 4 * i + 1]);
-        acc[32 + 4 * i + 2] = fmaf(__uint_as_float(r1[4 * i + 2]), v.z, acc[32 + 4 * i + 2]);
-        acc[32 + 4 * i + 3] = fmaf(__uint_as_float(r1[4 * i + 3]), v.w, acc[32 + 4 * i + 3]);
-      }
     }
     if (ok) {
       const int n = n0 + quad * 32 + lane;
       if (n < p.N) {
         uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 32; ++i) {
           const int tok = tok0 + col0 + i;
           if (tok < p.M)
             outp[(int64_t)tok * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(acc[i]))

@@ -21,3 +21,4 @@ from .ops import (  # noqa: F401
 launch_count = _lib.launch_count
 last_kernel = _lib.last_kernel
 set_force_kernel = _lib.set_force_kernel
+set_overlap_mode = _lib.set_overlap_mode

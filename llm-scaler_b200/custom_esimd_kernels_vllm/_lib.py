@@ -47,6 +47,7 @@ _SIGS = {
     "b2q_moe_gemm_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
                                i64, i64, i64, i32, vp, sz, vp]),
     "b2q_set_force_kernel": (None, [i32]),
+    "b2q_set_overlap_mode": (None, [i32]),
     "b2q_last_kernel": (C.c_char_p, []),
     "b2q_launch_count": (C.c_uint64, []),
 }
@@ -138,3 +139,9 @@ def device_status() -> int:
 
 def set_force_kernel(which: int) -> None:
     lib.b2q_set_force_kernel(int(which))
+
+
+def set_overlap_mode(mode: int) -> None:
+    """0 = no kernel overlap, 1 = pre-pass/GEMM overlap (default), 2 = also declare weights static
+    (a GEMM may stream weights while earlier kernels of the stream are still draining)."""
+    lib.b2q_set_overlap_mode(int(mode))

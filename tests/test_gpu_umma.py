@@ -168,3 +168,51 @@ def test_fp8_block_w8a8(e, M, N, K, dtype):
     e.gemm_fp8_block_w8a8(xq, xs, wq.to(DEV), ws.to(DEV), out)
     assert e.last_kernel() == "umma_w8a8"
     assert_close(out, fp8.linear_block_w8a8(rq, rs, wq, ws), what=f"w8a8 M={M} N={N} K={K}")
+
+
+@pytest.mark.parametrize("M", [8, 96])
+def test_kernel_overlap_modes_give_identical_results(e, M):
+    """A chain of dependent linears (each reads what the one before wrote, through the same scratch) must give
+    bit-identical results whether consecutive kernels overlap (modes 1, 2) or not (mode 0).  Shapes without
+    split-K, whose atomic accumulation order is not reproducible in any mode."""
+    N = K = 4736                                  # 37 strips x 128: ragged last wave, never split at M = 96
+    g = torch.Generator().manual_seed(11)
+    layers = []
+    for i in range(4):
+        q, s = _int4(N, K, torch.bfloat16, 100 + i)
+        layers.append((int4.pack_nmajor_i32(q).to(DEV), (s * 0.05).to(DEV)))
+    wq8 = (torch.randn(N, K, generator=g) * 0.02)
+    s8 = (wq8.abs().amax(dim=1) / 448.0).float()
+    w8 = (wq8 / s8[:, None]).to(torch.float8_e4m3fn).to(DEV)
+    s8 = s8.to(DEV)
+    x0 = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    bufs = [torch.empty(M, N, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
+
+    def chain():
+        cur = x0
+        for i, (w, s) in enumerate(layers):
+            e.esimd_gemm_int4_pgrp(cur, w, s, bufs[i & 1])
+            cur = bufs[i & 1]
+            e.esimd_gemv_fp8_pern(cur, w8, s8, bufs[(i + 1) & 1], N, K)
+            cur = bufs[(i + 1) & 1]
+        return cur.clone()
+
+    split = M <= 64
+    results = {}
+    try:
+        for mode in (0, 1, 2, 0, 2, 1):
+            e.set_overlap_mode(mode)
+            for _ in range(3):
+                r = chain()
+            results.setdefault(mode, []).append(r)
+    finally:
+        e.set_overlap_mode(1)
+    torch.cuda.synchronize()
+    base = results[0][0].float()
+    assert torch.isfinite(base).all()
+    for mode, rs in results.items():
+        for r in rs:
+            if split:
+                assert (r.float() - base).abs().max() <= 2e-2 * base.abs().max(), f"mode {mode}"
+            else:
+                assert torch.equal(r, results[0][0]), f"overlap mode {mode} changed the result"
