@@ -23,6 +23,7 @@ int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStre
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
 int act_prep(const void*, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
+int act_split_fp8(const void*, bool, int64_t, void*, float*, int64_t, int, cudaStream_t);
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -35,22 +36,23 @@ static inline size_t tile_list_bytes(int64_t rows, int E, int tile) {
   return align_up(16 + 8 * (size_t)((rows + tile - 1) / tile + E), 256);
 }
 
-// [pre-passed activations M x K fp16] [per-token scales] [fp32 split-K accumulator M x N, decode shapes only]
+// [pre-passed activations M x K fp16] [per-token scales] [partial sums of the balanced decode mode]
 static inline size_t ws_prep_bytes(int64_t M, int64_t K) {
   return align_up((size_t)M * (size_t)K * 2, 256) + align_up((size_t)M * 4, 256);
 }
 
-// Decode shapes: split K so that strips x splits fills the machine; the fp32 accumulator is zeroed here.
+// [e4m3 term rows x K] [per-token scales] of the FP8 decode path
+static inline size_t ws_direct_bytes(int64_t M, int64_t K) {
+  if (M > 64) return 0;
+  return align_up((size_t)umma_w8_direct_rows(M, false) * (size_t)K, 256) + align_up((size_t)M * 4, 256) +
+         umma_w8_direct_partial_bytes(M);
+}
+
 template <class Args>
-static int plan_split(Args& ua, void* workspace, int64_t M, int64_t N, int64_t K, int chunks_per_raw, cudaStream_t st) {
-  if (M > 64) return B2Q_OK;
-  int cps = 0;
-  const int sk = umma_plan_split_k((int)N, (int)K, chunks_per_raw, &cps);
-  if (sk <= 1) return B2Q_OK;
-  float* acc = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + ws_prep_bytes(M, K));
-  if (cudaMemsetAsync(acc, 0, (size_t)M * (size_t)N * 4, st) != cudaSuccess) return B2Q_ERR_CUDA;
-  ua.split_k = sk; ua.chunks_per_split = cps; ua.split_acc = acc;
-  return B2Q_OK;
+static void give_balanced_scratch(Args& ua, void* workspace, int64_t M, int64_t K) {
+  if (M > 64) return;
+  ua.sk_ws = reinterpret_cast<uint8_t*>(workspace) + ws_prep_bytes(M, K);
+  ua.sk_ws_bytes = umma_balanced_ws_bytes(M);
 }
 
 }  // namespace b2q
@@ -138,9 +140,9 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   const bool umma_ok = umma_w4_supported(ua);
   // measured on B200: the mma.sync streaming kernel wins only for a handful of tokens (its per-token cost is
   // fragment traffic), the tcgen05 kernel is flat in M up to 64 and the only one for K-major layouts and prefill
-  // small weights at small M: one launch of the streaming kernel beats pre-pass + GEMM (+ split-K finalize)
+  // small weights at small M: one launch of the streaming kernel beats pre-pass + GEMM
   const bool tiny = M <= 32 && N * K <= (int64_t)1 << 25;
-  const bool want_umma = force == 2 || force == 3 || (force == 0 && (kmajor || (M > 8 && !tiny)));
+  const bool want_umma = force >= 2 || (force == 0 && (kmajor || (M > 8 && !tiny)));
   if (umma_ok && want_umma) {
     // With scratch, activations go through the pre-pass (fp16, per-token power-of-two scale, pair order of
     // the magic-number transform) and the transform's integer work drops from 12 to 5 operations per word.
@@ -153,8 +155,7 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
       int rc = act_prep(x, act_dtype == B2Q_BF16, ldx, nullptr, 1, workspace, inv, M, (int)K, perm, st);
       if (rc) return rc;
       ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.tok_scale = inv; ua.magic = true; ua.after_prep = true;
-      rc = plan_split(ua, workspace, M, N, K, 4, st);
-      if (rc) return rc;
+      give_balanced_scratch(ua, workspace, M, K);
     }
     return umma_w4_linear(ua, st);
   }
@@ -170,9 +171,13 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
 }
 
 size_t b2q_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  return ws_prep_bytes(M, K) + (M <= 64 ? align_up((size_t)M * (size_t)N * 4, 256) : 0);
+  (void)N;
+  return ws_prep_bytes(M, K) + umma_balanced_ws_bytes(M);
 }
-size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K) { return b2q_linear_workspace_bytes(M, N, K); }
+size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  const size_t a = b2q_linear_workspace_bytes(M, N, K), b = ws_direct_bytes(M, K);
+  return a > b ? a : b;
+}
 
 int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
                    int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
@@ -197,10 +202,25 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
   ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
   const bool umma_ok = umma_w8_supported(ua);
   // bf16 activations + scratch: convert them once to per-token-scaled fp16 so the weight decode is one cvt per pair
-  const bool have_ws = workspace && aligned16(workspace) && workspace_bytes >= b2q_linear_workspace_bytes(M, N, K) &&
+  const bool have_ws = workspace && aligned16(workspace) && workspace_bytes >= b2q_linear_fp8_workspace_bytes(M, N, K) &&
                        force != 3;
+  // decode shapes with one scale per row or per tensor: weights stay e4m3 all the way into the 8-bit MMA, the
+  // activations are split into e4m3 terms instead (exact), see umma_w8_direct.cu
+  if (force == 0 && have_ws && M <= 64 && scale_mode != B2Q_SCALE_BLOCK128 && umma_ok) {
+    float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) +
+                                          align_up((size_t)umma_w8_direct_rows(M, false) * (size_t)K, 256));
+    int rc = act_split_fp8(x, act_dtype == B2Q_BF16, ldx, workspace, inv, M, (int)K, st);
+    if (rc) return rc;
+    UmmaW8DirectArgs da{};
+    da.xq = workspace; da.inv_scale = inv; da.terms = act_dtype == B2Q_BF16 ? 2 : 3;
+    da.w = w; da.fmt = fp8_format; da.scale = scale; da.scale_dtype = scale_dtype; da.scale_mode = scale_mode;
+    da.out = out; da.ldo = ldo; da.out_bf16 = act_dtype == B2Q_BF16; da.M = (int)M; da.N = (int)N; da.K = (int)K;
+    da.partials = reinterpret_cast<uint8_t*>(inv) + align_up((size_t)M * 4, 256);
+    da.partial_bytes = umma_w8_direct_partial_bytes(M);
+    return umma_w8_direct_linear(da, st);
+  }
   const bool prep = act_dtype == B2Q_BF16 && have_ws && (K % 8) == 0;
-  const bool want_umma = force == 2 || force == 3 || (force == 0 && (M > 4 || prep || act_dtype == B2Q_F16));
+  const bool want_umma = force >= 2 || (force == 0 && (M > 4 || prep || act_dtype == B2Q_F16));
   if (umma_ok && want_umma) {
     if (prep) {
       float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * (size_t)K * 2, 256));
@@ -208,10 +228,7 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
       if (rc) return rc;
       ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.out_bf16 = true; ua.tok_scale = inv; ua.after_prep = true;
     }
-    if (have_ws) {
-      const int rc = plan_split(ua, workspace, M, N, K, 2, st);
-      if (rc) return rc;
-    }
+    if (have_ws) give_balanced_scratch(ua, workspace, M, K);
     return umma_w8_linear(ua, st);
   }
 

@@ -601,4 +601,90 @@ int act_prep(const void* x, bool in_bf16, int64_t ldx, const int32_t* idx, int d
   return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
 }
 
+// ---------------------------------------------------------------------------
+// Activation pre-pass of the FP8-weight decode GEMM: every row is scaled by a power of two so that its
+// largest element lands in [128, 256) and then written as a sum of e4m3 terms,
+//     x * 2^e = t0 + t1 / 16 (+ t2 / 256),
+// t0 = rn(x * 2^e), t1 = rn(16 * remainder), ...  Each term keeps four more significant bits, so two terms
+// reproduce a bf16 value and three an fp16 value exactly (elements more than 2^14 below the row maximum lose
+// their last bits; their share of a dot product is below fp32 rounding).  Term j of token r is row j * Mp + r.
+template <bool IN_BF16>
+__global__ void act_split_fp8_kernel(const void* __restrict__ x, int64_t ldx, uint8_t* __restrict__ xq,
+                                     float* __restrict__ inv_scale, int Mp, int K, int release_early) {
+  __shared__ float red[32];
+  __shared__ float sc_sh;
+  if (release_early) grid_dep_release();
+  grid_dep_wait();
+  if (!release_early) grid_dep_release();
+  const int64_t r = blockIdx.x;
+  const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + r * ldx;
+  auto to_f = [](uint16_t h) -> float {
+    if constexpr (IN_BF16) return __uint_as_float((uint32_t)h << 16);
+    else return __half2float(__ushort_as_half(h));
+  };
+  float amax = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(to_f(e[j])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, red[i]);
+    float s = 1.f;
+    if (a > 0.f && a < INFINITY) {
+      int ex = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127;
+      if (ex < -126) ex = -126;                     // fp32-subnormal maximum (fp16 / bf16 inputs never get here)
+      int sh = 7 - ex;
+      sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+      s = __uint_as_float((uint32_t)(sh + 127) << 23);
+    }
+    sc_sh = s;
+    inv_scale[r] = 1.0f / s;
+  }
+  __syncthreads();
+  const float sc = sc_sh;
+  constexpr int NT = IN_BF16 ? 2 : 3;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+    uint8_t t[NT][8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float rem = to_f(e[j]) * sc;
+#pragma unroll
+      for (int q = 0; q < NT; ++q) {
+        const uint8_t b = (uint8_t)__nv_cvt_float_to_fp8(rem, __NV_SATFINITE, __NV_E4M3);
+        t[q][j] = b;
+        rem = (rem - fp8_to_float(b, false)) * 16.f;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < NT; ++q)
+      *reinterpret_cast<uint2*>(xq + ((int64_t)q * Mp + r) * K + k) = *reinterpret_cast<const uint2*>(t[q]);
+  }
+}
+
+int act_split_fp8(const void* x, bool in_bf16, int64_t ldx, void* xq, float* inv_scale, int64_t M, int K, cudaStream_t st) {
+  if (M == 0) return B2Q_OK;
+  int threads = (K / 8 + 31) / 32 * 32;
+  threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
+  const int mode = tls().overlap_mode;
+  const int mp = (int)((M + 7) / 8 * 8);
+  cudaError_t e;
+  if (in_bf16)
+    e = launch_overlapped(act_split_fp8_kernel<true>, dim3((unsigned)M), dim3(threads), 0, st, mode > 0, x, ldx,
+                          reinterpret_cast<uint8_t*>(xq), inv_scale, mp, K, mode == 2 ? 1 : 0);
+  else
+    e = launch_overlapped(act_split_fp8_kernel<false>, dim3((unsigned)M), dim3(threads), 0, st, mode > 0, x, ldx,
+                          reinterpret_cast<uint8_t*>(xq), inv_scale, mp, K, mode == 2 ? 1 : 0);
+  note_launch("act_split_fp8");
+  return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
+}
+
 }  // namespace b2q

@@ -18,6 +18,7 @@
 // FP8_GEMM_DPAS_V9 (fp8_GEMM_pert.h:2940-3150), moe_prefill_up/down_forward_kernel
 // (csrc/moe_prefill/moe_prefill_int4.sycl:121-395), moe_gemm_block_prefill_kernel
 // (fp8_moe_gemm_blockscale.h:187-302).
+#include <atomic>
 #include "umma_gemm.cuh"
 #include "sm100.cuh"
 #include "smallm.cuh"   // nib2_to_act / fp8x2_to_act / lds128
@@ -43,7 +44,11 @@ __device__ long long g_umma_prof[32];
 #endif
 
 enum { WK_W4N = 0, WK_W4K = 1, WK_W8 = 2 };
-enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWEMPTY = 105, ST_ACCUM = 106 };
+enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWEMPTY = 105, ST_ACCUM = 106, ST_ACCEMPTY = 107, ST_FIXUP = 108 };
+
+// One piece of a CTA's work: 64-k chunks [c_begin, c_begin + nk) of the strip of 128 weight rows at n0.
+// part = the strip's other chunks belong to other CTAs; slot = which of the CTA's two partial-sum slots it uses.
+struct Segment { int n0, c_begin, nk, strip, part, slot; };
 
 struct UmmaWoParams {
   const void* scale; int scale_dtype; int scale_mode;      // scale_mode: B2Q_SCALE_* (fp8) ; ignored for int4
@@ -51,8 +56,10 @@ struct UmmaWoParams {
   void* out; int64_t ldo;
   int M, N, K;
   int marlin; uint32_t xor_mask; int e5m2;
-  int split_k, chunks_per_split;   // split-K over blockIdx.z (dense decode only)
-  float* split_acc;          // fp32 [M, N] accumulation buffer for split-K (zeroed by the host side)
+  int sk_sps, sk_units;      // balanced mode: raw stages per strip and in total (0 = one CTA per token tile and strip)
+  float* sk_partials;        // balanced mode: [2 * grid][TOK][128] fp32 partial sums of cut strips
+  int* sk_counters;          // balanced mode: arrivals per strip, zero between launches
+  int sk_grid;               // host side only: CTAs of a balanced launch
   int magic;                 // INT4: fp16 magic-number transform; x was permuted / scaled by the pre-pass
   const int32_t* tiles; const int32_t* expert_offsets; const int32_t* out_map;
   int w_rows_per_expert;     // tensor-map rows per expert: N (N-major) or K/8 (K-major)
@@ -197,16 +204,18 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   // barrier map (8 bytes each)
   const uint32_t x_full = bar, x_empty = x_full + 8 * XS, a_full = x_empty + 8 * XS, ab_empty = a_full + 8 * S;
   const uint32_t raw_full = ab_empty + 8 * S, raw_empty = raw_full + 8 * RS, accum_full = raw_empty + 8 * RS;
+  const uint32_t accum_empty = accum_full + 8, fix_bar = accum_full + 16;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (accum_full + 8 - base));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + (accum_full + 16 - base));
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (accum_full + 24 - base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + (accum_full + 32 - base));
+  volatile int* last_flag = reinterpret_cast<volatile int*>(gen + (accum_full + 36 - base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #ifdef B2Q_UMMA_PROF
   const long long _kt0 = clock64();
 #endif
 
-  // ---- which tile ----
+  // ---- which work ----
   // Dense launches let the next kernel of the stream begin at once and themselves wait for the kernels
   // before them only where they first touch activations (the X producer below): the weight stream, the
   // conversion into tensor memory and all set-up overlap the tail of whatever ran before.
@@ -221,11 +230,33 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     xrow0 = p.expert_offsets[expert];
     M = p.expert_offsets[expert + 1] - xrow0;
   }
-  const int n0 = blockIdx.y * 128;
-  // split-K: blockIdx.z owns a contiguous range of 64-k chunks (a multiple of the raw stage size)
-  const int c_begin = p.split_k > 1 ? (int)blockIdx.z * p.chunks_per_split : 0;
-  const int c_stop = p.split_k > 1 ? min(p.K / 64, c_begin + p.chunks_per_split) : p.K / 64;
-  const int nk = c_stop - c_begin;
+  // A CTA works through a list of segments = (strip of 128 weight rows, range of 64-k chunks).  Normally that
+  // is one whole strip, blockIdx.y.  Balanced mode (decode shapes, one token tile): the launch is a 1-D grid
+  // that fills the machine exactly, the work is cut into units of one raw stage, and CTA b takes the units
+  // [b U / G, (b + 1) U / G): up to two partial strips around any number of whole ones.  Every role below walks
+  // the same list with its own copy of this cursor.
+  const bool balanced = p.sk_sps > 0;
+  int u = 0, u0 = 0, u1 = 1;
+  if (balanced) {
+    tok0 = 0;
+    u0 = (int)((int64_t)blockIdx.x * p.sk_units / gridDim.x);
+    u1 = (int)((int64_t)(blockIdx.x + 1) * p.sk_units / gridDim.x);
+    u = u0;
+  }
+  auto next_segment = [&](Segment& sg) -> bool {
+    if (u >= u1) return false;
+    if (!balanced) {
+      sg.n0 = blockIdx.y * 128; sg.c_begin = 0; sg.nk = p.K / 64; sg.strip = blockIdx.y; sg.part = 0; sg.slot = 0;
+      u = u1;
+      return true;
+    }
+    const int strip = u / p.sk_sps, r0 = u - strip * p.sk_sps;
+    const int take = min(p.sk_sps - r0, u1 - u);
+    sg.n0 = strip * 128; sg.c_begin = r0 * CPR; sg.nk = take * CPR; sg.strip = strip;
+    sg.part = take != p.sk_sps; sg.slot = (u == u0) ? 0 : 1;
+    u += take;
+    return true;
+  };
   const int64_t sbase = (int64_t)expert * p.s_expert_elems;
 
   if (threadIdx.x == 0) {
@@ -233,6 +264,8 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     for (int i = 0; i < XS; ++i) { mbar_init(x_full + 8 * i, 1); mbar_init(x_empty + 8 * i, 1); }
     for (int i = 0; i < RS; ++i) { mbar_init(raw_full + 8 * i, 1); mbar_init(raw_empty + 8 * i, GPR * 128); }
     mbar_init(accum_full, Cfg::NMMA);
+    mbar_init(accum_empty, NG * 128);
+    mbar_init(fix_bar, NG * 128);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -241,21 +274,27 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  Segment sg;
 
   if (warp == 0) {
     // ---------------- raw weight producer ----------------
     if (lane == 0) {
       PROF_DECL;
       tma_prefetch_desc(&tm_w);
-      const int nraw = (nk + CPR - 1) / CPR;
-      for (int r = 0; r < nraw; ++r) {
-        const int rs = r % RS;
-        { PROF_T0; if (r >= RS && !mbar_wait(raw_empty + 8 * rs, ((r / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) break; PROF_ADD(0); }
-        mbar_expect_tx(raw_full + 8 * rs, Cfg::RAW_BYTES);
-        if constexpr (WK == WK_W4K)
-          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, n0, expert * p.w_rows_per_expert + (c_begin / CPR + r) * 32, raw_full + 8 * rs);
-        else
-          tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, (c_begin / CPR + r) * 128, expert * p.w_rows_per_expert + n0, raw_full + 8 * rs);
+      int grb = 0;                       // raw stages issued so far: ring position and phase carry across segments
+      bool ok = true;
+      while (ok && next_segment(sg)) {
+        const int nraw = (sg.nk + CPR - 1) / CPR;
+        for (int r = 0; r < nraw; ++r) {
+          const int gr = grb + r, rs = gr % RS;
+          { PROF_T0; if (gr >= RS && !mbar_wait(raw_empty + 8 * rs, ((gr / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) { ok = false; break; } PROF_ADD(0); }
+          mbar_expect_tx(raw_full + 8 * rs, Cfg::RAW_BYTES);
+          if constexpr (WK == WK_W4K)
+            tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, sg.n0, expert * p.w_rows_per_expert + (sg.c_begin / CPR + r) * 32, raw_full + 8 * rs);
+          else
+            tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, (sg.c_begin / CPR + r) * 128, expert * p.w_rows_per_expert + sg.n0, raw_full + 8 * rs);
+        }
+        grb += nraw;
       }
       PROF_FLUSH(12);
     }
@@ -265,11 +304,16 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       PROF_DECL;
       tma_prefetch_desc(&tm_x);
       if (!p.tiles) grid_dep_wait();
-      for (int c = 0; c < nk; ++c) {
-        const int s = c % XS;
-        { PROF_T0; if (c >= XS && !mbar_wait(x_empty + 8 * s, ((c / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break; PROF_ADD(0); }
-        mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
-        tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, (c_begin + c) * 64, xrow0 + tok0, x_full + 8 * s);
+      int gb = 0;
+      bool ok = true;
+      while (ok && next_segment(sg)) {
+        for (int c = 0; c < sg.nk; ++c) {
+          const int g = gb + c, s = g % XS;
+          { PROF_T0; if (g >= XS && !mbar_wait(x_empty + 8 * s, ((g / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; } PROF_ADD(0); }
+          mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
+          tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, (sg.c_begin + c) * 64, xrow0 + tok0, x_full + 8 * s);
+        }
+        gb += sg.nk;
       }
       PROF_FLUSH(16);
     }
@@ -281,69 +325,78 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const uint32_t dacc = tmem + me * Cfg::ACC_COLS;
       const uint64_t db0 = smem_desc_sw128(x_smem);
       bool ok = true;
+      int gb = 0, si = 0;
       PROF_DECL;
 #ifdef B2Q_UMMA_PROF
       const long long _loop0 = clock64();
 #endif
+      while (ok && next_segment(sg)) {
+        // the accumulators are reused: wait until the epilogue warps have read the previous segment's
+        if (si > 0) { ok = mbar_wait(accum_empty, (si - 1) & 1, abort_flag, p.status, ST_ACCEMPTY); if (!ok) break; tc_fence_after(); }
 #pragma unroll 1
-      for (int c = me; c < nk; c += Cfg::NMMA) {
-        const int s = c % S, xs = c % XS;
-        { PROF_T0; ok = mbar_wait(x_full + 8 * xs, (c / XS) & 1, abort_flag, p.status, ST_XFULL); PROF_ADD(0); }
-        if (ok) { PROF_T0; ok = mbar_wait(a_full + 8 * s, (c / S) & 1, abort_flag, p.status, ST_AFULL); PROF_ADD(1); }
-        if (!ok) break;
-        PROF_T0;
-        tc_fence_after();
-        const uint32_t ta = tmem + Cfg::A_COL0 + 32 * s;
-        const uint64_t db = db0 + (uint64_t)(xs * (Cfg::X_BYTES >> 4));
-        mma_f16_ts(dacc, ta, db, idesc, c >= Cfg::NMMA ? 1u : 0u);
-        mma_f16_ts(dacc, ta + 8, db + 2, idesc, 1u);
-        mma_f16_ts(dacc, ta + 16, db + 4, idesc, 1u);
-        mma_f16_ts(dacc, ta + 24, db + 6, idesc, 1u);
-        tc_commit(ab_empty + 8 * s);
-        tc_commit(x_empty + 8 * xs);
-        PROF_ADD(2);
+        for (int c = me; c < sg.nk; c += Cfg::NMMA) {
+          const int g = gb + c, s = g % S, xs = g % XS;
+          { PROF_T0; ok = mbar_wait(x_full + 8 * xs, (g / XS) & 1, abort_flag, p.status, ST_XFULL); PROF_ADD(0); }
+          if (ok) { PROF_T0; ok = mbar_wait(a_full + 8 * s, (g / S) & 1, abort_flag, p.status, ST_AFULL); PROF_ADD(1); }
+          if (!ok) break;
+          PROF_T0;
+          tc_fence_after();
+          const uint32_t ta = tmem + Cfg::A_COL0 + 32 * s;
+          const uint64_t db = db0 + (uint64_t)(xs * (Cfg::X_BYTES >> 4));
+          mma_f16_ts(dacc, ta, db, idesc, c >= Cfg::NMMA ? 1u : 0u);
+          mma_f16_ts(dacc, ta + 8, db + 2, idesc, 1u);
+          mma_f16_ts(dacc, ta + 16, db + 4, idesc, 1u);
+          mma_f16_ts(dacc, ta + 24, db + 6, idesc, 1u);
+          tc_commit(ab_empty + 8 * s);
+          tc_commit(x_empty + 8 * xs);
+          PROF_ADD(2);
+        }
+        if (ok) tc_commit(accum_full);
+        gb += sg.nk; ++si;
       }
 #ifdef B2Q_UMMA_PROF
       _pa[3] = clock64() - _loop0;
       if (me == 0) { PROF_FLUSH(0); }
 #endif
-      if (ok) tc_commit(accum_full);
     }
   } else {
-    // ---------------- transform, then epilogue (warps 3..10) ----------------
+    // ---------------- transform, then epilogue (the NG x 4 warps after the control warps) ----------------
     // Two groups of four warps; group g converts the 64-k chunks with (c & 1) == g, one weight row
     // (N-major / fp8) or column (K-major) per thread, so two chunks are always in flight.
     const int t = (warp & 3) * 32 + lane;        // row of the strip == tensor-memory lane this thread may write
     const int grp = (threadIdx.x - Cfg::CW * 32) >> 7;
-    int nrow = n0 + t; if (nrow >= p.N) nrow = p.N - 1;
     const int sw = t & 7;
     const bool blockscale = (WK == WK_W8) && (p.scale_mode == B2Q_SCALE_BLOCK128);
     const int kblocks = (p.K + 127) >> 7;
     bool ok = true;
+    int gb = 0, grb = 0, si = 0, fixn = 0;       // chunks / raw stages / segments / fix-up barrier phases so far
     PROF_DECL;
 #ifdef B2Q_UMMA_PROF
     const long long _loop0 = clock64();
 #endif
+    while (ok && next_segment(sg)) {
+    const int n0 = sg.n0, nk = sg.nk, c_begin = sg.c_begin;
+    int nrow = n0 + t; if (nrow >= p.N) nrow = p.N - 1;
 #pragma unroll 1
     for (int c = grp; c < nk; c += NG) {
       const int r = c / CPR, j = c % CPR;
-      const int rs = r % RS;
-      { PROF_T0; ok = mbar_wait(raw_full + 8 * rs, (r / RS) & 1, abort_flag, p.status, ST_RAWFULL); PROF_ADD(0); }
+      const int gr = grb + r, rs = gr % RS;
+      { PROF_T0; ok = mbar_wait(raw_full + 8 * rs, (gr / RS) & 1, abort_flag, p.status, ST_RAWFULL); PROF_ADD(0); }
       if (!ok) break;
       const uint32_t rawrow = raw_smem + rs * Cfg::RAW_BYTES + t * 128;     // N-major / fp8: this thread's row
       const uint32_t rawcol = raw_smem + rs * Cfg::RAW_BYTES + t * 4;       // K-major: this thread's column
       {
-        const int s = c % S;
-        if (c >= S) { PROF_T0; ok = mbar_wait(ab_empty + 8 * s, ((c / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); PROF_ADD(1); if (!ok) break; }
+        const int g = gb + c, s = g % S;
+        if (g >= S) { PROF_T0; ok = mbar_wait(ab_empty + 8 * s, ((g / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); PROF_ADD(1); if (!ok) break; }
         tc_fence_after();
         const uint32_t ta = tmem + ((uint32_t)((warp & 3) * 32) << 16) + Cfg::A_COL0 + 32 * s;
         uint32_t av[32];                         // this row's 64 values of the chunk, two per register, k ascending
         PROF_T0;
         if constexpr (WK == WK_W4N || WK == WK_W4K) {
           uint32_t s2 = 0; float sf = 0.f;
-          const int64_t si = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)((c_begin + c) >> 1) * p.s_stride_g;
-          if constexpr (FAST) { if (!p.magic) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si]; s2 = sv | (sv << 16); } }
-          else sf = load_scalar(p.scale, si, p.scale_dtype);
+          const int64_t si_ = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)((c_begin + c) >> 1) * p.s_stride_g;
+          if constexpr (FAST) { if (!p.magic) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si_]; s2 = sv | (sv << 16); } }
+          else sf = load_scalar(p.scale, si_, p.scale_dtype);
           uint32_t ww[8];
           bool marlin = false;
           if constexpr (WK == WK_W4N) {
@@ -360,7 +413,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           if constexpr (!BF16 && FAST) {
             if (p.magic) {
               // fp16 magic-number path: the activation pre-pass stored x in the pair order this produces
-              const __half hs = __float2half_rn(load_scalar(p.scale, si, p.scale_dtype));
+              const __half hs = __float2half_rn(load_scalar(p.scale, si_, p.scale_dtype));
               const uint32_t hv = __half_as_ushort(hs);
               const uint32_t m2 = hv | (hv << 16);
 #pragma unroll
@@ -421,64 +474,115 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       // release the raw stage once this group's last chunk in it is converted
       if (c + NG >= nk || (c + NG) / CPR != r) mbar_arrive(raw_empty + 8 * rs);
     }
+    if (!ok) break;
 
+    // ---------------- epilogue of this segment ----------------
+    ok = mbar_wait(accum_full, si & 1, abort_flag, p.status, ST_ACCUM);
+    if (!ok) break;
+    tc_fence_after();
+    const int quad = warp & 3;                   // tensor-memory lane quadrant this warp may read
+    const int cgrp = (warp - Cfg::CW) >> 2;      // the NG warps of a quadrant take column blocks in turn
+    const int n = n0 + quad * 32 + lane;
+    float post = 1.f;
+    if constexpr (WK == WK_W8) {
+      if (p.scale_mode != B2Q_SCALE_BLOCK128) {
+        post = (BF16 ? 5192296858534827628530496329220096.0f : 1.0f);   // 2^112 undoes the bf16 bit trick
+        const int nn = n < p.N ? n : p.N - 1;
+        post *= load_scalar(p.scale, sbase + (p.scale_mode == B2Q_SCALE_CHANNEL ? nn : 0), p.scale_dtype);
+      }
+    }
+    uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
+    constexpr int CB = TOK >= 32 ? 32 : 16;
+    auto write_out = [&](const uint32_t (&r)[32], int cb) {
+      if (n >= p.N) return;
+#pragma unroll
+      for (int i = 0; i < CB; ++i) {
+        const int tok = tok0 + cb + i;
+        if (tok < M) {
+          int64_t orow = xrow0 + tok;
+          if (p.out_map) orow = p.out_map[orow];
+          float v = __uint_as_float(r[i]) * post;
+          if (p.tok_scale) v *= p.tok_scale[xrow0 + tok];
+          outp[orow * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
+                                              : __half_as_ushort(__float2half_rn(v));
+        }
+      }
+    };
+    // partial sums of a cut strip: [CTA][slot][token][row of the strip] fp32, raw accumulator values
+    float* const my_part = balanced ? p.sk_partials + ((size_t)(blockIdx.x * 2 + sg.slot) * TOK) * 128 + quad * 32 + lane : nullptr;
+    bool freed = false;
+#pragma unroll 1
+    for (int cb = cgrp * CB; cb < TOK; cb += NG * CB) {
+      if (tok0 + cb >= M) break;
+      uint32_t r[32];
+      if constexpr (CB == 32) tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + cb, r);
+      else { uint32_t r16[16]; tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + cb, r16);
+#pragma unroll
+             for (int i = 0; i < 16; ++i) r[i] = r16[i]; }
+      tmem_ld_wait();
+      if (Cfg::NMMA == 2 && nk >= 2) {
+        uint32_t q[32];
+        if constexpr (CB == 32) tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + Cfg::ACC_COLS + cb, q);
+        else { uint32_t q16[16]; tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + Cfg::ACC_COLS + cb, q16);
+#pragma unroll
+               for (int i = 0; i < 16; ++i) q[i] = q16[i]; }
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
+      }
+      // balanced mode has one column block per thread at most: the accumulators are free for the next segment now
+      if (balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); freed = true; }
+      if (!sg.part) {
+        write_out(r, cb);
+      } else {
+#pragma unroll
+        for (int i = 0; i < CB; ++i)
+          if (cb + i < M) __stcg(my_part + (cb + i) * 128, __uint_as_float(r[i]));
+      }
+    }
+    if (balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); }
+    if (sg.part) {
+      // Whoever delivers a strip's last partial sums adds all of them up, always in CTA order, and writes the
+      // result: no CTA ever waits for another one, and the sum does not depend on who came last.
+      const int64_t U = p.sk_units, G = gridDim.x;
+      const int64_t us = (int64_t)sg.strip * p.sk_sps, ue = us + p.sk_sps - 1;
+      const int b_lo = (int)(((us + 1) * G + U - 1) / U) - 1, b_hi = (int)(((ue + 1) * G + U - 1) / U) - 1;
+      __threadfence();
+      mbar_arrive(fix_bar);
+      ok = mbar_wait(fix_bar, fixn & 1, abort_flag, p.status, ST_FIXUP); ++fixn;
+      if (!ok) break;
+      if (threadIdx.x == Cfg::CW * 32) {
+        __threadfence();                               // orders the partial sums of all epilogue threads before the count
+        const int old = atomicAdd(p.sk_counters + sg.strip, 1);
+        const int last = old == b_hi - b_lo;
+        if (last) p.sk_counters[sg.strip] = 0;       // every contributor has arrived: ready for the next launch
+        *last_flag = last;
+      }
+      mbar_arrive(fix_bar);
+      ok = mbar_wait(fix_bar, fixn & 1, abort_flag, p.status, ST_FIXUP); ++fixn;
+      if (!ok) break;
+      const int cb = cgrp * CB;
+      if (*last_flag && cb < TOK && cb < M) {
+        __threadfence();
+        uint32_t r[32];
+#pragma unroll
+        for (int i = 0; i < CB; ++i) r[i] = 0u;
+        for (int b = b_lo; b <= b_hi; ++b) {
+          const int64_t bu0 = (int64_t)b * U / G;
+          const float* src = p.sk_partials + ((size_t)(b * 2 + (bu0 >= us ? 0 : 1)) * TOK) * 128 + quad * 32 + lane;
+#pragma unroll
+          for (int i = 0; i < CB; ++i)
+            if (cb + i < M) r[i] = __float_as_uint(__uint_as_float(r[i]) + __ldcg(src + (cb + i) * 128));
+        }
+        write_out(r, cb);
+      }
+    }
+    gb += nk; grb += (nk + CPR - 1) / CPR; ++si;
+    }   // segments
 #ifdef B2Q_UMMA_PROF
     _pa[3] = clock64() - _loop0;
     if (threadIdx.x == Cfg::CW * 32) { PROF_FLUSH(4); }
 #endif
-    // ---------------- epilogue ----------------
-    if (ok) ok = mbar_wait(accum_full, 0, abort_flag, p.status, ST_ACCUM);
-    if (ok) {
-      tc_fence_after();
-      const int quad = warp & 3;                   // tensor-memory lane quadrant this warp may read
-      const int cgrp = (warp - Cfg::CW) >> 2;            // the NG warps of a quadrant take column blocks in turn
-      const int n = n0 + quad * 32 + lane;
-      float post = 1.f;
-      if constexpr (WK == WK_W8) {
-        if (p.scale_mode != B2Q_SCALE_BLOCK128) {
-          post = (BF16 ? 5192296858534827628530496329220096.0f : 1.0f);   // 2^112 undoes the bf16 bit trick
-          const int nn = n < p.N ? n : p.N - 1;
-          post *= load_scalar(p.scale, sbase + (p.scale_mode == B2Q_SCALE_CHANNEL ? nn : 0), p.scale_dtype);
-        }
-      }
-      uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
-      constexpr int CB = TOK >= 32 ? 32 : 16;
-#pragma unroll 1
-      for (int cb = cgrp * CB; cb < TOK; cb += NG * CB) {
-        if (tok0 + cb >= M) break;
-        uint32_t r[32];
-        if constexpr (CB == 32) tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + cb, r);
-        else { uint32_t r16[16]; tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + cb, r16);
-#pragma unroll
-               for (int i = 0; i < 16; ++i) r[i] = r16[i]; }
-        tmem_ld_wait();
-        if (Cfg::NMMA == 2 && nk >= 2) {
-          uint32_t q[32];
-          if constexpr (CB == 32) tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + Cfg::ACC_COLS + cb, q);
-          else { uint32_t q16[16]; tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + Cfg::ACC_COLS + cb, q16);
-#pragma unroll
-                 for (int i = 0; i < 16; ++i) q[i] = q16[i]; }
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
-        }
-        if (n < p.N) {
-#pragma unroll
-          for (int i = 0; i < CB; ++i) {
-            const int tok = tok0 + cb + i;
-            if (tok < M) {
-              int64_t orow = xrow0 + tok;
-              if (p.out_map) orow = p.out_map[orow];
-              float v = __uint_as_float(r[i]) * post;
-              if (p.tok_scale) v *= p.tok_scale[xrow0 + tok];
-              if (p.split_acc) { atomicAdd(p.split_acc + (int64_t)(xrow0 + tok) * p.N + n, v); continue; }
-              outp[orow * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
-                                                  : __half_as_ushort(__float2half_rn(v));
-            }
-          }
-        }
-      }
-    }
   }
 
   tc_fence_before();
@@ -535,13 +639,16 @@ static int* status_ptr() {
 }
 
 int w8a8_read_status(int* out);
+int w8d_read_status(int* out);
 
 int umma_read_status(int* out) {
   int* p = status_ptr();
   if (!p) return B2Q_ERR_CUDA;
   int rc = cuda_status(cudaMemcpy(out, p, sizeof(int), cudaMemcpyDeviceToHost));
   if (rc || *out) return rc;
-  return w8a8_read_status(out);
+  rc = w8a8_read_status(out);
+  if (rc || *out) return rc;
+  return w8d_read_status(out);
 }
 
 #ifdef B2Q_UMMA_PROF
@@ -553,42 +660,65 @@ extern "C" __attribute__((visibility("default"))) int b2q_debug_prof(long long* 
 }
 #endif
 
-// out[m, n] = round(acc[m, n]) after a split-K launch
-__global__ void splitk_finalize_kernel(const float* __restrict__ acc, uint16_t* __restrict__ out, int64_t ldo, int M, int N,
-                                       int out_bf16) {
-  const int64_t total = (int64_t)M * N;
-  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t m = i / N, n = i % N;
-    const float v = acc[i];
-    out[m * ldo + n] = out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+// ---- balanced mode (decode shapes) ----------------------------------------------------------------
+// Arrival counters of cut strips.  They are zero whenever no launch is in flight (the last arriver of a
+// strip resets its counter), so nothing has to be cleared per launch; launches take one of 64 banks in turn
+// so that launches overlapping in time (other streams, programmatic dependent launch) do not share counters.
+constexpr int SK_BANKS = 64, SK_MAX_STRIPS = 1024;
+__device__ int g_sk_counters[SK_BANKS * SK_MAX_STRIPS];
+
+static int* sk_counter_bank() {
+  static thread_local int* basep[16] = {nullptr};
+  static std::atomic<unsigned> next_bank{0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) return nullptr;
+  if (!basep[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sk_counters) != cudaSuccess) return nullptr;
+    basep[dev] = reinterpret_cast<int*>(p);
   }
+  return basep[dev] + (size_t)(next_bank.fetch_add(1, std::memory_order_relaxed) % SK_BANKS) * SK_MAX_STRIPS;
 }
 
-// Picks the number of K splits for a decode-shaped launch so that (strips x splits) fills whole waves of
-// the two-CTAs-per-SM grid; returns 1 when splitting does not pay.  cps_out = chunks per split.
-int umma_plan_split_k(int N, int K, int chunks_per_raw, int* cps_out) {
-  static thread_local int sms = 0;
-  if (!sms) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (sms <= 0) sms = 148;
+static int device_slots() {
+  static thread_local int sms[16] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 16) return 296;
+  if (!sms[dev]) {
+    cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (sms[dev] <= 0) sms[dev] = 148;
   }
-  const int slots = 2 * sms, strips = (N + 127) / 128, nk = K / 64;
-  int best = 1, best_cps = nk;
-  double best_eff = (double)strips / ((double)((strips + slots - 1) / slots) * slots);
-  // every extra CTA pays a pipeline fill and an atomic epilogue: split only when most of the machine would idle
-  if (best_eff >= 0.6) { *cps_out = nk; return 1; }
-  for (int sk = 2; sk <= 16; ++sk) {
-    int cps = (nk + sk - 1) / sk;
-    cps = (cps + chunks_per_raw - 1) / chunks_per_raw * chunks_per_raw;
-    if (cps < 8 || (sk - 1) * cps >= nk) continue;
-    const int items = strips * sk;
-    const double eff = (double)items / ((double)((items + slots - 1) / slots) * slots);
-    if (eff > best_eff + 0.04) { best_eff = eff; best = sk; best_cps = cps; }
-  }
-  *cps_out = best_cps;
-  return best;
+  return 2 * sms[dev];                     // decode tiles run two CTAs per SM
+}
+
+static int pick_tok(int m);
+
+size_t umma_balanced_ws_bytes(int64_t M) {
+  if (M > 64) return 0;
+  return (size_t)2 * device_slots() * pick_tok((int)M) * 128 * sizeof(float);
+}
+
+// Fills the balanced-mode fields of p when the shape profits: one token tile, whole raw stages, and a grid of
+// one CTA per strip that would leave more than a twentieth of the machine idle in its last wave.
+static int plan_balanced(UmmaWoParams& p, const UmmaGroupArgs& a, int M, int N, int K, int cpr, int tok) {
+  p.sk_sps = 0; p.sk_units = 0; p.sk_partials = nullptr; p.sk_counters = nullptr;
+  if (tls().force_kernel == 4) return 0;       // benchmarking: one CTA per strip
+  if (a.expert_offsets || tok > 64 || M > tok || !a.sk_ws || a.sk_ws_bytes < umma_balanced_ws_bytes(M)) return 0;
+  if ((K % (64 * cpr)) != 0 || (reinterpret_cast<uintptr_t>(a.sk_ws) & 15u)) return 0;
+  const int strips = (N + 127) / 128, slots = device_slots();
+  if (strips > SK_MAX_STRIPS) return 0;
+  const double eff = (double)strips / ((double)((strips + slots - 1) / slots) * slots);
+  if (eff > 0.95) return 0;
+  const int sps = K / (64 * cpr);
+  const int64_t units = (int64_t)strips * sps;
+  if (units > INT32_MAX) return 0;
+  int* counters = sk_counter_bank();
+  if (!counters) return 0;
+  p.sk_sps = sps; p.sk_units = (int)units;
+  p.sk_partials = reinterpret_cast<float*>(a.sk_ws); p.sk_counters = counters;
+  return (int)(units < slots ? units : slots);
 }
 
 static int pick_tok(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256))); }
@@ -604,7 +734,8 @@ static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWo
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess) return B2Q_ERR_CUDA;
     if (dev < 16) configured[dev] = true;
   }
-  dim3 grid(token_tiles, (p.N + 127) / 128, p.split_k > 1 ? p.split_k : 1);
+  dim3 grid(token_tiles, (p.N + 127) / 128, 1);
+  if (p.sk_sps > 0) grid = dim3(p.sk_grid, 1, 1);
   const bool overlap = tls().overlap_mode > 0 && p.overlap_ok;
   if (launch_overlapped(kern, grid, dim3(Cfg::THREADS), Cfg::SMEM, st, overlap, tw, tx, p) != cudaSuccess) return B2Q_ERR_CUDA;
   note_launch("umma_wo");
@@ -632,15 +763,6 @@ static int launch_wk(bool bf16, bool fast, int tok, const CUtensorMap& tw, const
 static int grouped_tok(int rows, int E) {
   const int avg = E > 0 ? (rows + E - 1) / E : rows;
   return avg <= 16 ? 16 : (avg <= 32 ? 32 : (avg <= 96 ? 64 : 128));
-}
-
-static int splitk_finalize(const float* acc, void* out, int64_t ldo, int M, int N, bool out_bf16, cudaStream_t st) {
-  const int64_t total = (int64_t)M * N;
-  int64_t g = (total + 255) / 256;
-  if (g > 148 * 8) g = 148 * 8;
-  splitk_finalize_kernel<<<(int)g, 256, 0, st>>>(acc, reinterpret_cast<uint16_t*>(out), ldo, M, N, out_bf16 ? 1 : 0);
-  note_launch("splitk_finalize");
-  return launch_status();
 }
 
 bool umma_w4_supported(const UmmaW4Args& a) {
@@ -682,13 +804,11 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0; p.magic = a.magic ? 1 : 0;
   p.status = status_ptr();
   p.overlap_ok = (a.after_prep || tls().overlap_mode == 2) ? 1 : 0;
-  p.split_k = a.split_k; p.chunks_per_split = a.chunks_per_split; p.split_acc = a.split_k > 1 ? a.split_acc : nullptr;
+  p.sk_grid = plan_balanced(p, a, a.M, a.N, a.K, 4, tok);
   const bool fast = a.magic || (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
-  rc = kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)
-              : launch_wk<WK_W4N>(a.bf16, fast, tok, tw, tx, p, tiles, st);
-  if (rc || !p.split_acc) return rc;
-  return splitk_finalize(p.split_acc, a.out, a.ldo, a.M, a.N, a.out_bf16, st);
+  return kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)
+                : launch_wk<WK_W4N>(a.bf16, fast, tok, tw, tx, p, tiles, st);
 }
 
 bool umma_w8_supported(const UmmaW8Args& a) {
@@ -721,11 +841,9 @@ int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st) {
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0;
   p.status = status_ptr();
   p.overlap_ok = (a.after_prep || tls().overlap_mode == 2) ? 1 : 0;
-  p.split_k = a.split_k; p.chunks_per_split = a.chunks_per_split; p.split_acc = a.split_k > 1 ? a.split_acc : nullptr;
+  p.sk_grid = plan_balanced(p, a, a.M, a.N, a.K, 2, tok);
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
-  rc = launch_wk<WK_W8>(a.bf16, true, tok, tw, tx, p, tiles, st);
-  if (rc || !p.split_acc) return rc;
-  return splitk_finalize(p.split_acc, a.out, a.ldo, a.M, a.N, a.out_bf16, st);
+  return launch_wk<WK_W8>(a.bf16, true, tok, tw, tx, p, tiles, st);
 }
 
 

@@ -14,9 +14,9 @@ struct UmmaGroupArgs {
   const int32_t* tiles = nullptr;           // device tile list {n, pad3, int2...}
   int tile_cap = 0;
   int64_t s_expert_elems = 0;
-  // split-K (dense decode shapes only): fp32 [M, N] buffer zeroed by the caller, see umma_plan_split_k
-  int split_k = 1, chunks_per_split = 0;
-  float* split_acc = nullptr;
+  // scratch for the balanced decode mode (partial sums of strips cut between CTAs), umma_balanced_ws_bytes(M)
+  // bytes; without it every strip is one CTA's job
+  void* sk_ws = nullptr; size_t sk_ws_bytes = 0;
   // the activation pre-pass of the same call was launched directly before this GEMM: everything older on the
   // stream is then known to be complete, so the weight stream may start before the pre-pass has finished
   bool after_prep = false;
@@ -47,6 +47,19 @@ struct UmmaW8A8Args {
   int M, N, K;
 };
 
+// FP8-weight decode GEMM on the 8-bit MMA: the activations arrive split into e4m3 terms (act_split_fp8).
+struct UmmaW8DirectArgs {
+  const void* xq; const float* inv_scale; int terms;      // [umma_w8_direct_rows, K] e4m3, [M], 2 (bf16) or 3 (fp16)
+  const void* w; int fmt;
+  const void* scale; int scale_dtype; int scale_mode;     // per channel or per tensor
+  void* out; int64_t ldo; bool out_bf16;
+  int M, N, K;
+  void* partials; size_t partial_bytes;                   // umma_w8_direct_partial_bytes(M), or null: strips are not cut
+};
+int umma_w8_direct_rows(int64_t M, bool bf16);
+size_t umma_w8_direct_partial_bytes(int64_t M);
+int umma_w8_direct_linear(const UmmaW8DirectArgs& a, cudaStream_t st);
+
 bool umma_w4_supported(const UmmaW4Args& a);
 int umma_w4_token_tile(const UmmaW4Args& a);
 int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st);
@@ -57,7 +70,7 @@ int umma_w8_linear(const UmmaW8Args& a, cudaStream_t st);
 
 int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st);
 
-int umma_plan_split_k(int N, int K, int chunks_per_raw, int* cps_out);
+size_t umma_balanced_ws_bytes(int64_t M);
 
 // First device-side wait timeout recorded since the library was loaded (0 = none).  Synchronises.
 int umma_read_status(int* out);

@@ -121,8 +121,8 @@ def linear_fp8(input, weight, weight_scale, output, scale_mode, N=None, K=None):
     with L.on_device(input):
         ws, wsb = None, 0
         if input.dtype == torch.bfloat16 or M <= 64:
-            # scratch for the activation pre-pass / split-K accumulator (torch's caching allocator: no cudaMalloc in steady state)
-            wsb = L.lib.b2q_linear_workspace_bytes(M, wn, wk)
+            # scratch for the activation pre-pass and partial sums (torch's caching allocator: no cudaMalloc in steady state)
+            wsb = L.lib.b2q_linear_fp8_workspace_bytes(M, wn, wk)
             ws = torch.empty(wsb, dtype=torch.uint8, device=input.device)
         L.check(L.lib.b2q_linear_fp8(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else wk,
                                       weight.data_ptr(), L.fp8_fmt(weight), weight_scale.data_ptr(),

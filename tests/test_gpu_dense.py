@@ -204,3 +204,40 @@ def test_act_quant_1x128_bit_exact(e):
     rq, rs = fp8.quantize_act_1x128(x)
     assert torch.equal(xs.cpu(), rs)
     assert torch.equal(xq.cpu().view(torch.uint8), rq.view(torch.uint8))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M", [1, 8, 33, 64])
+def test_fp8_decode_path_keeps_activations_exact(e, M, dtype):
+    """Decode shapes run on the 8-bit MMA with the activations split into e4m3 terms.  With an identity weight
+    (code 0x38 = 1.0 on the diagonal) and unit scales the output must equal the activations bit for bit, for every
+    mantissa pattern and over twelve binades of dynamic range inside one row."""
+    K = N = 256
+    g = torch.Generator().manual_seed(17 + M)
+    mant = torch.rand(M, K, generator=g) + 1.0
+    expo = torch.randint(-6, 6, (M, K), generator=g).float()
+    sign = torch.where(torch.rand(M, K, generator=g) < 0.5, -1.0, 1.0)
+    x = (sign * mant * torch.exp2(expo)).to(dtype)
+    x[:, 5] = 0
+    w = torch.zeros(N, K, dtype=torch.uint8)
+    w[torch.arange(N), torch.arange(K)] = 0x38
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    e.esimd_gemv_fp8_pern(x.to(DEV), w.to(DEV), torch.ones(N, device=DEV), out, N, K)
+    assert e.last_kernel() == "umma_w8_direct"
+    assert torch.equal(out.cpu(), x)
+
+
+def test_fp8_decode_path_outliers_and_strip_heights(e):
+    """Rows with a 10^4 outlier, N values that make the launch pick strips lower than 128 rows or cut strips
+    along k, and a K that is not a multiple of 128."""
+    for M, N, K in ((4, 27648 // 8 + 24, 1088), (16, 148 * 96 + 8, 512), (2, 640, 2112), (48, 9000, 256)):
+        g = torch.Generator().manual_seed(N + K)
+        w = torch.randn(N, K, generator=g) * 0.05
+        wq, s = fp8.quantize_channel(w)
+        x = torch.randn(M, K, generator=g)
+        x[:, 7] *= 1e4
+        x = x.to(torch.bfloat16)
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+        e.esimd_gemv_fp8_pern(x.to(DEV), wq.to(DEV), s.to(DEV), out, N, K)
+        assert e.last_kernel() == "umma_w8_direct"
+        assert_close(out, fp8.linear_channel(x, wq, s), what=f"fp8 decode M={M} N={N} K={K}")

@@ -173,8 +173,8 @@ def test_fp8_block_w8a8(e, M, N, K, dtype):
 @pytest.mark.parametrize("M", [8, 96])
 def test_kernel_overlap_modes_give_identical_results(e, M):
     """A chain of dependent linears (each reads what the one before wrote, through the same scratch) must give
-    bit-identical results whether consecutive kernels overlap (modes 1, 2) or not (mode 0).  Shapes without
-    split-K, whose atomic accumulation order is not reproducible in any mode."""
+    bit-identical results whether consecutive kernels overlap (modes 1, 2) or not (mode 0): strips cut between
+    CTAs are summed in a fixed order, so decode shapes are reproducible too."""
     N = K = 4736                                  # 37 strips x 128: ragged last wave, never split at M = 96
     g = torch.Generator().manual_seed(11)
     layers = []
@@ -190,14 +190,12 @@ def test_kernel_overlap_modes_give_identical_results(e, M):
 
     def chain():
         cur = x0
-        for i, (w, s) in enumerate(layers):
-            e.esimd_gemm_int4_pgrp(cur, w, s, bufs[i & 1])
-            cur = bufs[i & 1]
-            e.esimd_gemv_fp8_pern(cur, w8, s8, bufs[(i + 1) & 1], N, K)
-            cur = bufs[(i + 1) & 1]
+        for w, s in layers:
+            e.esimd_gemm_int4_pgrp(cur, w, s, bufs[0])          # never in place: input and output differ
+            e.esimd_gemv_fp8_pern(bufs[0], w8, s8, bufs[1], N, K)
+            cur = bufs[1]
         return cur.clone()
 
-    split = M <= 64
     results = {}
     try:
         for mode in (0, 1, 2, 0, 2, 1):
@@ -212,7 +210,4 @@ def test_kernel_overlap_modes_give_identical_results(e, M):
     assert torch.isfinite(base).all()
     for mode, rs in results.items():
         for r in rs:
-            if split:
-                assert (r.float() - base).abs().max() <= 2e-2 * base.abs().max(), f"mode {mode}"
-            else:
-                assert torch.equal(r, results[0][0]), f"overlap mode {mode} changed the result"
+            assert torch.equal(r, results[0][0]), f"overlap mode {mode} changed the result"
