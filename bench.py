@@ -37,9 +37,9 @@ M_SWEEP = (1, 8, 32)
 N_COPIES = 3
 METRIC = "fp8_per_channel_gemv_weight_GBps"
 # dram__bytes_read.sum + dram__bytes_write.sum of the GEMV kernel, mean of three captured launches of this very
-# command under `ncu --set full` (141.7-142.0 MB read, 4.6-6.7 MB written; the writes include L2 write-back of
-# what earlier launches left dirty): 1.03 x the algorithmic bytes, i.e. the weights are read exactly once.
-NCU_DRAM_BYTES_PER_LAUNCH = 147.4e6
+# command under `ncu --set full` (141.8-142.0 MB read, 3.8-4.2 MB written; the writes include L2 write-back of
+# what earlier launches left dirty): 1.02 x the algorithmic bytes, i.e. the weights are read exactly once.
+NCU_DRAM_BYTES_PER_LAUNCH = 145.85e6
 
 
 def algo_bytes(M, N=N_W, K=K_W):
