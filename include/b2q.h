@@ -105,8 +105,9 @@ B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, in
  * of two in the element order its nibble decode produces; the dequantised weight is then
  * (q - 8) * scale rounded once to fp16 (11 significant bits) instead of to the activation type.
  * Without scratch the weight is rounded exactly as the torch reference rounds it.  For M <= 64
- * the scratch also holds an fp32 [M, N] accumulator: K is then split over several CTAs per strip of
- * output rows so that layers with few output rows still occupy every SM.                        */
+ * the scratch also holds partial sums: layers with few output rows are cut along K over several CTAs
+ * per strip of rows so that they still occupy every SM; the partial sums are added in a fixed order,
+ * so results are bit-reproducible from run to run.                                              */
 B2Q_API size_t b2q_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 B2Q_API int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx,
                     const void* w, int w_layout,
@@ -122,9 +123,13 @@ B2Q_API int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx,
  * w is [N, K] one byte per element, row-major.  Activation stays 16-bit
  * (w8a16); e4m3 decode is exact including subnormals.  K % 16 == 0.
  * workspace is optional (NULL / 0 allowed).  With at least
- * b2q_linear_fp8_workspace_bytes() of scratch, bf16 activations are first rewritten
- * as fp16 times a per-token power of two (exact for every element within 2^-31 of
- * its row maximum), which makes the in-kernel fp8 decode four times cheaper.        */
+ * b2q_linear_fp8_workspace_bytes() of scratch:
+ *  - M <= 64 with per-channel or per-tensor scales runs on the 8-bit tensor-core path: the weights are
+ *    used as stored and every activation row is rewritten as 2^e times a sum of two (bf16) or three
+ *    (fp16) e4m3 terms, which reproduces it exactly (elements more than 2^14 below their row maximum
+ *    lose low bits);
+ *  - otherwise bf16 activations are rewritten as fp16 times a per-token power of two (exact for every
+ *    element within 2^-31 of its row maximum), which makes the in-kernel fp8 decode four times cheaper. */
 B2Q_API size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K);
 B2Q_API int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx,
                    const void* w, int fp8_format,
@@ -232,8 +237,9 @@ B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
  * (0 = none).  Synchronises the device; meant for tests and post-mortems.       */
 B2Q_API int b2q_device_status(int* out);
 
-/* Kernel selection override for benchmarking: 0 = automatic,
- * 1 = force the mma.sync streaming kernel, 2 = force the tcgen05 kernel.     */
+/* Kernel selection override for benchmarking: 0 = automatic, 1 = the mma.sync streaming kernel,
+ * 2 = the tcgen05 kernel with 16-bit operands, 3 = the same without activation pre-pass,
+ * 4 = the same with one CTA per strip (no strip cutting), 5 = INT4 decode on the int8 MMA.  */
 B2Q_API void b2q_set_force_kernel(int which);
 /* Overlap of consecutive kernels on a stream (programmatic dependent launch), per calling thread:
  *   0  off: every kernel starts after the one before it has completed.

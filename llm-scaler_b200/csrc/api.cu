@@ -24,6 +24,7 @@ int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
 int act_prep(const void*, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
 int act_split_fp8(const void*, bool, int64_t, void*, float*, int64_t, int, cudaStream_t);
+int act_split_i8(const void*, bool, int64_t, void*, float*, float*, int64_t, int, cudaStream_t);
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -46,6 +47,13 @@ static inline size_t ws_direct_bytes(int64_t M, int64_t K) {
   if (M > 64) return 0;
   return align_up((size_t)umma_w8_direct_rows(M, false) * (size_t)K, 256) + align_up((size_t)M * 4, 256) +
          umma_w8_direct_partial_bytes(M);
+}
+
+// [int8 term rows x K] [per-token scales] [per-group activation sums] [partial sums] of the INT4 decode path
+static inline size_t ws_i8_bytes(int64_t M, int64_t K) {
+  if (M > 16) return 0;
+  return align_up((size_t)umma_w4_i8_rows(M) * (size_t)K, 256) + align_up((size_t)M * 4, 256) +
+         align_up((size_t)(K / 128) * 16 * 4, 256) + umma_w4_i8_partial_bytes();
 }
 
 template <class Args>
@@ -138,6 +146,23 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   ua.s_stride_n = s_stride_n; ua.s_stride_g = s_stride_g;
   ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
   const bool umma_ok = umma_w4_supported(ua);
+  // the int8 tensor-core path (umma_w4_i8.cu): decode shapes, N-major nibbles, scratch available; on request only
+  if (force == 5 && umma_ok && !kmajor && M <= 16 && workspace && aligned16(workspace) &&
+      workspace_bytes >= b2q_linear_workspace_bytes(M, N, K)) {
+    uint8_t* wsb = reinterpret_cast<uint8_t*>(workspace);
+    float* inv = reinterpret_cast<float*>(wsb + align_up((size_t)umma_w4_i8_rows(M) * (size_t)K, 256));
+    float* xsum = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(inv) + align_up((size_t)M * 4, 256));
+    int rc = act_split_i8(x, act_dtype == B2Q_BF16, ldx, workspace, inv, xsum, M, (int)K, st);
+    if (rc) return rc;
+    UmmaW4I8Args ia{};
+    ia.xq = workspace; ia.inv_scale = inv; ia.xsum = xsum;
+    ia.w = w; ia.xor_mask = (w_layout == B2Q_W4_NMAJOR_S4) ? 0x88888888u : 0u;
+    ia.scale = scale; ia.scale_dtype = scale_dtype; ia.s_stride_n = s_stride_n; ia.s_stride_g = s_stride_g;
+    ia.out = out; ia.ldo = ldo; ia.out_bf16 = act_dtype == B2Q_BF16; ia.M = (int)M; ia.N = (int)N; ia.K = (int)K;
+    ia.partials = reinterpret_cast<uint8_t*>(xsum) + align_up((size_t)(K / 128) * 16 * 4, 256);
+    ia.partial_bytes = umma_w4_i8_partial_bytes();
+    return umma_w4_i8_linear(ia, st);
+  }
   // measured on B200: the mma.sync streaming kernel wins only for a handful of tokens (its per-token cost is
   // fragment traffic), the tcgen05 kernel is flat in M up to 64 and the only one for K-major layouts and prefill
   // small weights at small M: one launch of the streaming kernel beats pre-pass + GEMM
@@ -172,7 +197,8 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
 
 size_t b2q_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   (void)N;
-  return ws_prep_bytes(M, K) + umma_balanced_ws_bytes(M);
+  const size_t a = ws_prep_bytes(M, K) + umma_balanced_ws_bytes(M), b = ws_i8_bytes(M, K);
+  return a > b ? a : b;
 }
 size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const size_t a = b2q_linear_workspace_bytes(M, N, K), b = ws_direct_bytes(M, K);

@@ -687,4 +687,107 @@ int act_split_fp8(const void* x, bool in_bf16, int64_t ldx, void* xq, float* inv
   return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
 }
 
+// ---------------------------------------------------------------------------
+// Activation pre-pass of the INT4 decode GEMM on the int8 MMA: every row is scaled by a power of two so that its
+// largest element lands in [32, 64) and written as three signed-byte terms,
+//     x * 2^e = t0 + t1 / 128 + t2 / 16384      (t0 = rint(x 2^e), t1 = rint(128 * remainder), ...),
+// 20 bits below the row maximum in all.  Inside every group of eight k the bytes are stored in the order
+// (0, 2, 4, 6, 1, 3, 5, 7), the order in which the weight transform's two masks deliver a word's nibbles.
+// Term j of token r is row j * Mp + r.  xsum[g][r] = sum over group g of the value token r's three terms stand for; the
+// GEMM subtracts 8 x that to undo the nibble offset.
+template <bool IN_BF16>
+__global__ void act_split_i8_kernel(const void* __restrict__ x, int64_t ldx, int8_t* __restrict__ xq,
+                                    float* __restrict__ inv_scale, float* __restrict__ xsum, int Mp, int K, int release_early) {
+  __shared__ float red[32];
+  __shared__ float sc_sh;
+  if (release_early) grid_dep_release();
+  grid_dep_wait();
+  if (!release_early) grid_dep_release();
+  const int64_t r = blockIdx.x;
+  const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + r * ldx;
+  auto to_f = [](uint16_t h) -> float {
+    if constexpr (IN_BF16) return __uint_as_float((uint32_t)h << 16);
+    else return __half2float(__ushort_as_half(h));
+  };
+  float amax = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(to_f(e[j])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, red[i]);
+    float s = 1.f;
+    if (a > 0.f && a < INFINITY) {
+      int ex = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127;
+      if (ex < -126) ex = -126;
+      int sh = 5 - ex;
+      sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+      s = __uint_as_float((uint32_t)(sh + 127) << 23);
+    }
+    sc_sh = s;
+    inv_scale[r] = 1.0f / s;
+  }
+  __syncthreads();
+  const float sc = sc_sh;
+  // blockDim.x * 8 is a multiple of 256, so the 16 lanes of a half warp always cover exactly one group of 128 k
+  for (int k0 = 0; k0 < K; k0 += blockDim.x * 8) {
+    const int k = k0 + threadIdx.x * 8;
+    float part = 0.f;
+    if (k < K) {
+      const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+      const uint16_t* e = reinterpret_cast<const uint16_t*>(&v);
+      int8_t t[3][8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int src = (j & 3) * 2 + (j >> 2);            // stored position j holds source element src
+        float rem = to_f(e[src]) * sc;
+        const float full = rem;
+        float rep = 0.f, w = 1.f;
+#pragma unroll
+        for (int q = 0; q < 3; ++q) {
+          float ti = rintf(rem);
+          ti = fminf(fmaxf(ti, -127.f), 127.f);
+          t[q][j] = (int8_t)(int)ti;
+          rep += ti * w;
+          rem = (rem - ti) * 128.f;
+          w *= 0.0078125f;
+        }
+        (void)full;
+        part += rep;
+      }
+#pragma unroll
+      for (int q = 0; q < 3; ++q)
+        *reinterpret_cast<uint2*>(xq + ((int64_t)q * Mp + r) * K + k) = *reinterpret_cast<const uint2*>(t[q]);
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((threadIdx.x & 15) == 0 && k < K) xsum[(int64_t)(k >> 7) * Mp + r] = part;
+  }
+}
+
+int act_split_i8(const void* x, bool in_bf16, int64_t ldx, void* xq, float* inv_scale, float* xsum, int64_t M, int K,
+                 cudaStream_t st) {
+  if (M == 0) return B2Q_OK;
+  int threads = (K / 8 + 31) / 32 * 32;
+  threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
+  const int mode = tls().overlap_mode;
+  const int mp = (int)((M + 7) / 8 * 8);
+  cudaError_t e;
+  if (in_bf16)
+    e = launch_overlapped(act_split_i8_kernel<true>, dim3((unsigned)M), dim3(threads), 0, st, mode > 0, x, ldx,
+                          reinterpret_cast<int8_t*>(xq), inv_scale, xsum, mp, K, mode == 2 ? 1 : 0);
+  else
+    e = launch_overlapped(act_split_i8_kernel<false>, dim3((unsigned)M), dim3(threads), 0, st, mode > 0, x, ldx,
+                          reinterpret_cast<int8_t*>(xq), inv_scale, xsum, mp, K, mode == 2 ? 1 : 0);
+  note_launch("act_split_i8");
+  return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
+}
+
 }  // namespace b2q

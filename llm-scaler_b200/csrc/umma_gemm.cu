@@ -502,7 +502,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           int64_t orow = xrow0 + tok;
           if (p.out_map) orow = p.out_map[orow];
           float v = __uint_as_float(r[i]) * post;
-          if (p.tok_scale) v *= p.tok_scale[xrow0 + tok];
+          if (p.tok_scale) v *= __ldcg(p.tok_scale + xrow0 + tok);   // past L1: it may hold the previous call's scales
           outp[orow * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
                                               : __half_as_ushort(__float2half_rn(v));
         }
@@ -640,6 +640,7 @@ static int* status_ptr() {
 
 int w8a8_read_status(int* out);
 int w8d_read_status(int* out);
+int w4i_read_status(int* out);
 
 int umma_read_status(int* out) {
   int* p = status_ptr();
@@ -648,7 +649,9 @@ int umma_read_status(int* out) {
   if (rc || *out) return rc;
   rc = w8a8_read_status(out);
   if (rc || *out) return rc;
-  return w8d_read_status(out);
+  rc = w8d_read_status(out);
+  if (rc || *out) return rc;
+  return w4i_read_status(out);
 }
 
 #ifdef B2Q_UMMA_PROF

@@ -60,6 +60,19 @@ int umma_w8_direct_rows(int64_t M, bool bf16);
 size_t umma_w8_direct_partial_bytes(int64_t M);
 int umma_w8_direct_linear(const UmmaW8DirectArgs& a, cudaStream_t st);
 
+// INT4 decode GEMM on the int8 MMA: the activations arrive split into three int8 terms (act_split_i8).
+struct UmmaW4I8Args {
+  const void* xq; const float* inv_scale; const float* xsum;   // [umma_w4_i8_rows, K] s8 (k permuted in eights), [M], [K/128][Mp]
+  const void* w; uint32_t xor_mask;                            // N-major nibbles; 0x88888888 for two's-complement storage
+  const void* scale; int scale_dtype; int64_t s_stride_n, s_stride_g;
+  void* out; int64_t ldo; bool out_bf16;
+  int M, N, K;
+  void* partials; size_t partial_bytes;                        // umma_w4_i8_partial_bytes(), or null: strips are not cut
+};
+int umma_w4_i8_rows(int64_t M);
+size_t umma_w4_i8_partial_bytes();
+int umma_w4_i8_linear(const UmmaW4I8Args& a, cudaStream_t st);
+
 bool umma_w4_supported(const UmmaW4Args& a);
 int umma_w4_token_tile(const UmmaW4Args& a);
 int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st);

@@ -49,7 +49,7 @@ template <int NTOK> struct Cfg {
 };
 
 // One piece of a CTA's work: stages [st_begin, st_end) of 128 k of the strip of 128 weight rows at n0.
-struct Segment { int n0, strip, st_begin, st_end, part, slot; };
+struct Segment { int n0, strip, st_begin, st_end, part, slot, rot; };   // stage order: st_begin + (i + rot) % count
 }  // namespace w8d
 
 struct W8DParams {
@@ -102,6 +102,9 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
     sg.strip = strip; sg.n0 = strip * p.h;
     sg.st_begin = r0 * p.ust; sg.st_end = min(nst, (r0 + take) * p.ust);
     sg.part = take != p.sps; sg.slot = (u == u0) ? 0 : 1;
+    // Every CTA starts at a different stage: all CTAs read the same small activation array, and in step they would
+    // all ask the same L2 lines for it at the same moment.
+    sg.rot = (int)((blockIdx.x * 5u + (unsigned)strip) % (unsigned)(sg.st_end - sg.st_begin));
     u += take;
     return true;
   };
@@ -127,7 +130,9 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       int g = 0;
       bool ok = true;
       while (ok && next_segment(sg)) {
-        for (int r = sg.st_begin; r < sg.st_end; ++r, ++g) {
+        const int cnt = sg.st_end - sg.st_begin;
+        for (int i = 0; i < cnt; ++i, ++g) {
+          const int r = sg.st_begin + (i + sg.rot) % cnt;
           const int s = g % NS;
           if (g >= NS && !mbar_wait(empty + 8 * s, ((g / NS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; }
           mbar_expect_tx(full + 8 * s, p.h * 128);
@@ -143,7 +148,9 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       int g = 0;
       bool ok = true;
       while (ok && next_segment(sg)) {
-        for (int r = sg.st_begin; r < sg.st_end; ++r, ++g) {
+        const int cnt = sg.st_end - sg.st_begin;
+        for (int i = 0; i < cnt; ++i, ++g) {
+          const int r = sg.st_begin + (i + sg.rot) % cnt;
           const int s = g % NS;
           if (g >= NS && !mbar_wait(empty + 8 * s, ((g / NS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; }
           mbar_expect_tx(full + 8 * s, C::X_BYTES);
@@ -201,7 +208,7 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         for (int i = 0; i < 8; ++i) {
           const int m = m0 + i;
           if (m < p.M) {
-            const float o = v[i] * sw * p.inv_scale[m];
+            const float o = v[i] * sw * __ldcg(p.inv_scale + m);   // past L1: it may hold the previous call's scales
             outp[(int64_t)m * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
           }
         }

@@ -67,11 +67,9 @@ def linear_int4(input, weight, weight_scale, output):
     _chk(tuple(output.shape) == (M, N), "output must be [M, N]")
     _chk(input.stride(1) == 1 and output.stride(1) == 1, "input/output rows must be contiguous")
     with L.on_device(input):
-        ws, wsb = None, 0
-        if M > 8 or layout != L.W4_NMAJOR:
-            # scratch for the activation pre-pass of the tensor-core kernel (caching allocator, no cudaMalloc)
-            wsb = L.lib.b2q_linear_workspace_bytes(M, N, K)
-            ws = torch.empty(wsb, dtype=torch.uint8, device=input.device)
+        # scratch for the activation pre-pass and partial sums of the tensor-core kernels (caching allocator, no cudaMalloc)
+        wsb = L.lib.b2q_linear_workspace_bytes(M, N, K)
+        ws = torch.empty(wsb, dtype=torch.uint8, device=input.device)
         L.check(L.lib.b2q_linear_int4(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else K,
                                        wt.data_ptr(), layout, weight_scale.data_ptr(), L.dt(weight_scale), sn, sg,
                                        output.data_ptr(), output.stride(0) if M > 1 else N, M, N, K, GROUP,

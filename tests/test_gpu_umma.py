@@ -211,3 +211,23 @@ def test_kernel_overlap_modes_give_identical_results(e, M):
     for mode, rs in results.items():
         for r in rs:
             assert torch.equal(r, results[0][0]), f"overlap mode {mode} changed the result"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 384, 256), (8, 1000, 2048), (13, 4224, 1024), (16, 20000, 512)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_int4_decode_on_the_int8_mma(e, M, N, K, dtype):
+    """The opt-in INT4 decode kernel (unsigned-byte weights x three int8 activation terms, one s32 accumulator per
+    group, fp32 promotion): strips cut along k (small N), strips lower than 128 rows, both activation types, and
+    the two's-complement nibble layout."""
+    q, s = _int4(N, K, dtype, 7 * M + N)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(M)).to(dtype)
+    x[:, 3] *= 300.0
+    ref = int4.linear(x, q, s)
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    e.set_force_kernel(5)
+    try:
+        e.esimd_gemm_int4_pgrp(x.to(DEV), int4.pack_nmajor_i32(q).to(DEV), s.to(DEV), out)
+        assert e.last_kernel() == "umma_w4_i8"
+        assert_close(out, ref, what=f"int8-MMA int4 M={M} N={N} K={K}")
+    finally:
+        e.set_force_kernel(2)
