@@ -204,13 +204,21 @@ def run_b200(args):
     hx = {M: xs[M].cpu().pin_memory() for M in M_SWEEP}
     ho = {M: torch.empty(M, N_W, dtype=torch.bfloat16).pin_memory() for M in M_SWEEP}
 
+    # results go back on a second stream so that the PCIe transfer of one GEMV's output runs under the next GEMV
+    main_stream, copy_stream = torch.cuda.current_stream(), torch.cuda.Stream()
+    done = {M: torch.cuda.Event() for M in M_SWEEP}
+
     def e2e_step(i):
         for j, M in enumerate(M_SWEEP):
             wq, s = copies[(i * len(M_SWEEP) + j) % N_COPIES]
             xs[M].copy_(hx[M], non_blocking=True)
             op(xs[M], wq, s, outs[M], N_W, K_W)
-            ho[M].copy_(outs[M], non_blocking=True)
-        torch.cuda.current_stream().synchronize()   # the caller reads the result on the host every step
+            done[M].record(main_stream)
+            copy_stream.wait_event(done[M])
+            with torch.cuda.stream(copy_stream):
+                ho[M].copy_(outs[M], non_blocking=True)
+        copy_stream.synchronize()                   # the caller reads the results on the host every step
+        main_stream.synchronize()
 
     for i in range(3):
         e2e_step(i)
@@ -323,6 +331,8 @@ def main():
     if args.case:
         import bench_extra
         import custom_esimd_kernels_vllm as e
+        if os.environ.get("B2Q_OVERLAP_MODE"):
+            e.set_overlap_mode(int(os.environ["B2Q_OVERLAP_MODE"]))
         print(json.dumps({"case": args.case, **bench_extra.run(e, torch.device("cuda", 0), only=args.case)}))
     elif args.impl == "reference":
         run_reference(args)

@@ -22,6 +22,26 @@ def _peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+def _time_graph(fn, reps):
+    """Decode-shaped cases: reps calls captured into one CUDA graph through the public op, one replay timed
+    (no Python dispatch between the launches, as in a serving engine's decode loop)."""
+    for i in range(3):
+        fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(reps):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / reps        # microseconds
+
+
 def _time(fn, reps, warm=3):
     for i in range(warm):
         fn(i)
@@ -49,10 +69,11 @@ def case_c1(e, dev, g, pk):
     ws, s = _int4(N, K, dev, g, copies=32)                       # 32 x 8.4 MB > 2 x L2
     x = torch.randn(16, K, generator=g, device=dev).to(torch.bfloat16)
     o = torch.empty(16, N, dtype=torch.bfloat16, device=dev)
-    us = _time(lambda i: op4(x, ws[i % 32], s, o), 64)
+    us_eager = _time(lambda i: op4(x, ws[i % 32], s, o), 64)
+    us = _time_graph(lambda i: op4(x, ws[i % 32], s, o), 64)
     byts = N * K // 2 + N * (K // 128) * 2 + 16 * K * 2 + 16 * N * 2
-    return {"us": round(us, 2), "GBps": round(byts / us / 1e3, 1), "hbm_frac": round(byts / us / 1e3 / pk["hbm_gbs"], 3),
-            "kernel": e.last_kernel()}
+    return {"us": round(us, 2), "us_eager_python": round(us_eager, 2), "GBps": round(byts / us / 1e3, 1),
+            "hbm_frac": round(byts / us / 1e3 / pk["hbm_gbs"], 3), "kernel": e.last_kernel()}
 
 
 def _c3_weights(dev, g, M, N, K):
@@ -109,7 +130,8 @@ def _case_c5(e, dev, g, pk, M):
         act = e._impl.silu_mul(bufs["gate_up"])
         op4(act, layer["down"][0][0], layer["down"][1], bufs["down"])
 
-    us = _time(layer_fwd, 5 if M > 64 else 20, warm=2)            # 428 MB of weights per pass: no L2 residency
+    # 428 MB of weights per pass: no L2 residency
+    us = _time_graph(layer_fwd, 20) if M <= 64 else _time(layer_fwd, 5, warm=2)
     rec = {"us_per_layer": round(us, 1), "tokens_per_s_80_layers": round(M / (us * 80) * 1e6, 1)}
     if M <= 64:
         rec.update(GBps=round(wbytes / us / 1e3, 1), hbm_frac=round(wbytes / us / 1e3 / pk["hbm_gbs"], 3))

@@ -235,7 +235,8 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   // that fills the machine exactly, the work is cut into units of one raw stage, and CTA b takes the units
   // [b U / G, (b + 1) U / G): up to two partial strips around any number of whole ones.  Every role below walks
   // the same list with its own copy of this cursor.
-  const bool balanced = p.sk_sps > 0;
+  constexpr bool BAL = TOK <= 64;               // only decode tiles carry the multi-segment / partial-sum code
+  const bool balanced = BAL && p.sk_sps > 0;
   int u = 0, u0 = 0, u1 = 1;
   if (balanced) {
     tok0 = 0;
@@ -332,7 +333,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 #endif
       while (ok && next_segment(sg)) {
         // the accumulators are reused: wait until the epilogue warps have read the previous segment's
-        if (si > 0) { ok = mbar_wait(accum_empty, (si - 1) & 1, abort_flag, p.status, ST_ACCEMPTY); if (!ok) break; tc_fence_after(); }
+        if (BAL && si > 0) { ok = mbar_wait(accum_empty, (si - 1) & 1, abort_flag, p.status, ST_ACCEMPTY); if (!ok) break; tc_fence_after(); }
 #pragma unroll 1
         for (int c = me; c < sg.nk; c += Cfg::NMMA) {
           const int g = gb + c, s = g % S, xs = g % XS;
@@ -494,15 +495,18 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
     constexpr int CB = TOK >= 32 ? 32 : 16;
     auto write_out = [&](const uint32_t (&r)[32], int cb) {
-      if (n >= p.N) return;
+      // per-token scales of this column block: one load per lane, read past L1 (it may still hold the previous
+      // call's scales at this address), handed round the warp by shuffle
+      float ts_lane = 1.f;
+      if (p.tok_scale && lane < CB && tok0 + cb + lane < M) ts_lane = __ldcg(p.tok_scale + xrow0 + tok0 + cb + lane);
 #pragma unroll
       for (int i = 0; i < CB; ++i) {
+        const float ts = __shfl_sync(0xffffffffu, ts_lane, i);
         const int tok = tok0 + cb + i;
-        if (tok < M) {
+        if (tok < M && n < p.N) {
           int64_t orow = xrow0 + tok;
           if (p.out_map) orow = p.out_map[orow];
-          float v = __uint_as_float(r[i]) * post;
-          if (p.tok_scale) v *= __ldcg(p.tok_scale + xrow0 + tok);   // past L1: it may hold the previous call's scales
+          const float v = __uint_as_float(r[i]) * post * ts;
           outp[orow * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
                                               : __half_as_ushort(__float2half_rn(v));
         }
@@ -531,8 +535,8 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
       }
       // balanced mode has one column block per thread at most: the accumulators are free for the next segment now
-      if (balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); freed = true; }
-      if (!sg.part) {
+      if (BAL && balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); freed = true; }
+      if (!BAL || !sg.part) {
         write_out(r, cb);
       } else {
 #pragma unroll
@@ -540,8 +544,8 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           if (cb + i < M) __stcg(my_part + (cb + i) * 128, __uint_as_float(r[i]));
       }
     }
-    if (balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); }
-    if (sg.part) {
+    if (BAL && balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); }
+    if (BAL && sg.part) {
       // Whoever delivers a strip's last partial sums adds all of them up, always in CTA order, and writes the
       // result: no CTA ever waits for another one, and the sum does not depend on who came last.
       const int64_t U = p.sk_units, G = gridDim.x;

@@ -203,12 +203,16 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
       const uint32_t trow = tmem + ((uint32_t)(quad * 32) << 16) + buf * C::ACC_COLS;
       float* const my_part = p.partials + ((size_t)(blockIdx.x * 2 + sg.slot) * p.Mp) * 128 + rowi;
       auto write_out = [&](const float (&v)[8], int m0) {
-        if (n >= p.N || rowi >= p.h) return;
+        // token scales of this block of eight: one load per lane, past L1 (it may still hold the previous call's
+        // scales at this address), handed round the warp by shuffle
+        float ts_lane = 1.f;
+        if (lane < 8 && m0 + lane < p.M) ts_lane = __ldcg(p.inv_scale + m0 + lane);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+          const float ts = __shfl_sync(0xffffffffu, ts_lane, i);
           const int m = m0 + i;
-          if (m < p.M) {
-            const float o = v[i] * sw * __ldcg(p.inv_scale + m);   // past L1: it may hold the previous call's scales
+          if (m < p.M && n < p.N && rowi < p.h) {
+            const float o = v[i] * sw * ts;
             outp[(int64_t)m * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
           }
         }
