@@ -166,7 +166,7 @@ template <int TOK> struct UmmaCfg {
   // of six (fp8) to ten (int4) times, which is what capped the shared-memory variant near 3 TB/s.
   static constexpr int NG = 2;                                       // transform groups of 4 warps
   static constexpr int CTAS = TOK <= 128 ? 2 : 1;                    // two CTAs per SM except for the 256-token prefill tile: a second CTA hides fill and epilogue of short K loops (MoE) and doubles the issuers for decode
-  static constexpr int XS = TOK <= 32 ? 6 : (TOK == 128 ? 3 : 4);    // activation stages (64 k each)
+  static constexpr int XS = TOK <= 64 ? 6 : (TOK == 128 ? 4 : 5);    // activation stages (64 k each)
   // Issuing tcgen05.mma is a serial job of one thread and costs it several hundred cycles per 64-k
   // chunk regardless of the tile width; decode tiles therefore use two issuer warps on alternate
   // chunks, each with its own accumulator (summed in the epilogue).
