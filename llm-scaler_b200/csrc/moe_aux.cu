@@ -114,37 +114,57 @@ __global__ void route_hist_kernel(const int32_t* __restrict__ ids, int64_t n_pai
   for (int e = threadIdx.x; e < E; e += blockDim.x) counts[(int64_t)blockIdx.x * E + e] = sh[e];
 }
 
-// counts[b][e] -> exclusive running sum over b (in place); expert_offsets[E+1]; rows_per_expert[E]
+// counts[b][e] -> exclusive running sum over b (in place); expert_offsets[E+1]; rows_per_expert[E].
+// One block of 1024 threads: 1024 / E threads share an expert's column of chunk counts, each summing one run of
+// chunks, so the dependent chain is nchunks * E / 1024 loads long instead of nchunks.
 __global__ void route_prefix_kernel(int32_t* __restrict__ counts, int nchunks, int E, int32_t* __restrict__ expert_offsets,
                                     int32_t* __restrict__ rows_per_expert) {
+  __shared__ int32_t part[1024];     // [segment][expert]
   __shared__ int32_t tot[1024];
   __shared__ int32_t scan[1024];
-  const int e = threadIdx.x;
-  int run = 0;
-  if (e < E) {
-    for (int b = 0; b < nchunks; ++b) {
+  const int tid = threadIdx.x;
+  const int segs = 1024 / E > 0 ? 1024 / E : 1;
+  const int e = tid % E, seg = tid / E;
+  const bool active = seg < segs;
+  const int cps = (nchunks + segs - 1) / segs;
+  const int b0 = seg * cps, b1 = min(nchunks, b0 + cps);
+  int sum = 0;
+  if (active) {
+#pragma unroll 4
+    for (int b = b0; b < b1; ++b) sum += counts[(int64_t)b * E + e];
+    part[seg * E + e] = sum;
+  }
+  __syncthreads();
+  if (active) {
+    int run = 0;
+    for (int s2 = 0; s2 < seg; ++s2) run += part[s2 * E + e];
+#pragma unroll 4
+    for (int b = b0; b < b1; ++b) {
       const int c = counts[(int64_t)b * E + e];
       counts[(int64_t)b * E + e] = run;
       run += c;
     }
   }
-  tot[e] = e < E ? run : 0;
+  int total = 0;
+  if (tid < E)
+    for (int s2 = 0; s2 < segs; ++s2) total += part[s2 * E + tid];
+  tot[tid] = tid < E ? total : 0;
   __syncthreads();
   // Hillis-Steele inclusive scan over 1024 slots
-  int val = tot[e];
-  scan[e] = val;
+  int val = tot[tid];
+  scan[tid] = val;
   __syncthreads();
   for (int off = 1; off < 1024; off <<= 1) {
-    const int add = e >= off ? scan[e - off] : 0;
+    const int add = tid >= off ? scan[tid - off] : 0;
     __syncthreads();
     val += add;
-    scan[e] = val;
+    scan[tid] = val;
     __syncthreads();
   }
-  if (e < E) {
-    expert_offsets[e] = val - tot[e];
-    if (rows_per_expert) rows_per_expert[e] = tot[e];
-    if (e == E - 1) expert_offsets[E] = val;
+  if (tid < E) {
+    expert_offsets[tid] = val - tot[tid];
+    if (rows_per_expert) rows_per_expert[tid] = tot[tid];
+    if (tid == E - 1) expert_offsets[E] = val;
   }
 }
 

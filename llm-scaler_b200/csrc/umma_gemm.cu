@@ -378,8 +378,22 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     while (ok && next_segment(sg)) {
     const int n0 = sg.n0, nk = sg.nk, c_begin = sg.c_begin;
     int nrow = n0 + t; if (nrow >= p.N) nrow = p.N - 1;
+    // The scale of a chunk (one per weight row for INT4, one per CTA for block-scaled FP8) comes from global memory
+    // and its line rarely survives in the small L1 left beside 100+ KB of shared memory, so it is requested two
+    // chunks ahead of its use: an L2 round trip on every chunk was what bounded the transform.
+    auto chunk_scale = [&](int c) -> float {
+      if (c >= nk) return 0.f;
+      if constexpr (WK == WK_W4N || WK == WK_W4K)
+        return load_scalar(p.scale, sbase + (int64_t)nrow * p.s_stride_n + (int64_t)((c_begin + c) >> 1) * p.s_stride_g, p.scale_dtype);
+      else
+        return blockscale ? reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * kblocks + ((c_begin + c) >> 1)] : 0.f;
+    };
+    float sc_a = chunk_scale(grp), sc_b = chunk_scale(grp + NG);
 #pragma unroll 1
     for (int c = grp; c < nk; c += NG) {
+      const float sc_cur = sc_a;
+      sc_a = sc_b;
+      sc_b = chunk_scale(c + 2 * NG);
       const int r = c / CPR, j = c % CPR;
       const int gr = grb + r, rs = gr % RS;
       { PROF_T0; ok = mbar_wait(raw_full + 8 * rs, (gr / RS) & 1, abort_flag, p.status, ST_RAWFULL); PROF_ADD(0); }
@@ -395,9 +409,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         PROF_T0;
         if constexpr (WK == WK_W4N || WK == WK_W4K) {
           uint32_t s2 = 0; float sf = 0.f;
-          const int64_t si_ = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)((c_begin + c) >> 1) * p.s_stride_g;
-          if constexpr (FAST) { if (!p.magic) { const uint32_t sv = reinterpret_cast<const uint16_t*>(p.scale)[si_]; s2 = sv | (sv << 16); } }
-          else sf = load_scalar(p.scale, si_, p.scale_dtype);
+          if constexpr (FAST) {
+            // the scale has the activation's 16-bit type here, so float -> 16 bit gives back its stored bits
+            if (!p.magic) { const uint32_t sv = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(sc_cur)) : __half_as_ushort(__float2half_rn(sc_cur)); s2 = sv | (sv << 16); }
+          } else sf = sc_cur;
           uint32_t ww[8];
           bool marlin = false;
           if constexpr (WK == WK_W4N) {
@@ -414,7 +429,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           if constexpr (!BF16 && FAST) {
             if (p.magic) {
               // fp16 magic-number path: the activation pre-pass stored x in the pair order this produces
-              const __half hs = __float2half_rn(load_scalar(p.scale, si_, p.scale_dtype));
+              const __half hs = __float2half_rn(sc_cur);
               const uint32_t hv = __half_as_ushort(hs);
               const uint32_t m2 = hv | (hv << 16);
 #pragma unroll
@@ -440,7 +455,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           for (int c4 = 0; c4 < 4; ++c4) rv[c4] = lds128(rawrow + (((4 * j + c4) ^ sw) << 4));
           uint32_t (&o)[32] = av;
           if (blockscale) {
-            const float sf = reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * kblocks + ((c_begin + c) >> 1)];
+            const float sf = sc_cur;
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) {
               w8_word<BF16, true>(rv[c4].x, p.e5m2, sf, o[8 * c4 + 0], o[8 * c4 + 1]);
