@@ -22,13 +22,20 @@ using namespace sm100;
 __device__ int g_w8a8_status = 0;
 
 namespace w8a8 {
-constexpr int TOK = 128;            // token tile (MMA N)
-constexpr int S = 4;                // operand stages: one K block of W (16 KB) + one of X (16 KB) each
-constexpr int NBUF = 4;             // accumulator buffers of TOK columns
-constexpr int THREADS = 64 + 512;   // TMA warp, MMA warp, 16 promotion / epilogue warps (4 quadrants x 4 column quarters)
-constexpr int STAGE_BYTES = 2 * 16384;
+constexpr int THREADS = 64 + 512;   // TMA warp, MMA warp, 16 promotion / epilogue warps (4 lane quadrants x 4 column groups)
 constexpr int MAX_KB = 128;         // K <= 16384
 enum { ST_FULL = 201, ST_EMPTY = 202, ST_ACCFULL = 203, ST_ACCEMPTY = 204 };
+
+// TOK = token tile (MMA N), 128 or 256.  Measured on B200 at [4096 x 17408 x 5120]: 128 -> 1.21 PFLOP/s, 256 ->
+// 1.13 PFLOP/s (only two accumulator buffers fit, so MMA and promotion overlap less); 128 is what is launched.
+template <int TOK> struct Cfg {
+  static constexpr int NBUF = 512 / TOK;                     // accumulator buffers of TOK columns (all of tensor memory)
+  static constexpr int STAGE_BYTES = 16384 + TOK * 128;      // one K block of W + one of X
+  static constexpr int S = TOK == 128 ? 4 : 3;               // operand stages
+  static constexpr int CPT = TOK / 4;                        // token columns per promotion thread
+  static constexpr int SC_PITCH = TOK + 4;   // scale-table row pitch in floats: float4 rows stay aligned, transposing writes spread over banks
+  static constexpr int smem_bytes(int nkb) { return S * STAGE_BYTES + nkb * SC_PITCH * 4 + 1024 + 256; }
+};
 }  // namespace w8a8
 
 struct W8A8Params {
@@ -38,17 +45,20 @@ struct W8A8Params {
   int* status;
 };
 
+template <int TOK>
 __global__ void __launch_bounds__(w8a8::THREADS, 1)
 umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const W8A8Params p) {
   using namespace w8a8;
+  using C = Cfg<TOK>;
+  constexpr int S = C::S, NBUF = C::NBUF, STAGE_BYTES = C::STAGE_BYTES, SC_PITCH = C::SC_PITCH, CPT = C::CPT;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* gen = smem_raw + (base - smem_u32(smem_raw));
   const int nkb = p.K >> 7;
-  // layout: [S stages of (W tile, X tile)] [scale table nkb x TOK fp32] [barriers]
+  // layout: [S stages of (W tile, X tile)] [scale table nkb x SC_PITCH fp32] [barriers]
   const uint32_t sc_off = S * STAGE_BYTES;
   float* sc = reinterpret_cast<float*>(gen + sc_off);
-  const uint32_t bar = base + sc_off + MAX_KB * TOK * 4;
+  const uint32_t bar = base + sc_off + nkb * SC_PITCH * 4;
   const uint32_t full = bar, empty = bar + 8 * S, acc_full = bar + 16 * S, acc_empty = acc_full + 8 * NBUF;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(gen + (acc_empty + 8 * NBUF - base));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(gen + (acc_empty + 8 * NBUF + 8 - base));
@@ -58,17 +68,11 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(full + 8 * i, 1); mbar_init(empty + 8 * i, 1); }
-    for (int i = 0; i < NBUF; ++i) { mbar_init(acc_full + 8 * i, 1); mbar_init(acc_empty + 8 * i, 512); }
+    for (int i = 0; i < NBUF; ++i) { mbar_init(acc_full + 8 * i, 1); mbar_init(acc_empty + 8 * i, 16); }   // one arrival per promotion warp
     *abort_flag = 0;
     fence_barrier_init();
   }
   if (warp == 1) { tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), 512); tmem_relinquish(); }
-  // combined scale table: sc[kb][t] = xs[tok0 + t, kb] * ws[n0 / 128, kb]
-  for (int i = threadIdx.x; i < nkb * TOK; i += THREADS) {
-    const int t = i % TOK, kb = i / TOK;        // kb-major in smem
-    const int tok = tok0 + t;
-    sc[i] = tok < p.M ? p.xs[(int64_t)tok * nkb + kb] * p.ws[(int64_t)(n0 >> 7) * nkb + kb] : 0.f;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -106,14 +110,27 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       }
     }
   } else {
-    // ---- promotion + epilogue: 16 warps, quadrant = warp & 3, column quarter = (warp - 2) >> 2 ----
-    // A thread owns one weight row and 32 token columns; the per-K-block chain (wait, tcgen05.ld, 32 FMAs) is
-    // short enough that the sixteen warps keep up with the MMA that refills the rotating buffers.
-    const int quad = warp & 3, quarter = (warp - 2) >> 2;
-    const int col0 = quarter * 32;
-    float acc[32];
+    // ---- promotion + epilogue: 16 warps, lane quadrant = warp & 3, column group = (warp - 2) >> 2 ----
+    // A thread owns one weight row and CPT token columns.
+    const int quad = warp & 3, cgroup = (warp - 2) >> 2;
+    const int col0 = cgroup * CPT;
+    // Combined scale table sc[kb][t] = xs[tok0 + t, kb] * ws[n0 / 128, kb], built by the 512 promotion threads while
+    // the TMA and MMA warps already run ahead: consecutive threads read consecutive kb of one token (coalesced), four
+    // independent loads in flight per thread.
+    {
+      const int total = nkb * TOK, ptid = threadIdx.x - 64;
+      const float* wsrow = p.ws + (int64_t)(n0 >> 7) * nkb;
+#pragma unroll 4
+      for (int i = ptid; i < total; i += 512) {
+        const int kb = i % nkb, t = i / nkb;
+        const int tok = tok0 + t;
+        sc[kb * SC_PITCH + t] = tok < p.M ? __ldg(p.xs + (int64_t)tok * nkb + kb) * __ldg(wsrow + kb) : 0.f;
+      }
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+    }
+    float acc[CPT];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.f;
+    for (int i = 0; i < CPT; ++i) acc[i] = 0.f;
     bool ok = true;
 #pragma unroll 1
     for (int kb = 0; kb < nkb; ++kb) {
@@ -121,19 +138,26 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       ok = mbar_wait(acc_full + 8 * b, (kb / NBUF) & 1, abort_flag, p.status, ST_ACCFULL);
       if (!ok) break;
       tc_fence_after();
-      uint32_t r0[32];
-      tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * TOK + col0, r0);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(acc_empty + 8 * b);           // the buffer may be overwritten while the FMAs run
-      const float4* s4 = reinterpret_cast<const float4*>(sc + kb * TOK + col0);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float4 v = s4[i];
-        acc[4 * i + 0] = fmaf(__uint_as_float(r0[4 * i + 0]), v.x, acc[4 * i + 0]);
-        acc[4 * i + 1] = fmaf(__uint_as_float(r0[4 * i + 1]), v.y, acc[4 * i + 1]);
-        acc[4 * i + 2] = fmaf(__uint_as_float(r0[4 * i + 2]), v.z, acc[4 * i + 2]);
-        acc[4 * i + 3] = fmaf(__uint_as_float(r0[4 * i + 3]), v.w, acc[4 * i + 3]);
+      for (int h = 0; h < CPT / 32; ++h) {
+        uint32_t r0[32];
+        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + b * TOK + col0 + h * 32, r0);
+        tmem_ld_wait();
+        if (h == CPT / 32 - 1) {
+          // the buffer may be overwritten while the FMAs run
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty + 8 * b);
+        }
+        const float4* s4 = reinterpret_cast<const float4*>(sc + kb * SC_PITCH + col0 + h * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 v = s4[i];
+          acc[h * 32 + 4 * i + 0] = fmaf(__uint_as_float(r0[4 * i + 0]), v.x, acc[h * 32 + 4 * i + 0]);
+          acc[h * 32 + 4 * i + 1] = fmaf(__uint_as_float(r0[4 * i + 1]), v.y, acc[h * 32 + 4 * i + 1]);
+          acc[h * 32 + 4 * i + 2] = fmaf(__uint_as_float(r0[4 * i + 2]), v.z, acc[h * 32 + 4 * i + 2]);
+          acc[h * 32 + 4 * i + 3] = fmaf(__uint_as_float(r0[4 * i + 3]), v.w, acc[h * 32 + 4 * i + 3]);
+        }
       }
     }
     if (ok) {
@@ -141,7 +165,7 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       if (n < p.N) {
         uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
+        for (int i = 0; i < CPT; ++i) {
           const int tok = tok0 + col0 + i;
           if (tok < p.M)
             outp[(int64_t)tok * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(acc[i]))
@@ -155,33 +179,42 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, 512); }
 }
 
-int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st) {
+template <int TOK>
+static int launch_w8a8(const UmmaW8A8Args& a, const W8A8Params& p, cudaStream_t st) {
   using namespace w8a8;
-  if ((a.K % 128) != 0 || a.K / 128 > MAX_KB) return B2Q_ERR_SHAPE;
-  if (!tensor_map_encoder()) return B2Q_ERR_CUDA;
+  using C = Cfg<TOK>;
   CUtensorMap tw, tx;
   int rc = make_tmap_2d(&tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, a.N, a.K, (uint64_t)a.K, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
   rc = make_tmap_2d(&tx, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.xq, a.M, a.K, (uint64_t)a.K, TOK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
+  const int smem = C::smem_bytes(a.K / 128);
+  static thread_local int configured[16] = {0};      // largest dynamic shared-memory size set so far, per device
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 16 || configured[dev] < smem) {
+    if (cudaFuncSetAttribute(umma_w8a8_kernel<TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return B2Q_ERR_CUDA;
+    if (dev < 16) configured[dev] = smem;
+  }
+  dim3 grid((a.M + TOK - 1) / TOK, (a.N + 127) / 128, 1);
+  umma_w8a8_kernel<TOK><<<grid, THREADS, smem, st>>>(tw, tx, p);
+  note_launch("umma_w8a8");
+  return launch_status();
+}
+
+int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st) {
+  using namespace w8a8;
+  if ((a.K % 128) != 0 || a.K / 128 > MAX_KB) return B2Q_ERR_SHAPE;
+  if (!tensor_map_encoder()) return B2Q_ERR_CUDA;
   W8A8Params p{};
   p.xs = a.xs; p.ws = a.ws; p.out = a.out; p.ldo = a.ldo; p.out_bf16 = a.bf16 ? 1 : 0;
   p.M = a.M; p.N = a.N; p.K = a.K;
   void* sym = nullptr;
   if (cudaGetSymbolAddress(&sym, g_w8a8_status) != cudaSuccess) return B2Q_ERR_CUDA;
   p.status = reinterpret_cast<int*>(sym);
-  constexpr int SMEM = S * STAGE_BYTES + MAX_KB * TOK * 4 + 1024 + 256;
-  static thread_local bool configured[16] = {false};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev >= 16 || !configured[dev]) {
-    if (cudaFuncSetAttribute(umma_w8a8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) return B2Q_ERR_CUDA;
-    if (dev < 16) configured[dev] = true;
-  }
-  dim3 grid((a.M + TOK - 1) / TOK, (a.N + 127) / 128, 1);
-  umma_w8a8_kernel<<<grid, THREADS, SMEM, st>>>(tw, tx, p);
-  note_launch("umma_w8a8");
-  return launch_status();
+  const int nkb = a.K / 128;
+  if (Cfg<128>::smem_bytes(nkb) > 232448 - 1024) return B2Q_ERR_LIMIT;
+  return launch_w8a8<128>(a, p, st);
 }
 
 int w8a8_read_status(int* out) {
