@@ -92,6 +92,14 @@ B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, in
                     int scale_mode, void* out, int out_dtype, int64_t N, int64_t K,
                     void* stream);
 
+/* GGML Q4_0 quantisation with group 128, the load-time step that produces b2q_linear_int4's inputs:
+ * qweight int32 [M, K/8] (B2Q_W4_NMAJOR), scale fp16 [M, K/128] = signed group maximum / -8,
+ * q = clamp(int(x / scale_fp32 + 8.5), 0, 15).  x is bf16 or fp16 [M, K] with row pitch ldx.
+ * Replaces q4_0_quantize (csrc/xpu/torch_extension_q4_0.cc:29-84, csrc/xpu/q4_0_quant.sycl:29-125)
+ * and follows that kernel's arithmetic step by step.  K % 128 == 0; rows 8-byte aligned.       */
+B2Q_API int b2q_quantize_q4_0(const void* x, int act_dtype, int64_t ldx, void* qweight, void* scale_f16,
+                      int64_t M, int64_t K, void* stream);
+
 /* ---- dense weight-only linear: out[M, N] = x[M, K] * dequant(W)[N, K]^T --
  * fp32 accumulate, one rounding to act_dtype (x and out share act_dtype).
  * Replaces esimd_gemv_int4 / esimd_gemm_int4_pgrp

@@ -119,4 +119,63 @@ int dequant_fp8(const void* w, int fmt, const void* scale, int scale_dtype, int 
   return launch_status();
 }
 
+// ---------------------------------------------------------------------------
+// GGML Q4_0 quantiser, group 128: the load-time step that produces the INT4 path's inputs.
+// Restates csrc/xpu/q4_0_quant.sycl:29-125 operation by operation so that the bytes agree:
+//   signed maximum of the group (the positive one wins a tie of magnitudes), d = max / -8 in fp32,
+//   id = 1 / d in fp32 (0 when d == 0), scale = fp16(d), q = clamp(int(x * id + 8.5), 0, 15) with the
+//   product and the sum rounded separately and the conversion truncating, nibble i of a word at bits 4i.
+// One warp per (row, group): a lane owns four consecutive elements.
+template <bool IN_BF16>
+__global__ void quantize_q4_0_kernel(const void* __restrict__ x, int64_t ldx, uint32_t* __restrict__ qweight,
+                                     __half* __restrict__ scale, int64_t M, int K) {
+  const int lane = threadIdx.x & 31;
+  const int64_t unit = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int groups = K >> 7;
+  if (unit >= M * groups) return;
+  const int64_t row = unit / groups;
+  const int g = (int)(unit - row * groups);
+  const uint16_t* src = reinterpret_cast<const uint16_t*>(x) + row * ldx + (int64_t)g * 128 + lane * 4;
+  const uint2 raw = *reinterpret_cast<const uint2*>(src);
+  const uint16_t h[4] = {(uint16_t)(raw.x & 0xFFFF), (uint16_t)(raw.x >> 16), (uint16_t)(raw.y & 0xFFFF), (uint16_t)(raw.y >> 16)};
+  float v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = IN_BF16 ? __uint_as_float((uint32_t)h[i] << 16) : __half2float(__ushort_as_half(h[i]));
+  float max_pos = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
+  float neg_max = fmaxf(fmaxf(-v[0], -v[1]), fmaxf(-v[2], -v[3]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    max_pos = fmaxf(max_pos, __shfl_xor_sync(0xffffffffu, max_pos, o));
+    neg_max = fmaxf(neg_max, __shfl_xor_sync(0xffffffffu, neg_max, o));
+  }
+  const float max_signed = max_pos >= neg_max ? max_pos : -neg_max;
+  const float d = __fdiv_rn(max_signed, -8.0f);
+  const float id = d != 0.0f ? __frcp_rn(d) : 0.0f;
+  uint32_t nib = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    int q = (int)__fadd_rn(__fmul_rn(v[i], id), 8.5f);      // two roundings, then truncation
+    q = q < 0 ? 0 : (q > 15 ? 15 : q);
+    nib |= (uint32_t)q << (4 * i);
+  }
+  const uint32_t other = __shfl_down_sync(0xffffffffu, nib, 1);
+  if ((lane & 1) == 0) qweight[row * (int64_t)(K >> 3) + g * 16 + (lane >> 1)] = nib | (other << 16);
+  if (lane == 0) scale[row * groups + g] = __float2half_rn(d);
+}
+
+int quantize_q4_0(const void* x, bool in_bf16, int64_t ldx, void* qweight, void* scale, int64_t M, int64_t K, cudaStream_t st) {
+  const int64_t units = M * (K / 128);
+  if (units == 0) return B2Q_OK;
+  const int wpb = 8;
+  const unsigned grid = (unsigned)((units + wpb - 1) / wpb);
+  if (in_bf16)
+    quantize_q4_0_kernel<true><<<grid, wpb * 32, 0, st>>>(x, ldx, reinterpret_cast<uint32_t*>(qweight),
+                                                          reinterpret_cast<__half*>(scale), M, (int)K);
+  else
+    quantize_q4_0_kernel<false><<<grid, wpb * 32, 0, st>>>(x, ldx, reinterpret_cast<uint32_t*>(qweight),
+                                                           reinterpret_cast<__half*>(scale), M, (int)K);
+  note_launch("quantize_q4_0");
+  return launch_status();
+}
+
 }  // namespace b2q

@@ -97,6 +97,21 @@ def dequant_int4(weight, weight_scale, out_dtype=torch.bfloat16, layout=None):
     return out
 
 
+def q4_0_quantize(input, out_qweight, out_scale):
+    """GGML Q4_0, group 128: fills out_qweight int32 [M, K/8] and out_scale fp16 [M, K/128] in place."""
+    L.require_cuda(input, out_qweight, out_scale)
+    _chk(input.dim() == 2 and input.dtype in (torch.bfloat16, torch.float16), "input must be a 2-D bf16 / fp16 tensor")
+    M, K = input.shape
+    _chk(K % 128 == 0 and input.stride(1) == 1, "K must be a multiple of 128 and rows contiguous")
+    _chk(out_qweight.dtype == torch.int32 and tuple(out_qweight.shape) == (M, K // 8) and out_qweight.is_contiguous(),
+         "out_qweight must be a contiguous int32 [M, K/8] tensor")
+    _chk(out_scale.dtype == torch.float16 and tuple(out_scale.shape) == (M, K // 128) and out_scale.is_contiguous(),
+         "out_scale must be a contiguous fp16 [M, K/128] tensor")
+    with L.on_device(input):
+        L.check(L.lib.b2q_quantize_q4_0(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else K,
+                                         out_qweight.data_ptr(), out_scale.data_ptr(), M, K, L.stream(input)))
+
+
 # --------------------------------------------------------------------------- FP8 dense
 def linear_fp8(input, weight, weight_scale, output, scale_mode, N=None, K=None):
     L.require_cuda(input, weight, weight_scale, output)

@@ -184,6 +184,12 @@ _op(NS, "esimd_moe_scatter(Tensor hidden_states, Tensor router_top_value, Tensor
 _op(NS, "esimd_moe_scatter_fused(Tensor hidden_states, Tensor top_values, Tensor top_indices, "
         "Tensor scattered_hidden, Tensor scattered_weights, Tensor topk_ids, Tensor expert_start, Tensor max_tokens_out, "
         "int K, int topk, int T, int num_experts) -> Tensor", _moe_scatter_fused)
+# load-time quantiser (reference: csrc/xpu/torch_extension_q4_0.cc:78-83, module q4_0_quant_ops)
+def _q4_0_quantize(input, out_qweight, out_scale):
+    I.q4_0_quantize(input, out_qweight, out_scale)
+
+
+_op(NS, "q4_0_quantize(Tensor input, Tensor(a!) out_qweight, Tensor(b!) out_scale) -> ()", _q4_0_quantize)
 _op(NS, "esimd_moe_silu_mul(Tensor input, Tensor output, int N_gate_up, int N_half, int total_rows) -> Tensor", _moe_silu_mul)
 _op(NS, "esimd_moe_gather(Tensor moe_output, Tensor topk_ids, Tensor scattered_weights, Tensor final_hidden, "
         "int K, int topk, int T) -> Tensor", _moe_gather)

@@ -23,6 +23,25 @@ def quantize_ggml_q4_0(w: torch.Tensor, group: int = GROUP):
     return q.to(torch.uint8), scale
 
 
+def quantize_q4_0_device(w: torch.Tensor, group: int = GROUP):
+    """The on-device GGML Q4_0 quantiser, operation by operation (csrc/xpu/q4_0_quant.sycl:60-104).
+
+    Differs from quantize_ggml_q4_0 (the tests' Python quantiser) in two places: the inverse is taken of the fp32
+    scale, not of its fp16 rounding, and when +amax and -amax both occur the positive one is the signed maximum.
+    Returns (q uint8 [N, K] in 0..15, scale fp16 [N, K/group]).
+    """
+    N, K = w.shape
+    g = w.float().reshape(N, K // group, group)
+    max_pos = g.amax(dim=-1)
+    neg_max = (-g).amax(dim=-1)
+    max_signed = torch.where(max_pos >= neg_max, max_pos, -neg_max)
+    d = max_signed / -8.0
+    inv = torch.where(d != 0, 1.0 / d, torch.zeros_like(d))
+    biased = g * inv.unsqueeze(-1) + 8.5                      # product and sum rounded separately (fp32 tensors)
+    q = biased.to(torch.int32).clamp(0, 15).reshape(N, K)     # conversion truncates
+    return q.to(torch.uint8), d.to(torch.float16)
+
+
 def quantize_symmetric(w: torch.Tensor, group: int = GROUP, scale_dtype=torch.float16):
     """amax/7 symmetric quantiser: q = round(w / scale).clip(-8, 7) + 8.
 

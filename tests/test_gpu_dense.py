@@ -241,3 +241,29 @@ def test_fp8_decode_path_outliers_and_strip_heights(e):
         e.esimd_gemv_fp8_pern(x.to(DEV), wq.to(DEV), s.to(DEV), out, N, K)
         assert e.last_kernel() == "umma_w8_direct"
         assert_close(out, fp8.linear_channel(x, wq, s), what=f"fp8 decode M={M} N={N} K={K}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,K", [(1, 128), (4, 256), (16, 128), (256, 512), (1024, 2048), (512, 5120)])
+def test_q4_0_quantize_bit_exact(e, M, K, dtype):
+    """On-device GGML Q4_0 quantiser (shapes of tests/test_q4_0_quant_xpu.py:52-61): words and scales equal the
+    restated kernel arithmetic bit for bit, including groups that hold +amax and -amax, all-zero groups and
+    values that land exactly on a rounding boundary."""
+    torch.manual_seed(M * 7 + K)
+    x = (torch.randn(M, K) * 0.5).to(dtype)
+    x[0, :128] = 0
+    if M > 1:
+        x[1, 5], x[1, 77] = 1.5, -1.5          # tie of magnitudes: the positive one is the signed maximum
+        x[1, 6] = 1.5 * 0.3125                 # 2.5 steps: exactly between two codes
+    q = torch.empty(M, K // 8, dtype=torch.int32, device=DEV)
+    s = torch.empty(M, K // 128, dtype=torch.float16, device=DEV)
+    torch.ops.custom_esimd_kernels_vllm.q4_0_quantize(x.to(DEV), q, s)
+    rq, rs = int4.quantize_q4_0_device(x)
+    assert torch.equal(s.cpu().view(torch.int16), rs.view(torch.int16))
+    assert torch.equal(q.cpu(), int4.pack_nmajor_i32(rq).to(torch.int32))
+    # what it produces is what the INT4 linear consumes
+    if M >= 16:
+        a = torch.randn(4, K).to(dtype)
+        out = torch.empty(4, M, dtype=dtype, device=DEV)
+        e.esimd_gemm_int4_pgrp(a.to(DEV), q, s.to(dtype), out)
+        assert_close(out, int4.linear(a, rq, rs.to(dtype)), what="linear on device-quantised weights")

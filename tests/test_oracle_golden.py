@@ -2,6 +2,7 @@
 (tests/golden/make_golden.py).  Integer / byte results must be identical; dequantised values
 are compared bit for bit."""
 import numpy as np
+import pytest
 import torch
 
 from oracle import fp8, int4, moe
@@ -124,3 +125,24 @@ def test_topk_lowest_index_wins_ties():
     logits = torch.zeros(1, 8)
     w, ids = moe.topk_softmax(logits, 3, True, torch.float32)
     assert torch.allclose(w, torch.full((1, 3), 1 / 3))
+
+
+@pytest.mark.parametrize("M,K", [(1, 128), (4, 256), (16, 128), (256, 512)])
+def test_q4_0_device_quantiser_restatement_within_the_reference_envelope(M, K):
+    """The reference checks its on-device quantiser against the CPU one through an envelope, not bit for bit
+    (tests/test_q4_0_quant_xpu.py:71-121): |scale| within one fp16 ulp, and at most two elements per group whose
+    dequantised value differs by more than |scale|.  The restatement of the kernel must sit inside the same envelope
+    relative to the tests' Python quantiser, which the golden vectors pin."""
+    from oracle import int4
+    torch.manual_seed(M * 7 + K)
+    x = (torch.randn(M, K) * 0.5).to(torch.bfloat16)
+    q_ref, s_ref = int4.quantize_ggml_q4_0(x)
+    q_dev, s_dev = int4.quantize_q4_0_device(x)
+    ulp = (s_ref.abs().view(torch.int16).to(torch.int32) - s_dev.abs().view(torch.int16).to(torch.int32)).abs()
+    assert int(ulp.max()) <= 1
+    d_ref = (q_ref.float() - 8) * s_ref.float().repeat_interleave(128, dim=1)
+    d_dev = (q_dev.float() - 8) * s_dev.float().repeat_interleave(128, dim=1)
+    tol = s_ref.abs().float().repeat_interleave(128, dim=1) + 1e-4
+    assert int(((d_ref - d_dev).abs() > tol).sum()) <= 2 * M * (K // 128)
+    # and the two agree exactly wherever the fp16 rounding of the scale does not move a rounding boundary
+    assert (q_ref == q_dev).float().mean() > 0.99
