@@ -241,11 +241,15 @@ def run_b200(args):
     def capture_e2e(i):
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
+            cur = torch.cuda.current_stream()
             for j, M in enumerate(M_SWEEP):
                 wq, s = copies[(i * len(M_SWEEP) + j) % N_COPIES]
                 xs[M].copy_(hx[M], non_blocking=True)
                 op(xs[M], wq, s, outs[M], N_W, K_W)
-                ho[M].copy_(outs[M], non_blocking=True)
+                copy_stream.wait_stream(cur)                 # a second branch of the graph: the result's PCIe transfer
+                with torch.cuda.stream(copy_stream):         # runs under the next GEMV
+                    ho[M].copy_(outs[M], non_blocking=True)
+            cur.wait_stream(copy_stream)
         return g
 
     e2e_graph = capture_e2e(0)      # the weight copy an M uses does not depend on the step index
