@@ -92,6 +92,16 @@ B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, in
                     int scale_mode, void* out, int out_dtype, int64_t N, int64_t K,
                     void* stream);
 
+/* Residual add + RMSNorm, the step the reference fuses in front of a decode GEMV
+ * (esimd_resadd_norm_gemv_fp8_pert / _int4_pert / gemv2_fp8_pert, csrc/xpu/torch_extension.cc and
+ * csrc/xpu/esimd_kernels/resadd_norm_gemv_int4.h, norm_gemv_fused.h):
+ *   s = hidden + residual (fp32);  residual <- s;  normed_out <- s * rsqrt(mean(s^2) + eps) * norm_weight.
+ * All tensors [M, K] contiguous in act_dtype (norm_weight [K]); K % 8 == 0.  The GEMV then runs on
+ * normed_out through b2q_linear_fp8 / b2q_linear_int4; with kernel overlap on, its pre-pass and
+ * weight stream start under this kernel.                                                       */
+B2Q_API int b2q_resadd_rmsnorm(const void* hidden, void* residual, const void* norm_weight, void* normed_out,
+                       int act_dtype, int64_t M, int64_t K, float eps, void* stream);
+
 /* GGML Q4_0 quantisation with group 128, the load-time step that produces b2q_linear_int4's inputs:
  * qweight int32 [M, K/8] (B2Q_W4_NMAJOR), scale fp16 [M, K/128] = signed group maximum / -8,
  * q = clamp(int(x / scale_fp32 + 8.5), 0, 15).  x is bf16 or fp16 [M, K] with row pitch ldx.

@@ -25,6 +25,7 @@ int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, 
 int act_prep(const void*, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
 int act_split_fp8(const void*, bool, int64_t, void*, float*, int64_t, int, cudaStream_t);
 int quantize_q4_0(const void*, bool, int64_t, void*, void*, int64_t, int64_t, cudaStream_t);
+int resadd_rmsnorm(const void*, void*, const void*, void*, bool, int64_t, int, float, cudaStream_t);
 int act_split_i8(const void*, bool, int64_t, void*, float*, float*, int64_t, int, cudaStream_t);
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -104,6 +105,16 @@ int b2q_quantize_q4_0(const void* x, int act_dtype, int64_t ldx, void* qweight, 
   if (M > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if ((reinterpret_cast<uintptr_t>(x) & 7u) || ((ldx * 2) & 7u)) return B2Q_ERR_ALIGN;
   return quantize_q4_0(x, act_dtype == B2Q_BF16, ldx, qweight, scale_f16, M, K, (cudaStream_t)stream);
+}
+
+int b2q_resadd_rmsnorm(const void* hidden, void* residual, const void* norm_weight, void* normed_out, int act_dtype, int64_t M,
+                       int64_t K, float eps, void* stream) {
+  if (!hidden || !residual || !norm_weight || !normed_out) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (M < 0 || K <= 0 || (K % 8) != 0) return B2Q_ERR_SHAPE;
+  if (M > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (!aligned16(hidden) || !aligned16(residual) || !aligned16(norm_weight) || !aligned16(normed_out)) return B2Q_ERR_ALIGN;
+  return resadd_rmsnorm(hidden, residual, norm_weight, normed_out, act_dtype == B2Q_BF16, M, (int)K, eps, (cudaStream_t)stream);
 }
 
 void b2q_set_force_kernel(int which) { tls().force_kernel = which; }

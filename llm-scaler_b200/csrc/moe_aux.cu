@@ -810,4 +810,77 @@ int act_split_i8(const void* x, bool in_bf16, int64_t ldx, void* xq, float* inv_
   return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
 }
 
+// ---------------------------------------------------------------------------
+// Residual add + RMSNorm in front of a decode GEMV (the first half of the reference's fused
+// esimd_resadd_norm_gemv_* kernels, csrc/xpu/esimd_kernels/resadd_norm_gemv_int4.h and norm_gemv_fused.h):
+//   s = hidden + residual (fp32);  residual <- s;  normed = s * rsqrt(mean(s^2) + eps) * weight  -> normed_out.
+// The norm is taken of the fp32 sum, not of its 16-bit rounding, as the reference's step-by-step check does
+// (tests/test_resadd_norm_gemv_int4.py:41-59).  One block per row; the GEMV's own pre-pass follows and overlaps
+// through programmatic dependent launch.
+template <bool BF16>
+__global__ void resadd_rmsnorm_kernel(const void* __restrict__ hidden, void* __restrict__ residual, const void* __restrict__ weight,
+                                      void* __restrict__ normed, int K, float eps) {
+  using T = typename Act<BF16>::T;
+  __shared__ float red[32];
+  __shared__ float inv_sh;
+  grid_dep_wait();
+  grid_dep_release();
+  const int64_t r = blockIdx.x;
+  const T* h = reinterpret_cast<const T*>(hidden) + r * K;
+  T* res = reinterpret_cast<T*>(residual) + r * K;
+  const T* w = reinterpret_cast<const T*>(weight);
+  T* out = reinterpret_cast<T*>(normed) + r * K;
+  float ss = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 hv = *reinterpret_cast<const uint4*>(h + k), rv = *reinterpret_cast<const uint4*>(res + k);
+    const T* he = reinterpret_cast<const T*>(&hv);
+    const T* re = reinterpret_cast<const T*>(&rv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { const float v = Act<BF16>::to_f(he[j]) + Act<BF16>::to_f(re[j]); ss = fmaf(v, v, ss); }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+    inv_sh = rsqrtf(t / (float)K + eps);
+  }
+  __syncthreads();
+  const float inv = inv_sh;
+  // second pass over the same (cache-resident) inputs: only now is the residual overwritten
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 hv = *reinterpret_cast<const uint4*>(h + k), rv = *reinterpret_cast<const uint4*>(res + k);
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+    const T* he = reinterpret_cast<const T*>(&hv);
+    const T* re = reinterpret_cast<const T*>(&rv);
+    const T* we = reinterpret_cast<const T*>(&wv);
+    uint4 so, no;
+    T* se = reinterpret_cast<T*>(&so);
+    T* ne = reinterpret_cast<T*>(&no);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float v = Act<BF16>::to_f(he[j]) + Act<BF16>::to_f(re[j]);
+      se[j] = Act<BF16>::from_f(v);
+      ne[j] = Act<BF16>::from_f(v * inv * Act<BF16>::to_f(we[j]));
+    }
+    *reinterpret_cast<uint4*>(res + k) = so;
+    *reinterpret_cast<uint4*>(out + k) = no;
+  }
+}
+
+int resadd_rmsnorm(const void* hidden, void* residual, const void* weight, void* normed, bool bf16, int64_t M, int K, float eps,
+                   cudaStream_t st) {
+  if (M == 0) return B2Q_OK;
+  int threads = (K / 8 + 31) / 32 * 32;
+  threads = threads > 1024 ? 1024 : (threads < 32 ? 32 : threads);
+  const bool overlap = tls().overlap_mode > 0;
+  cudaError_t e;
+  if (bf16) e = launch_overlapped(resadd_rmsnorm_kernel<true>, dim3((unsigned)M), dim3(threads), 0, st, overlap, hidden, residual, weight, normed, K, eps);
+  else e = launch_overlapped(resadd_rmsnorm_kernel<false>, dim3((unsigned)M), dim3(threads), 0, st, overlap, hidden, residual, weight, normed, K, eps);
+  note_launch("resadd_rmsnorm");
+  return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
+}
+
 }  // namespace b2q

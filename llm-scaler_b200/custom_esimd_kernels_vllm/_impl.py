@@ -97,6 +97,21 @@ def dequant_int4(weight, weight_scale, out_dtype=torch.bfloat16, layout=None):
     return out
 
 
+def resadd_rmsnorm(hidden_states, residual, norm_weight, normed_out, eps):
+    """residual += hidden_states (in place); normed_out = rmsnorm(residual) * norm_weight, norm of the fp32 sum."""
+    L.require_cuda(hidden_states, residual, norm_weight, normed_out)
+    _chk(hidden_states.dim() == 2 and hidden_states.dtype in (torch.bfloat16, torch.float16), "hidden_states must be 2-D bf16 / fp16")
+    M, K = hidden_states.shape
+    for t, what in ((residual, "residual"), (normed_out, "normed_out")):
+        _chk(t.dtype == hidden_states.dtype and tuple(t.shape) == (M, K) and t.is_contiguous(), what + " must be a contiguous [M, K] tensor of the activation type")
+    _chk(hidden_states.is_contiguous() and norm_weight.dtype == hidden_states.dtype and norm_weight.numel() == K and norm_weight.is_contiguous(),
+         "hidden_states must be contiguous and norm_weight a contiguous [K] tensor of the activation type")
+    _chk(K % 8 == 0, "K must be a multiple of 8")
+    with L.on_device(hidden_states):
+        L.check(L.lib.b2q_resadd_rmsnorm(hidden_states.data_ptr(), residual.data_ptr(), norm_weight.data_ptr(), normed_out.data_ptr(),
+                                          L.dt(hidden_states), M, K, float(eps), L.stream(hidden_states)))
+
+
 def q4_0_quantize(input, out_qweight, out_scale):
     """GGML Q4_0, group 128: fills out_qweight int32 [M, K/8] and out_scale fp16 [M, K/128] in place."""
     L.require_cuda(input, out_qweight, out_scale)

@@ -184,6 +184,33 @@ _op(NS, "esimd_moe_scatter(Tensor hidden_states, Tensor router_top_value, Tensor
 _op(NS, "esimd_moe_scatter_fused(Tensor hidden_states, Tensor top_values, Tensor top_indices, "
         "Tensor scattered_hidden, Tensor scattered_weights, Tensor topk_ids, Tensor expert_start, Tensor max_tokens_out, "
         "int K, int topk, int T, int num_experts) -> Tensor", _moe_scatter_fused)
+# residual add + RMSNorm + decode GEMV (reference: ops.py:411-489; kernels esimd_kernels/resadd_norm_gemv_int4.h,
+# norm_gemv_fused.h).  Here: one norm kernel, then the ordinary GEMV on normed_out; the kernels overlap on the stream.
+def _resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps):
+    I.resadd_rmsnorm(hidden_states, residual, norm_weight, normed_out, eps)
+    return I.linear_fp8(normed_out, gemv_weight, gemv_scale, output, L.SCALE_TENSOR)
+
+
+def _resadd_norm_gemv_int4_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps):
+    I.resadd_rmsnorm(hidden_states, residual, norm_weight, normed_out, eps)
+    return I.linear_int4(normed_out, gemv_weight, gemv_scale, output)
+
+
+def _resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s0, o0, w1, s1, o1, eps):
+    normed = torch.empty_like(hidden_states)
+    I.resadd_rmsnorm(hidden_states, residual, norm_weight, normed, eps)
+    I.linear_fp8(normed, w0, s0, o0, L.SCALE_TENSOR)
+    I.linear_fp8(normed, w1, s1, o1, L.SCALE_TENSOR)
+    return o0
+
+
+_op(NS, "esimd_resadd_norm_gemv_fp8_pert(Tensor hidden_states, Tensor residual, Tensor norm_weight, Tensor gemv_weight, "
+        "Tensor gemv_scale, Tensor output, Tensor normed_out, float eps) -> Tensor", _resadd_norm_gemv_fp8_pert)
+_op(NS, "esimd_resadd_norm_gemv_int4_pert(Tensor hidden_states, Tensor residual, Tensor norm_weight, Tensor gemv_weight, "
+        "Tensor gemv_scale, Tensor output, Tensor normed_out, float eps) -> Tensor", _resadd_norm_gemv_int4_pert)
+_op(NS, "esimd_resadd_norm_gemv2_fp8_pert(Tensor hidden_states, Tensor residual, Tensor norm_weight, Tensor w0, Tensor s0, "
+        "Tensor o0, Tensor w1, Tensor s1, Tensor o1, float eps) -> Tensor", _resadd_norm_gemv2_fp8_pert)
+
 # load-time quantiser (reference: csrc/xpu/torch_extension_q4_0.cc:78-83, module q4_0_quant_ops)
 def _q4_0_quantize(input, out_qweight, out_scale):
     I.q4_0_quantize(input, out_qweight, out_scale)

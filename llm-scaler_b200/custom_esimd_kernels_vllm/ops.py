@@ -196,3 +196,25 @@ act_quant_fp8_1x128 = _impl.act_quant_fp8_1x128
 gemm_fp8_block_w8a8 = _impl.gemm_fp8_block_w8a8
 dequant_int4 = _impl.dequant_int4
 dequant_fp8 = _impl.dequant_fp8
+
+
+# ---- residual add + RMSNorm + decode GEMV (reference ops.py:411-489) and the load-time Q4_0 quantiser ----
+def esimd_resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps):
+    """residual += hidden_states (in place); normed_out = rmsnorm(residual) * norm_weight;
+    output = normed_out @ dequant(gemv_weight)^T with a per-tensor fp32 scale.  Returns output."""
+    return _ops.esimd_resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps)
+
+
+def esimd_resadd_norm_gemv_int4_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps):
+    """As esimd_resadd_norm_gemv_fp8_pert with INT4 g=128 weights (int32 [N, K/8], scales [N, K/128])."""
+    return _ops.esimd_resadd_norm_gemv_int4_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps)
+
+
+def esimd_resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s0, o0, w1, s1, o1, eps):
+    """Residual add + RMSNorm feeding two per-tensor FP8 GEMVs (o0, o1).  Returns o0."""
+    return _ops.esimd_resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s0, o0, w1, s1, o1, eps)
+
+
+def q4_0_quantize(input, out_qweight, out_scale):
+    """GGML Q4_0 (group 128) on the device: fills out_qweight int32 [M, K/8] and out_scale fp16 [M, K/128]."""
+    _ops.q4_0_quantize(input, out_qweight, out_scale)

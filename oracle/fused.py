@@ -1,0 +1,14 @@
+"""CPU oracle (test infrastructure only) of the residual-add + RMSNorm front end of the reference's fused decode
+GEMVs, restating the step-by-step check of tests/test_resadd_norm_gemv_int4.py:41-59:
+    s = hidden + residual (fp32);  residual' = s -> 16 bit;  normed = s * rsqrt(mean(s^2) + eps) * weight -> 16 bit.
+The GEMV that follows consumes `normed` as stored (16 bit), through oracle.int4.linear / oracle.fp8.linear_tensor.
+"""
+import torch
+
+
+def resadd_rmsnorm(hidden: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float):
+    dt = hidden.dtype
+    s = hidden.float() + residual.float()
+    inv = torch.rsqrt(s.pow(2).mean(dim=-1, keepdim=True) + eps)
+    normed = s * inv * norm_weight.float()
+    return s.to(dt), normed.to(dt)

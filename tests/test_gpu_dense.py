@@ -267,3 +267,40 @@ def test_q4_0_quantize_bit_exact(e, M, K, dtype):
         out = torch.empty(4, M, dtype=dtype, device=DEV)
         e.esimd_gemm_int4_pgrp(a.to(DEV), q, s.to(dtype), out)
         assert_close(out, int4.linear(a, rq, rs.to(dtype)), what="linear on device-quantised weights")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("N,K", [(16, 128), (256, 512), (512, 2048), (128, 4096), (256, 3072)])
+def test_resadd_norm_gemv_fused_ops(e, N, K, dtype):
+    """esimd_resadd_norm_gemv_{int4,fp8}_pert and the two-matrix variant (shapes of tests/test_resadd_norm_gemv_int4.py:62-69):
+    residual updated in place, normed_out and the GEMV outputs against the step-by-step oracle."""
+    from oracle import fused
+    g = torch.Generator().manual_seed(42 + N)
+    hidden = torch.randn(1, K, generator=g).to(dtype)
+    residual = torch.randn(1, K, generator=g).to(dtype)
+    nw = (torch.randn(K, generator=g) * 0.1 + 1.0).to(dtype)
+    ref_res, ref_normed = fused.resadd_rmsnorm(hidden, residual, nw, 1e-6)
+    # INT4
+    q, s = _rand_int4(N, K, dtype, N + K)
+    res_d, normed_d = residual.to(DEV).clone(), torch.empty(1, K, dtype=dtype, device=DEV)
+    out = torch.empty(1, N, dtype=dtype, device=DEV)
+    r = e.esimd_resadd_norm_gemv_int4_pert(hidden.to(DEV), res_d, nw.to(DEV), int4.pack_nmajor_i32(q).to(DEV), s.to(DEV), out, normed_d, 1e-6)
+    assert r.data_ptr() == out.data_ptr()
+    assert torch.equal(res_d.cpu(), ref_res), "residual update must be the rounded fp32 sum"
+    assert_close(normed_d, ref_normed, what="normed_out", tol=4e-3)      # one ulp of the 16-bit type around rsqrt differences
+    assert_close(out, int4.linear(normed_d.cpu(), q, s), what=f"resadd+norm+int4 gemv N={N} K={K}")
+    # FP8 per tensor, one and two matrices
+    w = torch.randn(N, K, generator=g) * 0.05
+    wq, ws = fp8.quantize_tensor(w)
+    w2 = torch.randn(2 * N, K, generator=g) * 0.05
+    wq2, ws2 = fp8.quantize_tensor(w2)
+    res_d = residual.to(DEV).clone()
+    e.esimd_resadd_norm_gemv_fp8_pert(hidden.to(DEV), res_d, nw.to(DEV), wq.to(DEV), ws.to(DEV), out, normed_d, 1e-6)
+    assert torch.equal(res_d.cpu(), ref_res)
+    assert_close(out, fp8.linear_tensor(normed_d.cpu(), wq, ws), what="resadd+norm+fp8 gemv")
+    res_d = residual.to(DEV).clone()
+    o1 = torch.empty(1, 2 * N, dtype=dtype, device=DEV)
+    e.esimd_resadd_norm_gemv2_fp8_pert(hidden.to(DEV), res_d, nw.to(DEV), wq.to(DEV), ws.to(DEV), out, wq2.to(DEV), ws2.to(DEV), o1, 1e-6)
+    assert torch.equal(res_d.cpu(), ref_res)
+    assert_close(out, fp8.linear_tensor(normed_d.cpu(), wq, ws), what="gemv2 / 0")
+    assert_close(o1, fp8.linear_tensor(normed_d.cpu(), wq2, ws2), what="gemv2 / 1")
