@@ -102,6 +102,14 @@ B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, in
 B2Q_API int b2q_resadd_rmsnorm(const void* hidden, void* residual, const void* norm_weight, void* normed_out,
                        int act_dtype, int64_t M, int64_t K, float eps, void* stream);
 
+/* Gated RMSNorm, the step the reference fuses in front of the GDN out_proj GEMV
+ * (esimd_norm_gemv_fp8_pert / _fp8_blockscale / _int4_pert, csrc/xpu/torch_extension.cc:117-121 and
+ * csrc/xpu/esimd_kernels/norm_gemv_fused.h, norm_gemv_int4.h):  per row of x [rows, V]
+ *   out = x * rsqrt(mean(x^2) + eps) * norm_weight * silu(z)   (fp32, one rounding to act_dtype).
+ * x, z, out contiguous [rows, V], norm_weight [V].  The GEMV then runs on out viewed as [1, rows * V]. */
+B2Q_API int b2q_gated_rmsnorm(const void* x, const void* z, const void* norm_weight, void* out, int act_dtype,
+                      int64_t rows, int64_t V, float eps, void* stream);
+
 /* GGML Q4_0 quantisation with group 128, the load-time step that produces b2q_linear_int4's inputs:
  * qweight int32 [M, K/8] (B2Q_W4_NMAJOR), scale fp16 [M, K/128] = signed group maximum / -8,
  * q = clamp(int(x / scale_fp32 + 8.5), 0, 15).  x is bf16 or fp16 [M, K] with row pitch ldx.

@@ -26,6 +26,7 @@ int act_prep(const void*, bool, int64_t, const int32_t*, int, void*, float*, int
 int act_split_fp8(const void*, bool, int64_t, void*, float*, int64_t, int, cudaStream_t);
 int quantize_q4_0(const void*, bool, int64_t, void*, void*, int64_t, int64_t, cudaStream_t);
 int resadd_rmsnorm(const void*, void*, const void*, void*, bool, int64_t, int, float, cudaStream_t);
+int gated_rmsnorm(const void*, const void*, const void*, void*, bool, int, int, float, cudaStream_t);
 int act_split_i8(const void*, bool, int64_t, void*, float*, float*, int64_t, int, cudaStream_t);
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -115,6 +116,15 @@ int b2q_resadd_rmsnorm(const void* hidden, void* residual, const void* norm_weig
   if (M > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if (!aligned16(hidden) || !aligned16(residual) || !aligned16(norm_weight) || !aligned16(normed_out)) return B2Q_ERR_ALIGN;
   return resadd_rmsnorm(hidden, residual, norm_weight, normed_out, act_dtype == B2Q_BF16, M, (int)K, eps, (cudaStream_t)stream);
+}
+
+int b2q_gated_rmsnorm(const void* x, const void* z, const void* norm_weight, void* out, int act_dtype, int64_t rows, int64_t V,
+                      float eps, void* stream) {
+  if (!x || !z || !norm_weight || !out) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (rows < 0 || V <= 0) return B2Q_ERR_SHAPE;
+  if (rows > INT32_MAX || V > INT32_MAX) return B2Q_ERR_LIMIT;
+  return gated_rmsnorm(x, z, norm_weight, out, act_dtype == B2Q_BF16, (int)rows, (int)V, eps, (cudaStream_t)stream);
 }
 
 void b2q_set_force_kernel(int which) { tls().force_kernel = which; }

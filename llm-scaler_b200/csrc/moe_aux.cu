@@ -883,4 +883,46 @@ int resadd_rmsnorm(const void* hidden, void* residual, const void* weight, void*
   return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
 }
 
+// ---------------------------------------------------------------------------
+// Gated RMSNorm in front of a decode GEMV (first half of the reference's esimd_norm_gemv_* kernels,
+// csrc/xpu/esimd_kernels/norm_gemv_fused.h, norm_gemv_int4.h):  per row of x [rows, V]
+//   out = x * rsqrt(mean(x^2) + eps) * weight * silu(z),   all in fp32, one rounding to the activation type
+// (the check of tests/test_fp8_blockscale_fusions.py:81-100).  One warp per row.
+template <bool BF16>
+__global__ void gated_rmsnorm_kernel(const void* __restrict__ x, const void* __restrict__ z, const void* __restrict__ weight,
+                                     void* __restrict__ out, int rows, int V, float eps) {
+  using T = typename Act<BF16>::T;
+  grid_dep_wait();
+  grid_dep_release();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const T* xr = reinterpret_cast<const T*>(x) + (int64_t)row * V;
+  const T* zr = reinterpret_cast<const T*>(z) + (int64_t)row * V;
+  const T* w = reinterpret_cast<const T*>(weight);
+  T* o = reinterpret_cast<T*>(out) + (int64_t)row * V;
+  float ss = 0.f;
+  for (int k = lane; k < V; k += 32) { const float v = Act<BF16>::to_f(xr[k]); ss = fmaf(v, v, ss); }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  const float inv = rsqrtf(ss / (float)V + eps);
+  for (int k = lane; k < V; k += 32) {
+    const float g = Act<BF16>::to_f(zr[k]);
+    const float silu = g / (1.f + __expf(-g));
+    o[k] = Act<BF16>::from_f(Act<BF16>::to_f(xr[k]) * inv * Act<BF16>::to_f(w[k]) * silu);
+  }
+}
+
+int gated_rmsnorm(const void* x, const void* z, const void* weight, void* out, bool bf16, int rows, int V, float eps, cudaStream_t st) {
+  if (rows == 0) return B2Q_OK;
+  const int wpb = 4;
+  const bool overlap = tls().overlap_mode > 0;
+  const dim3 grid((rows + wpb - 1) / wpb), block(wpb * 32);
+  cudaError_t e;
+  if (bf16) e = launch_overlapped(gated_rmsnorm_kernel<true>, grid, block, 0, st, overlap, x, z, weight, out, rows, V, eps);
+  else e = launch_overlapped(gated_rmsnorm_kernel<false>, grid, block, 0, st, overlap, x, z, weight, out, rows, V, eps);
+  note_launch("gated_rmsnorm");
+  return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
+}
+
 }  // namespace b2q

@@ -17,6 +17,7 @@ from .ops import (  # noqa: F401
     to_cutlass_nmajor_int4, cutlass_nmajor_int4_to_signed, prepare_cutlass_nmajor_int4_weight, precompute_moe_route,
     moe_silu_mul_int4, moe_route_gather_int4, moe_gemm_int4_nmajor, moe_prefill_full_int4, moe_topk_softmax,
     esimd_resadd_norm_gemv_fp8_pert, esimd_resadd_norm_gemv_int4_pert, esimd_resadd_norm_gemv2_fp8_pert, q4_0_quantize,
+    esimd_norm_gemv_fp8_pert, esimd_norm_gemv_fp8_blockscale, esimd_norm_gemv_int4_pert,
 )
 
 launch_count = _lib.launch_count

@@ -112,6 +112,20 @@ def resadd_rmsnorm(hidden_states, residual, norm_weight, normed_out, eps):
                                           L.dt(hidden_states), M, K, float(eps), L.stream(hidden_states)))
 
 
+def gated_rmsnorm(x, z, norm_weight, eps):
+    """rmsnorm(x) * norm_weight * silu(z) per row of x [rows, V]; returns a new [1, rows * V] tensor."""
+    L.require_cuda(x, z, norm_weight)
+    _chk(x.dim() == 2 and x.dtype in (torch.bfloat16, torch.float16), "x must be 2-D bf16 / fp16")
+    rows, V = x.shape
+    _chk(z.dtype == x.dtype and tuple(z.shape) == (rows, V) and x.is_contiguous() and z.is_contiguous(), "x and z must be contiguous [rows, V]")
+    _chk(norm_weight.dtype == x.dtype and norm_weight.numel() == V and norm_weight.is_contiguous(), "norm_weight must be a contiguous [V] tensor")
+    out = torch.empty(1, rows * V, dtype=x.dtype, device=x.device)
+    with L.on_device(x):
+        L.check(L.lib.b2q_gated_rmsnorm(x.data_ptr(), z.data_ptr(), norm_weight.data_ptr(), out.data_ptr(), L.dt(x), rows, V,
+                                         float(eps), L.stream(x)))
+    return out
+
+
 def q4_0_quantize(input, out_qweight, out_scale):
     """GGML Q4_0, group 128: fills out_qweight int32 [M, K/8] and out_scale fp16 [M, K/128] in place."""
     L.require_cuda(input, out_qweight, out_scale)

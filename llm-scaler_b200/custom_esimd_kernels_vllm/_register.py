@@ -211,6 +211,23 @@ _op(NS, "esimd_resadd_norm_gemv_int4_pert(Tensor hidden_states, Tensor residual,
 _op(NS, "esimd_resadd_norm_gemv2_fp8_pert(Tensor hidden_states, Tensor residual, Tensor norm_weight, Tensor w0, Tensor s0, "
         "Tensor o0, Tensor w1, Tensor s1, Tensor o1, float eps) -> Tensor", _resadd_norm_gemv2_fp8_pert)
 
+# gated RMSNorm + decode GEMV (reference: ops.py:492-565, torch_extension.cc:117-121)
+def _norm_gemv(mode):
+    def fn(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps):
+        if tuple(x.shape) != (HV, V):
+            raise RuntimeError("b2q: x must be [HV, V]")
+        normed = I.gated_rmsnorm(x, z, norm_weight, eps)
+        if mode == "int4":
+            return I.linear_int4(normed, gemv_weight, gemv_scale, output)
+        return I.linear_fp8(normed, gemv_weight, gemv_scale, output, mode)
+    return fn
+
+
+_NORM_GEMV = "(Tensor x, Tensor z, Tensor norm_weight, Tensor gemv_weight, Tensor gemv_scale, Tensor output, int HV, int V, float eps) -> Tensor"
+_op(NS, "esimd_norm_gemv_fp8_pert" + _NORM_GEMV, _norm_gemv(L.SCALE_TENSOR))
+_op(NS, "esimd_norm_gemv_fp8_blockscale" + _NORM_GEMV, _norm_gemv(L.SCALE_BLOCK128))
+_op(NS, "esimd_norm_gemv_int4_pert" + _NORM_GEMV, _norm_gemv("int4"))
+
 # load-time quantiser (reference: csrc/xpu/torch_extension_q4_0.cc:78-83, module q4_0_quant_ops)
 def _q4_0_quantize(input, out_qweight, out_scale):
     I.q4_0_quantize(input, out_qweight, out_scale)

@@ -218,3 +218,18 @@ def esimd_resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s
 def q4_0_quantize(input, out_qweight, out_scale):
     """GGML Q4_0 (group 128) on the device: fills out_qweight int32 [M, K/8] and out_scale fp16 [M, K/128]."""
     _ops.q4_0_quantize(input, out_qweight, out_scale)
+
+
+def esimd_norm_gemv_fp8_pert(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps):
+    """output[1, N] = (rmsnorm(x) * norm_weight * silu(z)).flatten() @ dequant(gemv_weight)^T, per-tensor FP8 scale."""
+    return _ops.esimd_norm_gemv_fp8_pert(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps)
+
+
+def esimd_norm_gemv_fp8_blockscale(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps):
+    """As esimd_norm_gemv_fp8_pert with 128 x 128 block scales."""
+    return _ops.esimd_norm_gemv_fp8_blockscale(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps)
+
+
+def esimd_norm_gemv_int4_pert(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps):
+    """As esimd_norm_gemv_fp8_pert with INT4 g=128 weights."""
+    return _ops.esimd_norm_gemv_int4_pert(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps)

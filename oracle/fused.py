@@ -12,3 +12,12 @@ def resadd_rmsnorm(hidden: torch.Tensor, residual: torch.Tensor, norm_weight: to
     inv = torch.rsqrt(s.pow(2).mean(dim=-1, keepdim=True) + eps)
     normed = s * inv * norm_weight.float()
     return s.to(dt), normed.to(dt)
+
+
+def gated_rmsnorm(x: torch.Tensor, z: torch.Tensor, norm_weight: torch.Tensor, eps: float):
+    """rmsnorm(x) * norm_weight * silu(z) per row in fp32, one rounding; returns [1, rows * V]
+    (tests/test_fp8_blockscale_fusions.py:91-96)."""
+    xf = x.float()
+    n = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
+    n = n * norm_weight.float() * torch.nn.functional.silu(z.float())
+    return n.to(x.dtype).flatten().unsqueeze(0)

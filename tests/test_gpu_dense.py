@@ -304,3 +304,31 @@ def test_resadd_norm_gemv_fused_ops(e, N, K, dtype):
     assert torch.equal(res_d.cpu(), ref_res)
     assert_close(out, fp8.linear_tensor(normed_d.cpu(), wq, ws), what="gemv2 / 0")
     assert_close(o1, fp8.linear_tensor(normed_d.cpu(), wq2, ws2), what="gemv2 / 1")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("HV,V,N", [(8, 128, 2048), (16, 128, 512), (4, 256, 1000)])
+def test_gated_norm_gemv_fused_ops(e, HV, V, N, dtype):
+    """esimd_norm_gemv_{fp8_pert, fp8_blockscale, int4_pert} (first shape: tests/test_fp8_blockscale_fusions.py:81-100)."""
+    from oracle import fused
+    g = torch.Generator().manual_seed(HV + V + N)
+    core = (torch.randn(HV, V, generator=g) * 0.3).to(dtype)
+    gate = (torch.randn(HV, V, generator=g) * 0.3).to(dtype)
+    nw = (torch.randn(V, generator=g) * 0.1 + 1.0).to(dtype)
+    K = HV * V
+    normed = fused.gated_rmsnorm(core, gate, nw, 1e-6)
+    got = e._impl.gated_rmsnorm(core.to(DEV), gate.to(DEV), nw.to(DEV), 1e-6)
+    assert_close(got, normed, what="gated rmsnorm", tol=4e-3)
+    normed_d = got.cpu()
+    w = torch.randn(N, K, generator=g) * 0.2
+    out = torch.empty(1, N, dtype=dtype, device=DEV)
+    wq, ws = fp8.quantize_tensor(w)
+    e.esimd_norm_gemv_fp8_pert(core.to(DEV), gate.to(DEV), nw.to(DEV), wq.to(DEV), ws.to(DEV), out, HV, V, 1e-6)
+    assert_close(out, fp8.linear_tensor(normed_d, wq, ws), what="gated norm + fp8 pert")
+    if N % 128 == 0:
+        wqb, wsb = fp8.quantize_block(w)
+        e.esimd_norm_gemv_fp8_blockscale(core.to(DEV), gate.to(DEV), nw.to(DEV), wqb.to(DEV), wsb.to(DEV), out, HV, V, 1e-6)
+        assert_close(out, fp8.linear_block_w8a16(normed_d, wqb, wsb), what="gated norm + fp8 block")
+    q, s = _rand_int4(N, K, dtype, N)
+    e.esimd_norm_gemv_int4_pert(core.to(DEV), gate.to(DEV), nw.to(DEV), int4.pack_nmajor_i32(q).to(DEV), s.to(DEV), out, HV, V, 1e-6)
+    assert_close(out, int4.linear(normed_d, q, s), what="gated norm + int4")
