@@ -60,6 +60,7 @@ struct UmmaWoParams {
   float* sk_partials;        // balanced mode: [2 * grid][TOK][128] fp32 partial sums of cut strips
   int* sk_counters;          // balanced mode: arrivals per strip, zero between launches
   int sk_grid;               // host side only: CTAs of a balanced launch
+  int tiles_on_y;            // grouped launches: tile index on blockIdx.y, strip on blockIdx.x (see the kernel)
   int magic;                 // INT4: fp16 magic-number transform; x was permuted / scaled by the pre-pass
   const int32_t* tiles; const int32_t* expert_offsets; const int32_t* out_map;
   int w_rows_per_expert;     // tensor-map rows per expert: N (N-major) or K/8 (K-major)
@@ -221,11 +222,15 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   // conversion into tensor memory and all set-up overlap the tail of whatever ran before.
   // Grouped launches read a tile list the previous kernel built, so they wait here.
   grid_dep_release();
-  int tok0 = blockIdx.x * TOK, xrow0 = 0, M = p.M, expert = 0;
+  // Grid axes: dense launches put the token tile on x (neighbouring CTAs share a weight strip), grouped launches
+  // the strip (neighbouring CTAs share an expert's activation tile, whose rows would otherwise be re-read from
+  // DRAM once per strip: the gathered activations of a MoE layer do not fit in L2 next to the weights).
+  const int tile_idx = p.tiles_on_y ? blockIdx.y : blockIdx.x, strip_idx = p.tiles_on_y ? blockIdx.x : blockIdx.y;
+  int tok0 = tile_idx * TOK, xrow0 = 0, M = p.M, expert = 0;
   if (p.tiles) {
     grid_dep_wait();
-    if ((int)blockIdx.x >= p.tiles[0]) return;
-    const int2 td = reinterpret_cast<const int2*>(p.tiles + 4)[blockIdx.x];
+    if (tile_idx >= p.tiles[0]) return;
+    const int2 td = reinterpret_cast<const int2*>(p.tiles + 4)[tile_idx];
     expert = td.x; tok0 = td.y;
     xrow0 = p.expert_offsets[expert];
     M = p.expert_offsets[expert + 1] - xrow0;
@@ -247,7 +252,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   auto next_segment = [&](Segment& sg) -> bool {
     if (u >= u1) return false;
     if (!balanced) {
-      sg.n0 = blockIdx.y * 128; sg.c_begin = 0; sg.nk = p.K / 64; sg.strip = blockIdx.y; sg.part = 0; sg.slot = 0;
+      sg.n0 = strip_idx * 128; sg.c_begin = 0; sg.nk = p.K / 64; sg.strip = strip_idx; sg.part = 0; sg.slot = 0;
       u = u1;
       return true;
     }
@@ -746,7 +751,9 @@ static int plan_balanced(UmmaWoParams& p, const UmmaGroupArgs& a, int M, int N, 
 static int pick_tok(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256))); }
 
 template <int WK, bool BF16, int TOK, bool FAST>
-static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWoParams& p, int token_tiles, cudaStream_t st) {
+static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWoParams& p_in, int token_tiles, cudaStream_t st) {
+  UmmaWoParams p = p_in;
+  p.tiles_on_y = (p.tiles && token_tiles <= 65535) ? 1 : 0;      // gridDim.y is limited to 65535
   using Cfg = UmmaCfg<TOK>;
   auto kern = umma_wo_kernel<WK, BF16, TOK, FAST>;
   static thread_local bool configured[16] = {false};
@@ -757,6 +764,7 @@ static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWo
     if (dev < 16) configured[dev] = true;
   }
   dim3 grid(token_tiles, (p.N + 127) / 128, 1);
+  if (p.tiles_on_y) grid = dim3((p.N + 127) / 128, token_tiles, 1);
   if (p.sk_sps > 0) grid = dim3(p.sk_grid, 1, 1);
   const bool overlap = tls().overlap_mode > 0 && p.overlap_ok;
   if (launch_overlapped(kern, grid, dim3(Cfg::THREADS), Cfg::SMEM, st, overlap, tw, tx, p) != cudaSuccess) return B2Q_ERR_CUDA;
