@@ -158,6 +158,8 @@ CASES = {
     "c1_int4_m16_4096": case_c1,
     "c3_fp8_block_w8a16_m4096": case_c3_w8a16,
     "c3_fp8_block_w8a8_m4096": case_c3_w8a8,
+    "c5_m1": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 1),
+    "c5_m8": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 8),
     "c5_m64": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 64),
     "c5_m2048": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 2048),
     "c4_moe_int4_t4096": case_c4,

@@ -178,8 +178,9 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   ua.s_stride_n = s_stride_n; ua.s_stride_g = s_stride_g;
   ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
   const bool umma_ok = umma_w4_supported(ua);
-  // the int8 tensor-core path (umma_w4_i8.cu): decode shapes, N-major nibbles, scratch available; on request only
-  if (force == 5 && umma_ok && !kmajor && M <= 16 && workspace && aligned16(workspace) &&
+  // the int8 tensor-core path (umma_w4_i8.cu): decode shapes, N-major nibbles, scratch available; on request, or
+  // where it measured fastest
+  if ((force == 5 || (force == 0 && umma_w4_i8_preferred(M, N, K))) && umma_ok && !kmajor && M <= 16 && workspace && aligned16(workspace) &&
       workspace_bytes >= b2q_linear_workspace_bytes(M, N, K)) {
     uint8_t* wsb = reinterpret_cast<uint8_t*>(workspace);
     float* inv = reinterpret_cast<float*>(wsb + align_up((size_t)umma_w4_i8_rows(M) * (size_t)K, 256));

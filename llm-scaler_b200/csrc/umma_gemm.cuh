@@ -70,6 +70,7 @@ struct UmmaW4I8Args {
   void* partials; size_t partial_bytes;                        // umma_w4_i8_partial_bytes(), or null: strips are not cut
 };
 int umma_w4_i8_rows(int64_t M);
+bool umma_w4_i8_preferred(int64_t M, int64_t N, int64_t K);
 size_t umma_w4_i8_partial_bytes();
 int umma_w4_i8_linear(const UmmaW4I8Args& a, cudaStream_t st);
 

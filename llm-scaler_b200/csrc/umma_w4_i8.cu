@@ -15,11 +15,11 @@
 // Work is shared out like in umma_w8_direct.cu: one CTA per strip of h <= 128 rows, h chosen for equal load
 // per SM, or, when there are few strips, strips cut along k with ordered partial sums.
 //
-// Status: parity-tested, not dispatched automatically.  Measured on B200 it streams 1.2-1.9 TB/s, on a level with
-// the two 16-bit kernels and ahead of them only for few rows and very long k ([8192 x 28672], M <= 8: +8 %): with
+// Status: measured on B200 it streams 1.2-1.9 TB/s, on a level with the two 16-bit kernels and ahead of them only
+// for few rows and a long k ([8192 x 28672] at M <= 8), which is where it is dispatched (umma_w4_i8_preferred): with
 // one accumulator per group of 128 k, only four groups (32 KB of weights) fit in a CTA's tensor memory between the
 // transform and the promotion warps, and the barrier hand-offs along that chain, not arithmetic, set the pace.
-// b2q_set_force_kernel(5) selects it.
+// b2q_set_force_kernel(5) selects it for every decode shape.
 //
 // Reference counterpart: esimd_gemv_int4 / esimd_gemm_int4_pgrp
 // (vllm/custom-esimd-kernels-vllm/csrc/xpu/esimd_kernels/gemv_int4.h, gemm_int4_pgrp.h), GGML N-major weights.
@@ -425,6 +425,12 @@ static int* w4i_counter_bank() {
 
 // term rows of the activation buffer: three terms x (M rounded up to 8), as a legal MMA N
 int umma_w4_i8_rows(int64_t M) { return M <= 8 ? 32 : 64; }
+
+// Shapes on which this kernel measured faster than both 16-bit kernels: few rows (strips get cut along k, which the
+// mma.sync kernel cannot do) and a long k.  [8192 x 28672] at M <= 8: 58-65 us against 94 us (mma.sync) and 71 us (tcgen05, 16 bit).
+bool umma_w4_i8_preferred(int64_t M, int64_t N, int64_t K) {
+  return M <= 8 && ((N + 127) / 128) * 2 <= w4i_sm_count() && N * K >= ((int64_t)1 << 27);
+}
 // fp32 partial sums of cut strips: [two CTAs per SM][2 slots][16][128]
 size_t umma_w4_i8_partial_bytes() { return (size_t)w4i_sm_count() * 2 * 2 * 16 * 128 * sizeof(float); }
 
