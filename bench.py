@@ -372,8 +372,6 @@ def main():
     if args.case:
         import bench_extra
         import custom_esimd_kernels_vllm as e
-        if os.environ.get("B2Q_OVERLAP_MODE"):
-            e.set_overlap_mode(int(os.environ["B2Q_OVERLAP_MODE"]))
         print(json.dumps({"case": args.case, **bench_extra.run(e, torch.device("cuda", 0), only=args.case)}))
     elif args.impl == "reference":
         run_reference(args)

@@ -173,6 +173,12 @@ def run(e, dev, only=None):
         if only is not None and name != only:
             continue
         g = torch.Generator(device=dev).manual_seed(7)
-        out[name] = fn(e, dev, g, pk)
+        # the weights of every case are written once, before the timed calls: the serving contract of overlap mode 2
+        # (a GEMM may stream weights while the kernel before it drains); an explicit B2Q_OVERLAP_MODE wins
+        e.set_overlap_mode(int(os.environ.get("B2Q_OVERLAP_MODE", "2")))
+        try:
+            out[name] = fn(e, dev, g, pk)
+        finally:
+            e.set_overlap_mode(1)
         torch.cuda.empty_cache()
     return out

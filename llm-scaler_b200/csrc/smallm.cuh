@@ -116,7 +116,12 @@ __global__ void __launch_bounds__(128) smallm_kernel(const SmallMParams p) {
   const uint8_t* wbase = p.w;
   int64_t sbase = 0;
   int tok0 = blockIdx.y * (NT * 8);
+  // The next kernel of the stream may start at once; this one waits for earlier kernels only before it first reads
+  // something they may have written: the tile list (grouped launches, here) or the activations (dense launches, after
+  // the first weight stages are already in flight).  Both are no-ops for a plain launch.
+  grid_dep_release();
   if (p.tiles) {
+    grid_dep_wait();
     if ((int)blockIdx.y >= p.tiles[0]) return;
     const int2 td = reinterpret_cast<const int2*>(p.tiles + 4)[blockIdx.y];
     const int e = td.x;
@@ -170,6 +175,7 @@ __global__ void __launch_bounds__(128) smallm_kernel(const SmallMParams p) {
 
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) { if (s < n_my) issue(s); cp_async_commit(); }
+  if (!p.tiles) grid_dep_wait();
 
   for (int it = 0; it < n_my; ++it) {
     cp_async_wait<STAGES - 2>();
@@ -356,7 +362,10 @@ inline int smallm_launch_one(const SmallMParams& p, int m_max, int n_tiles_cap, 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return B2Q_ERR_CUDA;
   }
   dim3 grid((p.N + ROWS - 1) / ROWS, p.tiles ? n_tiles_cap : (m_max + NT * 8 - 1) / (NT * 8), 1);
-  kern<<<grid, 128, smem, st>>>(p);
+  // overlap with the previous kernel only when the caller has declared the weights static (overlap mode 2): this
+  // kernel has no pre-pass of its own in front of it that would order it behind whatever wrote them
+  const bool overlap = tls().overlap_mode == 2 && !p.tiles;
+  if (launch_overlapped(kern, grid, dim3(128), (size_t)smem, st, overlap, p) != cudaSuccess) return B2Q_ERR_CUDA;
   note_launch("smallm");
   return launch_status();
 }
