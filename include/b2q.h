@@ -265,7 +265,8 @@ B2Q_API int b2q_device_status(int* out);
 
 /* Kernel selection override for benchmarking: 0 = automatic, 1 = the mma.sync streaming kernel,
  * 2 = the tcgen05 kernel with 16-bit operands, 3 = the same without activation pre-pass,
- * 4 = the same with one CTA per strip (no strip cutting), 5 = INT4 decode on the int8 MMA.  */
+ * 4 = the same with one CTA per strip (no strip cutting), 5 = INT4 decode on the int8 MMA,
+ * 6 = the CTA-pair (cta_group::2) variant of the W8A8 GEMM.                                  */
 B2Q_API void b2q_set_force_kernel(int which);
 /* Overlap of consecutive kernels on a stream (programmatic dependent launch), per calling thread:
  *   0  off: every kernel starts after the one before it has completed.

@@ -231,3 +231,22 @@ def test_int4_decode_on_the_int8_mma(e, M, N, K, dtype):
         assert_close(out, ref, what=f"int8-MMA int4 M={M} N={N} K={K}")
     finally:
         e.set_force_kernel(2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (300, 512, 1024), (1000, 1024, 1024), (64, 256, 5120)])
+def test_fp8_block_w8a8_cta_pair_kernel(e, M, N, K):
+    """The opt-in CTA-pair variant of the W8A8 GEMM (cluster of two, tcgen05 cta_group::2: one MMA over 256 weight
+    rows, each CTA loading its own rows and half of the token tile) against the same oracle as the default kernel."""
+    g = torch.Generator().manual_seed(M + N + K)
+    w = torch.randn(N, K, generator=g) * 0.3
+    wq, ws = fp8.quantize_block(w)
+    x = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    xq, xs = fp8.quantize_act_1x128(x)
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    e.set_force_kernel(6)
+    try:
+        e.gemm_fp8_block_w8a8(xq.to(DEV), xs.to(DEV), wq.to(DEV), ws.to(DEV), out)
+        assert e.last_kernel() == "umma_w8a8_pair"
+        assert_close(out, fp8.linear_block_w8a8(xq, xs, wq, ws), what=f"w8a8 pair M={M} N={N} K={K}")
+    finally:
+        e.set_force_kernel(2)
