@@ -262,6 +262,12 @@ B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
 /* Code of the first bounded device-side wait that expired since the library was loaded
  * (0 = none).  Synchronises the device; meant for tests and post-mortems.       */
 B2Q_API int b2q_device_status(int* out);
+/* Clears that code (after a post-mortem, or after the self-test below).                        */
+B2Q_API int b2q_device_status_reset(void);
+/* Self-test of the bounded waits: launches one CTA that waits, with a limit of about a millisecond,
+ * on a barrier nobody arrives on.  The wait gives up, records `code` (> 0) as the device status and
+ * writes 1 to *gave_up (a DEVICE int); the context stays usable.  Nothing faults or hangs.       */
+B2Q_API int b2q_selftest_bounded_wait(int code, int* gave_up, void* stream);
 
 /* Kernel selection override for benchmarking: 0 = automatic, 1 = the mma.sync streaming kernel,
  * 2 = the tcgen05 kernel with 16-bit operands, 3 = the same without activation pre-pass,

@@ -387,6 +387,14 @@ int b2q_device_status(int* out) {
   return umma_read_status(out);
 }
 
+int b2q_device_status_reset(void) { return umma_reset_status(); }
+
+int b2q_selftest_bounded_wait(int code, int* gave_up, void* stream) {
+  if (!gave_up) return B2Q_ERR_NULL;
+  if (code <= 0) return B2Q_ERR_SHAPE;
+  return umma_selftest_bounded_wait(code, gave_up, (cudaStream_t)stream);
+}
+
 // Shared tail of the grouped GEMMs once the kernel family is chosen: optional row gather in
 // front of the tcgen05 kernel, optional SiLU*mul behind either kernel.
 struct GroupedPlan {

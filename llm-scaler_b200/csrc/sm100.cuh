@@ -47,7 +47,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // timeout releases all the others; `status` is a global word the host can read.  The clock
 // and the abort flag are looked at once every 128 polls so the spin itself stays two
 // instructions long.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          long long limit_ticks = WAIT_LIMIT_TICKS) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (;;) {
@@ -55,7 +56,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     for (int i = 0; i < 128; ++i)
       if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_TICKS) {
+    if (clock64() - t0 > limit_ticks) {
       *abort_flag = 1;
       atomicCAS(status, 0, code);
       return false;

@@ -662,9 +662,35 @@ static int* status_ptr() {
   return ptr[dev];
 }
 
+// Self-test of the bounded-wait machinery: one CTA waits on an mbarrier that nobody ever arrives on, with a limit of
+// about a millisecond instead of two seconds.  The wait must give up, record `code` in the status word and return;
+// the context stays usable.  Nothing here faults or spins without bound.
+__global__ void bounded_wait_selftest_kernel(int* status, int code, long long limit_ticks, int* gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) { sm100::mbar_init(sm100::smem_u32(&bar), 1); abort_flag = 0; sm100::fence_barrier_init(); }
+  __syncthreads();
+  const bool ok = sm100::mbar_wait(sm100::smem_u32(&bar), 0, &abort_flag, status, code, limit_ticks);
+  if (threadIdx.x == 0) *gave_up = ok ? 0 : 1;
+}
+
 int w8a8_read_status(int* out);
 int w8d_read_status(int* out);
 int w4i_read_status(int* out);
+
+int umma_selftest_bounded_wait(int code, int* gave_up_dev, cudaStream_t st) {
+  int* p = status_ptr();
+  if (!p) return B2Q_ERR_CUDA;
+  bounded_wait_selftest_kernel<<<1, 64, 0, st>>>(p, code, 2000000LL, gave_up_dev);     // ~1 ms at 1.9 GHz
+  note_launch("bounded_wait_selftest");
+  return launch_status();
+}
+
+int umma_reset_status() {
+  int* p = status_ptr();
+  if (!p) return B2Q_ERR_CUDA;
+  return cuda_status(cudaMemset(p, 0, sizeof(int)));
+}
 
 int umma_read_status(int* out) {
   int* p = status_ptr();

@@ -88,5 +88,8 @@ size_t umma_balanced_ws_bytes(int64_t M);
 
 // First device-side wait timeout recorded since the library was loaded (0 = none).  Synchronises.
 int umma_read_status(int* out);
+// Clears the status word of the tcgen05 weight-only kernels; launches the bounded-wait self-test (see the kernel).
+int umma_reset_status();
+int umma_selftest_bounded_wait(int code, int* gave_up_dev, cudaStream_t st);
 
 }  // namespace b2q

@@ -45,6 +45,8 @@ _SIGS = {
     "b2q_moe_combine": (i32, [vp, vp, i32, vp, vp, i32, i64, i32, i64, i32, vp]),
     "b2q_moe_gemm_workspace_bytes": (sz, [i64, i32, i64, i64, i32, i32]),
     "b2q_device_status": (i32, [vp]),
+    "b2q_device_status_reset": (i32, []),
+    "b2q_selftest_bounded_wait": (i32, [i32, vp, vp]),
     "b2q_moe_gemm_int4": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
                                 i64, i64, i64, i32, i32, vp, sz, vp]),
     "b2q_moe_gemm_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
@@ -138,6 +140,17 @@ def device_status() -> int:
     v = C.c_int(0)
     check(lib.b2q_device_status(C.addressof(v)))
     return int(v.value)
+
+
+def device_status_reset() -> None:
+    check(lib.b2q_device_status_reset())
+
+
+def selftest_bounded_wait(code: int = 999) -> bool:
+    """Runs the bounded-wait self-test on the current device; True when the wait gave up as it must."""
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    check(lib.b2q_selftest_bounded_wait(int(code), flag.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    return int(flag.item()) == 1
 
 
 def set_force_kernel(which: int) -> None:

@@ -250,3 +250,21 @@ def test_fp8_block_w8a8_cta_pair_kernel(e, M, N, K):
         assert_close(out, fp8.linear_block_w8a8(xq, xs, wq, ws), what=f"w8a8 pair M={M} N={N} K={K}")
     finally:
         e.set_force_kernel(2)
+
+
+def test_bounded_wait_gives_up_and_reports(e):
+    """Failure detection without a fault: a device-side wait on a barrier nobody arrives on runs out after its limit
+    (about a millisecond in this self-test), the kernel records its code in the status word the host reads, returns,
+    and the context is still usable for the next launch."""
+    L = e._lib
+    assert L.device_status() == 0
+    assert L.selftest_bounded_wait(code=777) is True
+    assert L.device_status() == 777
+    L.device_status_reset()
+    assert L.device_status() == 0
+    q, s = _int4(256, 512, torch.bfloat16, 3)
+    x = torch.randn(40, 512).to(torch.bfloat16)
+    out = torch.empty(40, 256, dtype=torch.bfloat16, device=DEV)
+    e.esimd_gemm_int4_pgrp(x.to(DEV), int4.pack_nmajor_u8(q).to(DEV), s.to(DEV), out)
+    assert_close(out, int4.linear(x, q, s), what="launch after an expired wait")
+    assert L.device_status() == 0
