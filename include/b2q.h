@@ -72,6 +72,9 @@ extern "C" {
 /* ---- activation functions fused into grouped GEMM epilogues ------------- */
 #define B2Q_ACT_NONE      0
 #define B2Q_ACT_SILU_MUL  1    /* out[:, j] = silu(g[:, j]) * g[:, I + j]    */
+#define B2Q_ACT_SILU_MUL_IN 2  /* INT4 grouped GEMM only: x has 2K columns (gate, then up; ldx >= 2K) and the
+                                  GEMM's input row is silu(x[:, :K]) * x[:, K:], rounded to the activation type as
+                                  B2Q_ACT_SILU_MUL would have stored it.  No output activation, no row_map.     */
 
 B2Q_API const char* b2q_strerror(int code);
 B2Q_API int b2q_version(void);

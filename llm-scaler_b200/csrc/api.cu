@@ -19,10 +19,10 @@ size_t moe_route_workspace_bytes(int64_t, int);
 int moe_route(const int32_t*, int64_t, int, int32_t*, int32_t*, int32_t*, int32_t*, void*, cudaStream_t);
 int moe_build_tiles(const int32_t*, int, int, int32_t*, cudaStream_t);
 int gather_rows(const void*, const int32_t*, int, void*, int64_t, int64_t, int, cudaStream_t);
-int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t);
+int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t, int64_t ld_in = 0);
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
-int act_prep(const void*, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
+int act_prep(const void*, bool, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
 int act_split_fp8(const void*, bool, int64_t, void*, float*, int64_t, int, cudaStream_t);
 int quantize_q4_0(const void*, bool, int64_t, void*, void*, int64_t, int64_t, cudaStream_t);
 int resadd_rmsnorm(const void*, void*, const void*, void*, bool, int64_t, int, float, cudaStream_t);
@@ -210,7 +210,7 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
     if (prep) {
       float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * (size_t)K * 2, 256));
       const int perm = w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1;
-      int rc = act_prep(x, act_dtype == B2Q_BF16, ldx, nullptr, 1, workspace, inv, M, (int)K, perm, st);
+      int rc = act_prep(x, act_dtype == B2Q_BF16, false, ldx, nullptr, 1, workspace, inv, M, (int)K, perm, st);
       if (rc) return rc;
       ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.tok_scale = inv; ua.magic = true; ua.after_prep = true;
       give_balanced_scratch(ua, workspace, M, K);
@@ -283,7 +283,7 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
   if (umma_ok && want_umma) {
     if (prep) {
       float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + align_up((size_t)M * (size_t)K * 2, 256));
-      int rc = act_prep(x, true, ldx, nullptr, 1, workspace, inv, M, (int)K, 0, st);
+      int rc = act_prep(x, true, false, ldx, nullptr, 1, workspace, inv, M, (int)K, 0, st);
       if (rc) return rc;
       ua.x = workspace; ua.ldx = K; ua.bf16 = false; ua.out_bf16 = true; ua.tok_scale = inv; ua.after_prep = true;
     }
@@ -378,7 +378,7 @@ size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int64_t K, i
   (void)gather;
   size_t b = tile_list_bytes(rows, E, 8);
   b += align_up((size_t)rows * (size_t)K * 2, 256) + align_up((size_t)rows * 4, 256);
-  if (act != B2Q_ACT_NONE) b += align_up((size_t)rows * (size_t)N * 2, 256);
+  if (act == B2Q_ACT_SILU_MUL) b += align_up((size_t)rows * (size_t)N * 2, 256);
   return b;
 }
 
@@ -417,10 +417,12 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
   if (!is16(act_dtype) || scale_dtype < 0 || scale_dtype > 2) return B2Q_ERR_DTYPE;
   if (w_layout < 0 || w_layout > 3) return B2Q_ERR_LAYOUT;
   if (group != 128) return B2Q_ERR_SHAPE;
-  if (rows < 0 || N <= 0 || K <= 0 || (K % group) != 0 || E <= 0 || ldx < K) return B2Q_ERR_SHAPE;
-  if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL) return B2Q_ERR_UNSUPPORTED;
+  const bool gated_in = act == B2Q_ACT_SILU_MUL_IN;
+  if (rows < 0 || N <= 0 || K <= 0 || (K % group) != 0 || E <= 0 || ldx < (gated_in ? 2 * K : K)) return B2Q_ERR_SHAPE;
+  if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL && !gated_in) return B2Q_ERR_UNSUPPORTED;
+  if (gated_in && row_map) return B2Q_ERR_UNSUPPORTED;
   if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0 || ldo != N / 2)) return B2Q_ERR_SHAPE;
-  if (act == B2Q_ACT_NONE && ldo < N) return B2Q_ERR_SHAPE;
+  if (act != B2Q_ACT_SILU_MUL && ldo < N) return B2Q_ERR_SHAPE;
   if (E > 1024 || rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if (row_map && row_div <= 0) return B2Q_ERR_SHAPE;
   if (!aligned16(x) || !aligned16(w) || !aligned16(workspace) || ((ldx * 2) & 15)) return B2Q_ERR_ALIGN;
@@ -432,9 +434,10 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
   const int force = tls().force_kernel;
   const GroupedPlan pl = plan_workspace(workspace, rows, E, K, row_map != nullptr);
   int32_t* tiles = reinterpret_cast<int32_t*>(pl.tiles);
-  void* gemm_out = act == B2Q_ACT_NONE ? out : pl.g;
-  const int64_t gemm_ldo = act == B2Q_ACT_NONE ? ldo : N;
-  const int32_t* gemm_out_map = act == B2Q_ACT_NONE ? out_map : nullptr;
+  const bool act_out = act == B2Q_ACT_SILU_MUL;
+  void* gemm_out = act_out ? pl.g : out;
+  const int64_t gemm_ldo = act_out ? N : ldo;
+  const int32_t* gemm_out_map = act_out ? nullptr : out_map;
   int rc;
 
   UmmaW4Args ua{};
@@ -448,7 +451,9 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
   ua.out_bf16 = bf;
   if (umma_w4_supported(ua) && want_umma) {
     // gather (if any), fp16 re-scaling and pair permutation in one pre-pass over the rows
-    rc = act_prep(x, bf, ldx, row_map, row_div, pl.xg, pl.inv, rows, (int)K, w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1, st);
+    // (with a gated input also silu(gate) * up, so that the gate_up result is read once and never re-written)
+    rc = act_prep(x, bf, gated_in, ldx, row_map, row_div, pl.xg, pl.inv, rows, (int)K,
+                  w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1, st);
     if (rc) return rc;
     ua.x = pl.xg; ua.ldx = K; ua.bf16 = false; ua.tok_scale = pl.inv; ua.magic = true;
     const int tile = umma_w4_token_tile(ua);
@@ -458,11 +463,18 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
     rc = umma_w4_linear(ua, st);
   } else {
     if (kmajor) return B2Q_ERR_UNSUPPORTED;
+    const void* xin = x;
+    int64_t ldin = ldx;
+    if (gated_in) {          // few rows per expert: activate into the scratch first, then the plain grouped kernel
+      rc = silu_mul(x, pl.xg, act_dtype, rows, K, nullptr, st, ldx);
+      if (rc) return rc;
+      xin = pl.xg; ldin = K;
+    }
     const int tile = grouped_tile(rows, E);
     rc = moe_build_tiles(expert_offsets, E, tile, tiles, st);
     if (rc) return rc;
     SmallMParams p{};
-    p.x = x; p.ldx = ldx;
+    p.x = xin; p.ldx = ldin;
     p.w = reinterpret_cast<const uint8_t*>(w); p.w_row_bytes = K / 2;
     p.scale = scale; p.scale_dtype = scale_dtype; p.s_stride_n = K / group; p.s_stride_g = 1;
     p.M = (int)rows; p.N = (int)N; p.K = (int)K;
@@ -472,7 +484,7 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
     p.out = gemm_out; p.ldo = gemm_ldo; p.out_map = gemm_out_map;
     rc = smallm_int4(p, bf, tile, (int)((rows + tile - 1) / tile + E), st);
   }
-  if (rc || act == B2Q_ACT_NONE) return rc;
+  if (rc || !act_out) return rc;
   return silu_mul(pl.g, out, act_dtype, rows, N / 2, out_map, st);
 }
 

@@ -273,15 +273,15 @@ int gather_rows(const void* src, const int32_t* idx, int div, void* dst, int64_t
 // ---------------------------------------------------------------------------
 template <bool BF16>
 __global__ void silu_mul_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t rows, int64_t I8,
-                                const int32_t* __restrict__ out_map) {
+                                const int32_t* __restrict__ out_map, int64_t ld8) {
   using A = Act<BF16>;
   using T = typename A::T;
   const int64_t total = rows * I8;
   for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
        idx += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = idx / I8, c = idx % I8;
-    const uint4 g = in[r * 2 * I8 + c];
-    const uint4 u = in[r * 2 * I8 + I8 + c];
+    const uint4 g = in[r * ld8 + c];
+    const uint4 u = in[r * ld8 + I8 + c];
     const T* gp = reinterpret_cast<const T*>(&g);
     const T* up = reinterpret_cast<const T*>(&u);
     uint4 o;
@@ -296,15 +296,17 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ in, uint4* __restrict_
   }
 }
 
-int silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, const int32_t* out_map, cudaStream_t st) {
+int silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, const int32_t* out_map, cudaStream_t st,
+             int64_t ld_in) {
   if (rows == 0) return B2Q_OK;
+  const int64_t ld8 = (ld_in > 0 ? ld_in : 2 * I) / 8;       // source row pitch in 16-byte units
   const int64_t total = rows * (I / 8);
   int64_t g = (total + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
   if (dtype == B2Q_BF16)
-    silu_mul_kernel<true><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map);
+    silu_mul_kernel<true><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map, ld8);
   else
-    silu_mul_kernel<false><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map);
+    silu_mul_kernel<false><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map, ld8);
   note_launch("silu_mul");
   return launch_status();
 }
@@ -535,9 +537,13 @@ namespace b2q {
 //   perm 0: identity      perm 1: (0,4,1,5,2,6,3,7)  nibble i at bits 4i (GGML / N-major, plain K-major)
 //                         perm 2: (0,2,4,6,1,3,5,7)  marlin-shuffled words
 // dst row r = f(src row (idx ? idx[r] / div : r)); fp16 input keeps scale 1.
-template <bool IN_BF16>
+// GATED: the source row holds 2K values, gate then up, and the row fed to the GEMM is silu(gate) * up, computed in
+// fp32 and rounded to the source type first, exactly as the separate silu_mul_kernel writes it.
+template <bool IN_BF16, bool GATED>
 __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const int32_t* __restrict__ idx, int div,
                                 __half* __restrict__ x16, float* __restrict__ inv_scale, int K, int perm, int release_early) {
+  using A = Act<IN_BF16>;
+  using T = typename A::T;
   __shared__ float red[32];
   __shared__ float sc_sh;
   // The GEMM that follows may start streaming its weights as soon as this kernel lets it.  With static
@@ -549,14 +555,42 @@ __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const i
   const int64_t r = blockIdx.x;
   const int64_t srow = idx ? (int64_t)(idx[r] / div) : r;
   const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + srow * ldx;
+  // eight consecutive source values of the row as floats that are exactly representable in the source type
+  auto load8 = [&](int k, float* f) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+    const T* e = reinterpret_cast<const T*>(&v);
+    if constexpr (GATED) {
+      const uint4 u = *reinterpret_cast<const uint4*>(row + K + k);
+      const T* ue = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float gv = A::to_f(e[j]);
+        const float sl = gv / (1.0f + expf(-gv));
+        f[j] = A::to_f(A::from_f(sl * A::to_f(ue[j])));
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] = A::to_f(e[j]);
+    }
+  };
+  const bool one_pass = K <= (int)blockDim.x * 8;      // every thread owns at most one group of eight: keep it
+  float f[8];
+  const int k0 = threadIdx.x * 8;
+  if (one_pass && k0 < K) load8(k0, f);
   float sc = 1.f;
   if constexpr (IN_BF16) {
     float amax = 0.f;
-    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-      const uint4 v = *reinterpret_cast<const uint4*>(row + k);
-      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
+    if (one_pass) {
+      if (k0 < K) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(__bfloat162float(e[j])));
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      }
+    } else {
+      for (int k = k0; k < K; k += blockDim.x * 8) {
+        load8(k, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+      }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -580,18 +614,11 @@ __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const i
   } else {
     if (threadIdx.x == 0) inv_scale[r] = 1.0f;
   }
-  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-    const uint4 v = *reinterpret_cast<const uint4*>(row + k);
+  for (int k = k0; k < K; k += blockDim.x * 8) {
+    if (!one_pass) load8(k, f);
     __half h[8];
-    if constexpr (IN_BF16) {
-      const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&v);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(__bfloat162float(e[j]) * sc);
-    } else {
-      const __half* e = reinterpret_cast<const __half*>(&v);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) h[j] = e[j];
-    }
+    for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(f[j] * sc);       // fp16 source: sc = 1, the value is exact
     uint4 o;
     __half* oh = reinterpret_cast<__half*>(&o);
 #pragma unroll
@@ -604,19 +631,19 @@ __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const i
   }
 }
 
-int act_prep(const void* x, bool in_bf16, int64_t ldx, const int32_t* idx, int div, void* x16, float* inv_scale,
-             int64_t rows, int K, int perm, cudaStream_t st) {
+int act_prep(const void* x, bool in_bf16, bool gated, int64_t ldx, const int32_t* idx, int div, void* x16,
+             float* inv_scale, int64_t rows, int K, int perm, cudaStream_t st) {
   if (rows == 0) return B2Q_OK;
   int threads = (K / 8 + 31) / 32 * 32;
   threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
   const int mode = tls().overlap_mode;
+  auto go = [&](auto kern) {
+    return launch_overlapped(kern, dim3((unsigned)rows), dim3(threads), 0, st, mode > 0, x, ldx, idx,
+                             div > 0 ? div : 1, reinterpret_cast<__half*>(x16), inv_scale, K, perm, mode == 2 ? 1 : 0);
+  };
   cudaError_t e;
-  if (in_bf16)
-    e = launch_overlapped(act_prep_kernel<true>, dim3((unsigned)rows), dim3(threads), 0, st, mode > 0, x, ldx, idx,
-                          div > 0 ? div : 1, reinterpret_cast<__half*>(x16), inv_scale, K, perm, mode == 2 ? 1 : 0);
-  else
-    e = launch_overlapped(act_prep_kernel<false>, dim3((unsigned)rows), dim3(threads), 0, st, mode > 0, x, ldx, idx,
-                          div > 0 ? div : 1, reinterpret_cast<__half*>(x16), inv_scale, K, perm, mode == 2 ? 1 : 0);
+  if (in_bf16) e = gated ? go(act_prep_kernel<true, true>) : go(act_prep_kernel<true, false>);
+  else         e = gated ? go(act_prep_kernel<false, true>) : go(act_prep_kernel<false, false>);
   note_launch("act_prep");
   return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
 }

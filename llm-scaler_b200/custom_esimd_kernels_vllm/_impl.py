@@ -296,10 +296,13 @@ def _moe_int4_layout(weight, scale, K):
 
 def moe_gemm_int4(x, weight, scale, expert_offsets, rows, *, row_map=None, row_div=1, out_map=None, act=L.ACT_NONE,
                   out_rows=None, layout=None):
-    """Grouped INT4 GEMM over expert-sorted rows (see b2q_moe_gemm_int4 in include/b2q.h)."""
+    """Grouped INT4 GEMM over expert-sorted rows (see b2q_moe_gemm_int4 in include/b2q.h).
+
+    act=ACT_SILU_MUL_IN: x is the un-activated [rows, 2K] gate_up result and the GEMM runs on silu(gate) * up.
+    """
     L.require_cuda(x, weight, scale, expert_offsets)
     _chk(x.dim() == 2 and x.stride(1) == 1, "x rows must be contiguous")
-    K = x.shape[1]
+    K = x.shape[1] // 2 if act == L.ACT_SILU_MUL_IN else x.shape[1]
     N, kmajor = _moe_int4_layout(weight, scale, K)
     if layout is None:
         layout = L.W4_NMAJOR if not kmajor else L.W4_KMAJOR_MARLIN
@@ -351,6 +354,6 @@ def moe_forward_int4(x, logits, w13, s13, w2, s2, top_k, num_experts, layout=Non
     wts, ids = moe_topk(logits, top_k, True, weight_dtype=x.dtype)
     offsets, tokens, p2p, _ = moe_route(ids, num_experts)
     rows = T * top_k
-    inter = moe_gemm_int4(x, w13, s13, offsets, rows, row_map=tokens, row_div=top_k, act=L.ACT_SILU_MUL, layout=layout)
-    y = moe_gemm_int4(inter, w2, s2, offsets, rows, layout=layout)
+    gate_up = moe_gemm_int4(x, w13, s13, offsets, rows, row_map=tokens, row_div=top_k, layout=layout)
+    y = moe_gemm_int4(gate_up, w2, s2, offsets, rows, act=L.ACT_SILU_MUL_IN, layout=layout)
     return moe_combine(y, wts, p2p, T, top_k)

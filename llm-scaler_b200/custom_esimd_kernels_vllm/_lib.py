@@ -68,7 +68,7 @@ BF16, F16, F32 = 0, 1, 2
 W4_NMAJOR, W4_KMAJOR, W4_KMAJOR_MARLIN, W4_NMAJOR_S4 = 0, 1, 2, 3
 E4M3, E5M2 = 0, 1
 SCALE_CHANNEL, SCALE_TENSOR, SCALE_BLOCK128 = 0, 1, 2
-ACT_NONE, ACT_SILU_MUL = 0, 1
+ACT_NONE, ACT_SILU_MUL, ACT_SILU_MUL_IN = 0, 1, 2
 
 _DT = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
 

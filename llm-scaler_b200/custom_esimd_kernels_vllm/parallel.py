@@ -71,8 +71,9 @@ class CudaBackend:
 
     def expert_mlp(self, x, w13, s13, w2, s2, offsets, tokens, rows):
         """rows of x (in arrival order) -> y in arrival order, through the experts given by the route."""
-        inter = self.I.moe_gemm_int4(x, w13, s13, offsets, rows, row_map=tokens, row_div=1, act=self.L.ACT_SILU_MUL)
-        return self.I.moe_gemm_int4(inter, w2, s2, offsets, rows, out_map=tokens, out_rows=x.shape[0])
+        gate_up = self.I.moe_gemm_int4(x, w13, s13, offsets, rows, row_map=tokens, row_div=1)
+        return self.I.moe_gemm_int4(gate_up, w2, s2, offsets, rows, out_map=tokens, out_rows=x.shape[0],
+                                    act=self.L.ACT_SILU_MUL_IN)
 
     def combine(self, y, weights, perm, T, k):
         return self.I.moe_combine(y, weights, perm, T, k)

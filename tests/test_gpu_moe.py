@@ -178,3 +178,41 @@ def test_moe_pipeline_config4_shape_reduced(e, T):
     out = e.moe_prefill_full_int4(c["x"].to(DEV), c["logits"].to(DEV), int4.pack_nmajor_i32(c["q13"]).to(DEV),
                                   c["s13"].to(DEV), int4.pack_nmajor_i32(c["q2"]).to(DEV), c["s2"].to(DEV), 4, 16)
     assert_close(out, ref.float(), tol=3e-2, what=f"moe T={T}")
+
+
+@pytest.mark.parametrize("rows_per,E,I,H,dt", [(150, 8, 768, 512, torch.bfloat16), (150, 8, 256, 384, torch.float16),
+                                               (5, 16, 128, 256, torch.bfloat16), (40, 4, 640, 256, torch.bfloat16)])
+def test_gated_input_grouped_gemm_equals_silu_mul_then_gemm(e, rows_per, E, I, H, dt):
+    """The down GEMM fed the un-activated gate_up rows (B2Q_ACT_SILU_MUL_IN) must give, bit for bit, what the separate
+    silu_mul op followed by the plain grouped GEMM gives, on the tcgen05 path (many rows per expert) and on the
+    few-rows path alike; and both agree with the oracle."""
+    I_, L = e._impl, e._lib
+    g = torch.Generator().manual_seed(rows_per * 31 + E)
+    counts = torch.randint(max(rows_per - 4, 0), rows_per + 5, (E,), generator=g)
+    counts[1] = 0
+    off = torch.zeros(E + 1, dtype=torch.int32)
+    off[1:] = counts.cumsum(0)
+    rows = int(off[-1])
+    gate_up = (torch.randn(rows, 2 * I, generator=g) * 1.5).to(dt)
+    qs = [int4.quantize_symmetric((torch.randn(H, I, generator=g) * 0.05).to(dt)) for _ in range(E)]
+    q = torch.stack([a for a, _ in qs])
+    s = torch.stack([b for _, b in qs]).to(dt)
+    w = torch.stack([int4.pack_nmajor_i32(a) for a in q])
+    args = (w.to(DEV), s.to(DEV), off.to(DEV), rows)
+    fused = I_.moe_gemm_int4(gate_up.to(DEV), *args, act=L.ACT_SILU_MUL_IN)
+    inter = I_.silu_mul(gate_up.to(DEV))
+    plain = I_.moe_gemm_int4(inter, *args)
+    assert torch.equal(fused, plain)
+    ref_inter = moe.silu_mul(gate_up)
+    assert torch.allclose(inter.cpu().float(), ref_inter.float(), rtol=1e-2, atol=1e-3)
+    ref = torch.empty(rows, H, dtype=dt)
+    for x in range(E):
+        a, b = int(off[x]), int(off[x + 1])
+        if b > a:
+            ref[a:b] = int4.linear(ref_inter[a:b], q[x], s[x])
+    assert_close(fused, ref, what="gated-input grouped GEMM")
+    # a strided source (the gate_up rows living inside a wider buffer) is read through ldx
+    wide = torch.zeros(rows, 2 * I + 64, dtype=dt)
+    wide[:, :2 * I] = gate_up
+    v = wide.to(DEV)[:, :2 * I]
+    assert torch.equal(I_.moe_gemm_int4(v, *args, act=L.ACT_SILU_MUL_IN), plain)
