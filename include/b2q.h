@@ -233,6 +233,13 @@ B2Q_API int b2q_silu_mul(const void* in, void* out, int dtype, int64_t rows, int
 B2Q_API int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int32_t* perm,
                     void* out, int dtype, int64_t T, int top_k, int64_t H, int w_by_row, void* stream);
 
+/* Tail of the decode pipeline with a shared expert (moe_forward_full_int4,
+ * csrc/moe_batch/moe_int4.sycl:3086-3166: gate precompute, shared down scaled by the gate, accumulate):
+ *   out[t, :] = routed[t, :] + sigmoid(x[t, :] . gate_w[:]) * shared[t, :]   (fp32, one rounding).
+ * x, shared, routed, out contiguous [T, H] in dtype, gate_w [H]; H % 8 == 0; out may alias routed.   */
+B2Q_API int b2q_moe_shared_gate_add(const void* x, const void* gate_w, const void* shared, const void* routed,
+                            void* out, int dtype, int64_t T, int64_t H, void* stream);
+
 /* ---- MoE grouped GEMMs ----------------------------------------------------
  * Rows [expert_offsets[e], expert_offsets[e+1]) of the (virtual) expert-sorted
  * input use expert e's weight.  If row_map != NULL the input row of sorted row

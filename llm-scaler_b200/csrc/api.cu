@@ -20,6 +20,7 @@ int moe_route(const int32_t*, int64_t, int, int32_t*, int32_t*, int32_t*, int32_
 int moe_build_tiles(const int32_t*, int, int, int32_t*, cudaStream_t);
 int gather_rows(const void*, const int32_t*, int, void*, int64_t, int64_t, int, cudaStream_t);
 int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t, int64_t ld_in = 0);
+int shared_gate_add(const void*, const void*, const void*, const void*, void*, int, int64_t, int64_t, cudaStream_t);
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
 int act_prep(const void*, bool, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
@@ -370,6 +371,15 @@ int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int32_t* pe
   if (T < 0 || top_k <= 0 || H < 0 || (H % 8) != 0) return B2Q_ERR_SHAPE;
   if (!aligned16(y) || !aligned16(out)) return B2Q_ERR_ALIGN;
   return moe_combine(y, w, w_dtype, perm, out, dtype, T, top_k, H, w_by_row, (cudaStream_t)stream);
+}
+
+int b2q_moe_shared_gate_add(const void* x, const void* gate_w, const void* shared, const void* routed, void* out,
+                            int dtype, int64_t T, int64_t H, void* stream) {
+  if (!x || !gate_w || !shared || !routed || !out) return B2Q_ERR_NULL;
+  if (!is16(dtype)) return B2Q_ERR_DTYPE;
+  if (T < 0 || H <= 0 || (H % 8) != 0 || T > INT32_MAX) return B2Q_ERR_SHAPE;
+  if (!aligned16(x) || !aligned16(gate_w) || !aligned16(shared) || !aligned16(routed) || !aligned16(out)) return B2Q_ERR_ALIGN;
+  return shared_gate_add(x, gate_w, shared, routed, out, dtype, T, H, (cudaStream_t)stream);
 }
 
 size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int64_t K, int act, int gather) {

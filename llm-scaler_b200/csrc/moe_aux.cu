@@ -312,6 +312,60 @@ int silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, cons
 }
 
 // ---------------------------------------------------------------------------
+// Tail of the decode pipeline with a shared expert: out[t, :] = routed[t, :] + sigmoid(x[t, :] . gate_w) * shared[t, :],
+// all in fp32 with one rounding.  One CTA per token; out may alias routed.
+template <bool BF16>
+__global__ void shared_gate_add_kernel(const uint4* __restrict__ x, const uint4* __restrict__ gate_w,
+                                       const uint4* __restrict__ shared, const uint4* routed, uint4* out, int H8) {
+  using A = Act<BF16>;
+  using T = typename A::T;
+  __shared__ float red[32];
+  __shared__ float gate_sh;
+  const int64_t t = blockIdx.x;
+  float dot = 0.f;
+  for (int c = threadIdx.x; c < H8; c += blockDim.x) {
+    const uint4 xv = x[t * H8 + c], gv = gate_w[c];
+    const T* xp = reinterpret_cast<const T*>(&xv);
+    const T* gp = reinterpret_cast<const T*>(&gv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dot += A::to_f(xp[j]) * A::to_f(gp[j]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = dot;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a += red[i];
+    gate_sh = 1.0f / (1.0f + expf(-a));
+  }
+  __syncthreads();
+  const float gate = gate_sh;
+  for (int c = threadIdx.x; c < H8; c += blockDim.x) {
+    const uint4 sv = shared[t * H8 + c], rv = routed[t * H8 + c];
+    const T* sp = reinterpret_cast<const T*>(&sv);
+    const T* rp = reinterpret_cast<const T*>(&rv);
+    uint4 o;
+    T* op = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) op[j] = A::from_f(A::to_f(rp[j]) + gate * A::to_f(sp[j]));
+    out[t * H8 + c] = o;
+  }
+}
+
+int shared_gate_add(const void* x, const void* gate_w, const void* shared, const void* routed, void* out, int dtype,
+                    int64_t T, int64_t H, cudaStream_t st) {
+  if (T == 0) return B2Q_OK;
+  auto u = [](const void* p) { return reinterpret_cast<const uint4*>(p); };
+  if (dtype == B2Q_BF16)
+    shared_gate_add_kernel<true><<<(unsigned)T, 256, 0, st>>>(u(x), u(gate_w), u(shared), u(routed), reinterpret_cast<uint4*>(out), (int)(H / 8));
+  else
+    shared_gate_add_kernel<false><<<(unsigned)T, 256, 0, st>>>(u(x), u(gate_w), u(shared), u(routed), reinterpret_cast<uint4*>(out), (int)(H / 8));
+  note_launch("shared_gate_add");
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
 // out[t, :] = sum_s w[t, s] * y[row(t, s), :], slots added in order s = 0..k-1 in fp32.
 template <bool BF16>
 __global__ void moe_combine_kernel(const uint4* __restrict__ y, const void* __restrict__ w, int wdt,

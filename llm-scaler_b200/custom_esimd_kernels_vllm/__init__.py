@@ -18,6 +18,8 @@ from .ops import (  # noqa: F401
     moe_silu_mul_int4, moe_route_gather_int4, moe_gemm_int4_nmajor, moe_prefill_full_int4, moe_topk_softmax,
     esimd_resadd_norm_gemv_fp8_pert, esimd_resadd_norm_gemv_int4_pert, esimd_resadd_norm_gemv2_fp8_pert, q4_0_quantize,
     esimd_norm_gemv_fp8_pert, esimd_norm_gemv_fp8_blockscale, esimd_norm_gemv_int4_pert,
+    moe_router_forward_int4, moe_router_topk_int4, moe_forward_full_int4, moe_shared_expert_forward_int4_nmajor,
+    moe_forward_cutlass_nmajor_int4_full,
 )
 
 launch_count = _lib.launch_count

@@ -77,6 +77,30 @@ def linear_int4(input, weight, weight_scale, output):
     return output
 
 
+def linear_int4_nmajor(input, weight, weight_scale, N, K, scale_is_kmajor, output=None, signed=False):
+    """out = input @ dequant(W)^T for a weight whose BYTES are the N-major [N, K/8] matrix whatever shape the tensor
+    carries (the column-major repack of csrc/moe_batch/moe_int4.sycl:171-215, :3036-3040 hands over a [K/8, N]-shaped
+    tensor with exactly that memory), and scales stored [K/128, N] (scale_is_kmajor) or [N, K/128].  signed: the
+    nibbles are two's complement (value, not value + 8), the encoding of ops.py:1243-1263."""
+    L.require_cuda(input, weight, weight_scale)
+    _chk(weight.is_contiguous() and weight_scale.is_contiguous(), "weight and scale must be contiguous")
+    _chk(weight.numel() * weight.element_size() * 2 == N * K, "weight bytes do not match N x K nibbles")
+    G = K // GROUP
+    _chk(K % GROUP == 0 and weight_scale.numel() == N * G, "scale size does not match N x K/128")
+    _chk(input.dim() == 2 and input.shape[1] == K and input.stride(1) == 1, "input must be [M, K]")
+    M = input.shape[0]
+    if output is None:
+        output = torch.empty(M, N, dtype=input.dtype, device=input.device)
+    sn, sg = (1, N) if scale_is_kmajor else (G, 1)
+    with L.on_device(input):
+        wsb = L.lib.b2q_linear_workspace_bytes(M, N, K)
+        ws = torch.empty(wsb, dtype=torch.uint8, device=input.device)
+        L.check(L.lib.b2q_linear_int4(input.data_ptr(), L.dt(input), input.stride(0) if M > 1 else K,
+                                       weight.data_ptr(), L.W4_NMAJOR_S4 if signed else L.W4_NMAJOR, weight_scale.data_ptr(),
+                                       L.dt(weight_scale), sn, sg, output.data_ptr(), N, M, N, K, GROUP, L.ptr(ws), wsb, L.stream(input)))
+    return output
+
+
 def dequant_int4(weight, weight_scale, out_dtype=torch.bfloat16, layout=None):
     """Debug / bit-exactness gate: [N, K] dequantised weight."""
     L.require_cuda(weight, weight_scale)
@@ -357,3 +381,103 @@ def moe_forward_int4(x, logits, w13, s13, w2, s2, top_k, num_experts, layout=Non
     gate_up = moe_gemm_int4(x, w13, s13, offsets, rows, row_map=tokens, row_div=top_k, layout=layout)
     y = moe_gemm_int4(gate_up, w2, s2, offsets, rows, act=L.ACT_SILU_MUL_IN, layout=layout)
     return moe_combine(y, wts, p2p, T, top_k)
+
+
+def moe_shared_gate_add(x, gate_w, shared, routed, out=None):
+    """out = routed + sigmoid(x . gate_w) * shared (b2q_moe_shared_gate_add)."""
+    L.require_cuda(x, gate_w, shared, routed)
+    T, H = x.shape
+    _chk(x.is_contiguous() and shared.is_contiguous() and routed.is_contiguous(), "operands must be contiguous")
+    _chk(gate_w.numel() == H and gate_w.is_contiguous() and gate_w.dtype == x.dtype, "gate weight must be [1, H] in x's dtype")
+    _chk(tuple(shared.shape) == (T, H) and tuple(routed.shape) == (T, H), "shared / routed must be [T, H]")
+    if out is None:
+        out = torch.empty_like(routed)
+    with L.on_device(x):
+        L.check(L.lib.b2q_moe_shared_gate_add(x.data_ptr(), gate_w.data_ptr(), shared.data_ptr(), routed.data_ptr(),
+                                               out.data_ptr(), L.dt(x), T, H, L.stream(x)))
+    return out
+
+
+def moe_router_forward_int4(x, weight, scale, use_ggml_layout):
+    """Router logits x @ dequant(Wg)^T, [T, E] (moe_router_forward_int4, csrc/moe_batch/moe_int4.sycl:171-260).
+
+    GGML layout: weight uint8 [E, K/2] or int32 [E, K/8], scale [E, K/128].  Otherwise the weight may arrive shaped
+    [K/8, E] after the column-major repack (its memory is still [E, K/8]) with scale [K/128, E].
+    """
+    _chk(x.dim() == 2 and x.is_contiguous(), "x must be contiguous [T, K]")
+    K = x.shape[1]
+    E = weight.numel() * weight.element_size() * 2 // K
+    G = K // GROUP
+    if use_ggml_layout:
+        _chk(tuple(scale.shape) == (E, G), "gate scale must be [E, K/128]")
+        return linear_int4_nmajor(x, weight, scale, E, K, False)
+    kmaj = tuple(scale.shape) == (G, E) or scale.numel() == G * E
+    _chk(kmaj, "gate scale must hold K/128 x E values")
+    return linear_int4_nmajor(x, weight, scale.contiguous(), E, K, True)
+
+
+def moe_shared_expert_int4(x, gu_w, gu_s, down_w, down_s, gate_w, scale_is_kmajor, signed=False):
+    """sigmoid(x . gate_w) * down(silu(gate(x)) * up(x)) with N-major INT4 weights, returned un-added: [T, H] shared
+    output and the gate is applied by moe_shared_gate_add."""
+    K = x.shape[1]
+    two_i = gu_w.numel() * gu_w.element_size() * 2 // K
+    g = linear_int4_nmajor(x, gu_w, gu_s, two_i, K, scale_is_kmajor, signed=signed)
+    a = silu_mul(g)
+    return linear_int4_nmajor(a, down_w, down_s, K, two_i // 2, scale_is_kmajor, signed=signed)
+
+
+def moe_shared_expert_forward_int4_nmajor(x, gate_up_qweight, gate_up_scale, down_qweight, down_scale, gate_weight):
+    """moe_shared_expert_forward_int4_nmajor (csrc/moe_batch/moe_int4.sycl:3311-3366; ops.py:1209-1230): uint8
+    [2I, H/2] / [H, I/2] two's-complement nibbles with [N, K/128] scales; returns the sigmoid-gated shared expert
+    output [T, H]."""
+    _chk(gate_weight.shape[0] == 1, "one shared expert is supported")
+    _chk(gate_up_qweight.dtype == torch.uint8 and down_qweight.dtype == torch.uint8, "weights must be uint8 nibble pairs")
+    x = x.contiguous()
+    y = moe_shared_expert_int4(x, gate_up_qweight, gate_up_scale, down_qweight, down_scale, gate_weight, False,
+                               signed=True)
+    return moe_shared_gate_add(x, gate_weight.contiguous(), y, torch.zeros_like(y))
+
+
+def moe_forward_full_int4(x, logits, gate_up_qweight, gate_up_scales, shared_gate_up_weight, shared_gate_up_scale,
+                          down_qweight, down_scales, shared_down_weight, shared_down_scale, shared_expert_gate_weight,
+                          top_k, num_shared_experts, n_routed_experts, use_ggml_layout=False):
+    """Decode pipeline with the sigmoid-gated shared expert (moe_forward_full_int4,
+    csrc/moe_batch/moe_int4.sycl:2933-3166; python ops.py:1171-1206).
+
+    Routed experts: K-major marlin-shuffled int32 [E, K/8, N] with scales [E, K/128, N], or, with use_ggml_layout,
+    N-major [E, N, K/8] with scales [E, N, K/128].  Shared expert: INT4 (int32, column-major repacked, scales
+    [K/128, N]) or 16-bit dense [2*Is, H] / [H, Is], told apart by dtype as the reference does (:2965).  The dense
+    16-bit shared expert is a plain library GEMM (torch.nn.functional.linear); everything else runs in this library.
+    """
+    _chk(num_shared_experts in (0, 1), "0 or 1 shared experts are supported")
+    x = x.contiguous()
+    layout = L.W4_NMAJOR if use_ggml_layout else L.W4_KMAJOR_MARLIN
+    routed = moe_forward_int4(x, logits.contiguous(), gate_up_qweight, gate_up_scales, down_qweight, down_scales,
+                              top_k, n_routed_experts, layout=layout)
+    if num_shared_experts == 0 or shared_gate_up_weight.numel() == 0:
+        return routed
+    if shared_gate_up_weight.dtype in (torch.int32, torch.uint8):
+        y = moe_shared_expert_int4(x, shared_gate_up_weight, shared_gate_up_scale, shared_down_weight,
+                                   shared_down_scale, shared_expert_gate_weight, True)
+    else:
+        g = torch.nn.functional.linear(x, shared_gate_up_weight.to(x.dtype))
+        y = torch.nn.functional.linear(silu_mul(g), shared_down_weight.to(x.dtype)).contiguous()
+    return moe_shared_gate_add(x, shared_expert_gate_weight.to(x.dtype).contiguous(), y, routed, out=routed)
+
+
+def moe_forward_cutlass_nmajor_int4_full(x, logits, w13, w13_scales, w2, w2_scales, shared_gu_w, shared_d_w,
+                                         shared_gate_w, top_k, num_shared_experts, n_routed_experts):
+    """moe_forward_cutlass_nmajor_int4_full (csrc/moe_batch/moe_int4.sycl:3702-3770): routed experts as two's-complement
+    N-major nibbles uint8 [E, N, K/2] (ops.py:1243-1297) with scales [E, N, K/128], 16-bit dense shared expert."""
+    _chk(num_shared_experts in (0, 1), "0 or 1 shared experts are supported")
+    x = x.contiguous()
+    routed = moe_forward_int4(x, logits.contiguous(), w13, w13_scales, w2, w2_scales, top_k, n_routed_experts,
+                              layout=L.W4_NMAJOR_S4)
+    if num_shared_experts == 0 or shared_gu_w.numel() == 0:
+        return routed
+    sg = shared_gu_w[0] if shared_gu_w.dim() == 3 else shared_gu_w
+    sd = shared_d_w[0] if shared_d_w.dim() == 3 else shared_d_w
+    sw = shared_gate_w[0] if shared_gate_w.dim() == 3 else shared_gate_w
+    g = torch.nn.functional.linear(x, sg.to(x.dtype))
+    y = torch.nn.functional.linear(silu_mul(g), sd.to(x.dtype)).contiguous()
+    return moe_shared_gate_add(x, sw.to(x.dtype).contiguous(), y, routed, out=routed)

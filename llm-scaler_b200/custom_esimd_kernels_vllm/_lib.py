@@ -44,6 +44,7 @@ _SIGS = {
     "b2q_silu_mul": (i32, [vp, vp, i32, i64, i64, vp]),
     "b2q_moe_combine": (i32, [vp, vp, i32, vp, vp, i32, i64, i32, i64, i32, vp]),
     "b2q_moe_gemm_workspace_bytes": (sz, [i64, i32, i64, i64, i32, i32]),
+    "b2q_moe_shared_gate_add": (i32, [vp, vp, vp, vp, vp, i32, i64, i64, vp]),
     "b2q_device_status": (i32, [vp]),
     "b2q_device_status_reset": (i32, []),
     "b2q_selftest_bounded_wait": (i32, [i32, vp, vp]),

@@ -371,4 +371,32 @@ _op(INS, "moe_route_gather_int4(Tensor route_output, Tensor sorted_rows, Tensor 
 _op(INS, "moe_gemm_int4_nmajor(Tensor x, Tensor weight, Tensor scale, Tensor expert_idx, int group_size) -> Tensor",
     _gemm_int4_nmajor)
 
+
+
+def _router_topk_int4(x, weight, scale, use_ggml_layout, top_k, n_routed_experts, norm):
+    logits = I.moe_router_forward_int4(x, weight, scale, use_ggml_layout)
+    return _topk_int4(logits, top_k, n_routed_experts, norm)
+
+
+_op(INS, "moe_router_forward_int4(Tensor x, Tensor weight, Tensor scale, bool use_ggml_layout) -> Tensor",
+    I.moe_router_forward_int4)
+_op(INS, "moe_router_topk_int4(Tensor x, Tensor weight, Tensor scale, bool use_ggml_layout, int top_k, "
+    "int n_routed_experts, bool norm) -> (Tensor, Tensor)", _router_topk_int4)
+_op(INS, "moe_forward_full_int4(Tensor x, Tensor logits, "
+    "Tensor gate_up_qweight, Tensor gate_up_scales, "
+    "Tensor shared_gate_up_weight, Tensor shared_gate_up_scale, "
+    "Tensor down_qweight, Tensor down_scales, "
+    "Tensor shared_down_weight, Tensor shared_down_scale, "
+    "Tensor shared_expert_gate_weight, "
+    "int top_k, int num_shared_experts, int n_routed_experts, "
+    "bool use_ggml_layout) -> Tensor", I.moe_forward_full_int4)
+_op(INS, "moe_shared_expert_forward_int4_nmajor(Tensor x, "
+    "Tensor gate_up_qweight, Tensor gate_up_scale, "
+    "Tensor down_qweight, Tensor down_scale, "
+    "Tensor gate_weight) -> Tensor", I.moe_shared_expert_forward_int4_nmajor)
+_op(INS, "moe_forward_cutlass_nmajor_int4_full(Tensor x, Tensor logits, "
+    "Tensor w13, Tensor w13_scales, Tensor w2, Tensor w2_scales, "
+    "Tensor shared_gu_w, Tensor shared_d_w, Tensor shared_gate_w, "
+    "int top_k, int num_shared_experts, int n_routed_experts) -> Tensor", I.moe_forward_cutlass_nmajor_int4_full)
+
 REGISTERED = {ns: lib for ns, lib in _LIBS.items()}

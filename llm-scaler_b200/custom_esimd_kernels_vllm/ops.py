@@ -125,6 +125,40 @@ def moe_topk_int4(logits, top_k, n_routed_experts, norm=True):
     return _moe_int4.moe_topk_int4(logits.contiguous(), top_k, n_routed_experts, norm)
 
 
+def moe_router_forward_int4(x, weight, scale, use_ggml_layout=False):
+    """INT4 router GEMV, logits [T, E] (ops.py:1139-1150)."""
+    return _moe_int4.moe_router_forward_int4(x.contiguous(), weight, scale, use_ggml_layout)
+
+
+def moe_router_topk_int4(x, weight, scale, use_ggml_layout, top_k, n_routed_experts, norm=True):
+    """INT4 router followed by top-k (ops.py:1153-1168)."""
+    return _moe_int4.moe_router_topk_int4(x.contiguous(), weight, scale, use_ggml_layout, top_k, n_routed_experts, norm)
+
+
+def moe_forward_full_int4(x, logits, gate_up_qweight, gate_up_scales, shared_gate_up_weight, shared_gate_up_scale,
+                          down_qweight, down_scales, shared_down_weight, shared_down_scale, shared_expert_gate_weight,
+                          top_k, num_shared_experts, n_routed_experts, use_ggml_layout=False):
+    """INT4 MoE decode pipeline with the shared expert: topk + up + down + finalize (ops.py:1171-1206)."""
+    return _moe_int4.moe_forward_full_int4(x, logits, gate_up_qweight, gate_up_scales, shared_gate_up_weight,
+                                           shared_gate_up_scale, down_qweight, down_scales, shared_down_weight,
+                                           shared_down_scale, shared_expert_gate_weight, top_k, num_shared_experts,
+                                           n_routed_experts, use_ggml_layout)
+
+
+def moe_shared_expert_forward_int4_nmajor(x, gate_up_qweight, gate_up_scale, down_qweight, down_scale, gate_weight):
+    """Sigmoid-gated shared expert with N-major uint8 INT4 weights (ops.py:1209-1230)."""
+    return _moe_int4.moe_shared_expert_forward_int4_nmajor(x, gate_up_qweight, gate_up_scale, down_qweight,
+                                                           down_scale, gate_weight)
+
+
+def moe_forward_cutlass_nmajor_int4_full(x, logits, w13, w13_scales, w2, w2_scales, shared_gu_w, shared_d_w,
+                                         shared_gate_w, top_k, num_shared_experts, n_routed_experts):
+    """Decode pipeline on two's-complement N-major INT4 experts with a 16-bit shared expert (ops.py:1674-1690)."""
+    return _moe_int4.moe_forward_cutlass_nmajor_int4_full(x, logits, w13, w13_scales, w2, w2_scales, shared_gu_w,
+                                                          shared_d_w, shared_gate_w, top_k, num_shared_experts,
+                                                          n_routed_experts)
+
+
 def to_cutlass_nmajor_int4(qweight):
     """int32 [.., N, K/8] -> uint8 [.., N, K/2], low nibble = even k (pure torch, device agnostic)."""
     if qweight.dtype == torch.uint8:

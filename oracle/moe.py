@@ -80,6 +80,32 @@ def forward(x, logits, w13d, w2d, top_k, round_intermediates=True):
     return _ordered_sum(yp.reshape(T, top_k, H)).to(x.dtype)
 
 
+def shared_expert(x, shared_gate_up, shared_down, shared_gate_w, round_intermediates=True):
+    """sigmoid(x . gate_w) * down(silu(gate(x)) * up(x)) for one shared expert, fp32 result [T, H].
+
+    tests/test_moe_int4_kernel.py:232-244.  shared_gate_up [2*Is, H] (gate rows first), shared_down [H, Is],
+    shared_gate_w [1, H]; all dequantised / 16-bit weights in x.dtype.
+    """
+    xf = x.float()
+    g = xf @ shared_gate_up.float().T
+    if round_intermediates:
+        g = g.to(x.dtype)
+    a = silu_mul(g)
+    y = a.float() @ shared_down.float().T
+    if round_intermediates:
+        y = y.to(x.dtype).float()
+    gate = torch.sigmoid(xf @ shared_gate_w.float().T)          # [T, 1]
+    return y * gate
+
+
+def forward_full(x, logits, w13d, w2d, shared_gate_up, shared_down, shared_gate_w, top_k, round_intermediates=True):
+    """The decode pipeline moe_forward_full_int4 computes: routed experts plus the sigmoid-gated shared expert
+    (tests/test_moe_int4_kernel.py:198-247; csrc/moe_batch/moe_int4.sycl:2933-3166)."""
+    routed = forward(x, logits, w13d, w2d, top_k, round_intermediates)
+    sh = shared_expert(x, shared_gate_up, shared_down, shared_gate_w, round_intermediates)
+    return (routed.float() + sh).to(x.dtype)
+
+
 def _ordered_sum(v: torch.Tensor) -> torch.Tensor:
     acc = torch.zeros(v.shape[0], v.shape[2], dtype=torch.float32)
     for s in range(v.shape[1]):

@@ -101,6 +101,39 @@ def main(ref_root):
     np.savez_compressed(os.path.join(OUT, "moe_int4.npz"), x=xm.numpy(), logits=logits.numpy(), q13=torch.stack(q13).numpy(),
              s13=torch.stack(s13).numpy(), q2=torch.stack(q2).numpy(), s2=torch.stack(s2).numpy(), out=out.numpy(),
              top_k=np.int32(k))
+    # 6. the decode pipeline with the sigmoid-gated shared expert (test_moe_int4_kernel.py:198-247 in full), fp16
+    #    and INT4 shared weights, with the packed tensors exactly as the tests hand them to moe_forward_full_int4
+    #    (:268-310, :350-420): routed experts K-major + marlin shuffle, INT4 shared expert column-major repacked.
+    torch.manual_seed(15)
+    T, H, I, IS, E, k = 5, 256, 128, 128, 16, 4
+    xs_ = (torch.randn(T, H) * 0.1).half()
+    lg = (torch.randn(T, E) * 0.1).half()
+    w13 = (torch.randn(E, 2 * I, H) * 0.02).half()
+    w2m = (torch.randn(E, H, I) * 0.02).half()
+    sgu = (torch.randn(2 * IS, H) * 0.02).half()
+    sdn = (torch.randn(H, IS) * 0.02).half()
+    sgw = (torch.randn(1, H) * 0.02).half()
+    q13, s13, q2, s2, d13, d2 = [], [], [], [], [], []
+    for e in range(E):
+        a_, b_ = tm.quantize_int4(w13[e]); q13.append(a_); s13.append(b_); d13.append(tm.dequantize_int4(a_, b_, 2 * I, H))
+        a_, b_ = tm.quantize_int4(w2m[e]); q2.append(a_); s2.append(b_); d2.append(tm.dequantize_int4(a_, b_, H, I))
+    q13, s13, q2, s2 = torch.stack(q13), torch.stack(s13), torch.stack(q2), torch.stack(s2)
+    d13, d2 = torch.stack(d13), torch.stack(d2)
+    w13_ipex, s13_ipex = tm.ipex_transform_expert_weights(q13, s13, E, 2 * I, H // 8, H // 128)
+    w2_ipex, s2_ipex = tm.ipex_transform_expert_weights(q2, s2, E, H, I // 8, I // 128)
+    out_f16 = tm._ref_moe_forward_full(xs_, lg, d13, sgu, d2, sdn, sgw, k, E)
+    gq, gs = tm.quantize_int4(sgu)
+    dq, ds = tm.quantize_int4(sdn)
+    out_i4 = tm._ref_moe_forward_full(xs_, lg, d13, tm.dequantize_int4(gq, gs, 2 * IS, H), d2,
+                                      tm.dequantize_int4(dq, ds, H, IS), sgw, k, E)
+    np.savez_compressed(os.path.join(OUT, "moe_int4_shared.npz"), x=xs_.numpy(), logits=lg.numpy(),
+             q13=q13.numpy(), s13=s13.numpy(), q2=q2.numpy(), s2=s2.numpy(),
+             w13_ipex=w13_ipex.numpy(), s13_ipex=s13_ipex.numpy(), w2_ipex=w2_ipex.numpy(), s2_ipex=s2_ipex.numpy(),
+             sgu=sgu.numpy(), sdn=sdn.numpy(), sgw=sgw.numpy(),
+             sgu_q=tm.ipex_column_major_repack(gq.t().contiguous()).numpy(), sgu_s=gs.t().contiguous().numpy(),
+             sdn_q=tm.ipex_column_major_repack(dq.t().contiguous()).numpy(), sdn_s=ds.t().contiguous().numpy(),
+             sgu_qn=gq.numpy(), sgu_sn=gs.numpy(), sdn_qn=dq.numpy(), sdn_sn=ds.numpy(),
+             out_f16=out_f16.numpy(), out_i4=out_i4.numpy(), top_k=np.int32(k))
     print("wrote", sorted(f for f in os.listdir(OUT) if f.endswith(".npz")))
 
 

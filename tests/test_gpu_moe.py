@@ -216,3 +216,90 @@ def test_gated_input_grouped_gemm_equals_silu_mul_then_gemm(e, rows_per, E, I, H
     wide[:, :2 * I] = gate_up
     v = wide.to(DEV)[:, :2 * I]
     assert torch.equal(I_.moe_gemm_int4(v, *args, act=L.ACT_SILU_MUL_IN), plain)
+
+
+def _g(golden, name):
+    g = golden(name)
+    return {k: torch.from_numpy(g[k]) for k in g.files}
+
+
+def _rel(a, ref):
+    return float((a.float().cpu() - ref.float()).abs().max() / ref.float().abs().max())
+
+
+def test_decode_pipeline_with_shared_expert_golden(e, golden):
+    """moe_forward_full_int4 on the tensors the reference's own tests build (K-major marlin experts; 16-bit or
+    column-major repacked INT4 shared expert) against outputs of the reference's per-token loop."""
+    g = _g(golden, "moe_int4_shared")
+    k, E = int(g["top_k"]), g["q13"].shape[0]
+    d = lambda n: g[n].to(DEV)
+    empty = torch.empty(0, dtype=torch.float16, device=DEV)
+    out = e.moe_forward_full_int4(d("x"), d("logits"), d("w13_ipex"), d("s13_ipex"), d("sgu"), empty,
+                                  d("w2_ipex"), d("s2_ipex"), d("sdn"), empty, d("sgw"), k, 1, E, False)
+    assert _rel(out, g["out_f16"]) < 3e-2
+    out = e.moe_forward_full_int4(d("x"), d("logits"), d("w13_ipex"), d("s13_ipex"), d("sgu_q"), d("sgu_s"),
+                                  d("w2_ipex"), d("s2_ipex"), d("sdn_q"), d("sdn_s"), d("sgw"), k, 1, E, False)
+    assert _rel(out, g["out_i4"]) < 3e-2
+    # N-major (GGML) experts give the same result as the K-major ones
+    out_n = e.moe_forward_full_int4(d("x"), d("logits"), d("q13"), d("s13"), d("sgu_q"), d("sgu_s"),
+                                    d("q2"), d("s2"), d("sdn_q"), d("sdn_s"), d("sgw"), k, 1, E, True)
+    assert _rel(out_n, g["out_i4"]) < 3e-2
+    # two's-complement N-major bytes + 16-bit shared expert
+    s4 = lambda n: int4.u4_to_s4_bytes(int4.pack_nmajor_u8(int4.unpack_nmajor_i32(g[n]))).to(DEV)
+    out_c = e.moe_forward_cutlass_nmajor_int4_full(d("x"), d("logits"), s4("q13"), d("s13"), s4("q2"), d("s2"),
+                                                   d("sgu"), d("sdn"), d("sgw"), k, 1, E)
+    assert _rel(out_c, g["out_f16"]) < 3e-2
+    # no shared expert: the routed part alone
+    out_0 = e.moe_forward_full_int4(d("x"), d("logits"), d("w13_ipex"), d("s13_ipex"), empty, empty,
+                                    d("w2_ipex"), d("s2_ipex"), empty, empty, empty, k, 0, E, False)
+    d13 = int4.dequant(int4.unpack_nmajor_i32(g["q13"]), g["s13"], torch.float16)
+    d2 = int4.dequant(int4.unpack_nmajor_i32(g["q2"]), g["s2"], torch.float16)
+    assert _rel(out_0, moe.forward(g["x"], g["logits"], d13, d2, k)) < 3e-2
+
+
+@pytest.mark.parametrize("T,H,E", [(1, 256, 16), (4, 2048, 256), (16, 2048, 16), (3, 3072, 256)])
+def test_int4_router_both_layouts(e, T, H, E):
+    """moe_router_forward_int4 (tests/test_moe_int4_kernel.py:146-190): weight [E, K/8] directly or shaped [K/8, E]
+    over the same memory, scales [K/128, E]; and the GGML presentation with scales [E, K/128].  E == K/128 is the
+    case where the two scale layouts have the same shape."""
+    gen = torch.Generator().manual_seed(T + H + E)
+    w = (torch.randn(E, H, generator=gen) * 0.02).half()
+    q, s = int4.quantize_symmetric(w)
+    x = (torch.randn(T, H, generator=gen) * 0.1).half()
+    ref = int4.linear(x, q, s)
+    qw = int4.pack_nmajor_i32(q)
+    sc = s.t().contiguous()
+    for shaped in (qw, qw.flatten().reshape(H // 8, E)):
+        out = e.moe_router_forward_int4(x.to(DEV), shaped.to(DEV), sc.to(DEV), False)
+        assert tuple(out.shape) == (T, E)
+        assert_close(out, ref, what="router logits")
+    out = e.moe_router_forward_int4(x.to(DEV), int4.pack_nmajor_u8(q).to(DEV), s.to(DEV), True)
+    assert_close(out, ref, what="router logits, GGML layout")
+    wts, ids = e.moe_router_topk_int4(x.to(DEV), qw.to(DEV), sc.to(DEV), False, 4, E, True)
+    rw, rids = moe.topk_softmax(out.cpu(), 4, True, torch.float16)
+    assert torch.equal(ids.cpu(), rids)
+    zero = e.moe_router_forward_int4(torch.zeros(1, H, dtype=torch.float16, device=DEV), qw.to(DEV), sc.to(DEV), False)
+    assert float(zero.abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("T,H,I,dt", [(2, 256, 128, torch.float16), (33, 2048, 256, torch.bfloat16)])
+def test_shared_expert_nmajor_signed_nibbles(e, T, H, I, dt):
+    gen = torch.Generator().manual_seed(T * H)
+    gu = (torch.randn(2 * I, H, generator=gen) * 0.02).to(dt)
+    dn = (torch.randn(H, I, generator=gen) * 0.02).to(dt)
+    gw = (torch.randn(1, H, generator=gen) * 0.05).to(dt)
+    x = (torch.randn(T, H, generator=gen) * 0.5).to(dt)
+    (qg, sg), (qd, sd) = int4.quantize_symmetric(gu), int4.quantize_symmetric(dn)
+    sg, sd = sg.to(dt), sd.to(dt)
+    s4 = lambda q: int4.u4_to_s4_bytes(int4.pack_nmajor_u8(q)).to(DEV)
+    out = e.moe_shared_expert_forward_int4_nmajor(x.to(DEV), s4(qg), sg.to(DEV), s4(qd), sd.to(DEV), gw.to(DEV))
+    ref = moe.shared_expert(x, int4.dequant(qg, sg, dt), int4.dequant(qd, sd, dt), gw).to(dt)
+    assert _rel(out, ref) < 2e-2
+    # the gate-add kernel on its own: bit-level check against fp32 arithmetic with one rounding
+    y = torch.randn(T, H, generator=gen).to(dt)
+    r = torch.randn(T, H, generator=gen).to(dt)
+    got = e._impl.moe_shared_gate_add(x.to(DEV), gw.to(DEV), y.to(DEV), r.to(DEV))
+    gate = torch.sigmoid(x.float() @ gw.float().T)
+    want = (r.float() + gate * y.float()).to(dt)
+    assert torch.allclose(got.cpu().float(), want.float(), rtol=1e-2, atol=1e-2)
+    assert (got.cpu() != want).float().mean() < 0.02

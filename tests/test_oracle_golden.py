@@ -112,6 +112,34 @@ def test_moe_forward_matches_reference_per_token_loop(golden):
     assert err < 2e-3, err
 
 
+def test_moe_decode_pipeline_with_shared_expert_matches_reference_loop(golden):
+    """moe_forward_full_int4's reference loop with fp16 and with INT4 shared-expert weights; the packed tensors the
+    reference tests hand to the op (K-major marlin experts, column-major repacked shared expert) must unpack to the
+    same nibbles."""
+    g = golden("moe_int4_shared")
+    x, logits, k = t(g["x"]), t(g["logits"]), int(g["top_k"])
+    q13, q2 = int4.unpack_nmajor_i32(t(g["q13"])), int4.unpack_nmajor_i32(t(g["q2"]))
+    d13 = int4.dequant(q13, t(g["s13"]), torch.float16)
+    d2 = int4.dequant(q2, t(g["s2"]), torch.float16)
+    out = moe.forward_full(x, logits, d13, d2, t(g["sgu"]), t(g["sdn"]), t(g["sgw"]), k, round_intermediates=False)
+    ref = t(g["out_f16"]).float()
+    assert (out.float() - ref).abs().max() / ref.abs().max() < 2e-3
+    # INT4 shared expert: flat memory of the repacked [K/8, N] tensor is the N-major [N, K/8] matrix
+    gq = t(g["sgu_q"]).reshape(t(g["sgu_qn"]).shape)
+    dq = t(g["sdn_q"]).reshape(t(g["sdn_qn"]).shape)
+    assert torch.equal(gq, t(g["sgu_qn"])) and torch.equal(dq, t(g["sdn_qn"]))
+    assert torch.equal(t(g["sgu_s"]).T.contiguous(), t(g["sgu_sn"]))
+    sgu_d = int4.dequant(int4.unpack_nmajor_i32(gq), t(g["sgu_sn"]), torch.float16)
+    sdn_d = int4.dequant(int4.unpack_nmajor_i32(dq), t(g["sdn_sn"]), torch.float16)
+    out = moe.forward_full(x, logits, d13, d2, sgu_d, sdn_d, t(g["sgw"]), k, round_intermediates=False)
+    ref = t(g["out_i4"]).float()
+    assert (out.float() - ref).abs().max() / ref.abs().max() < 2e-3
+    # routed experts: K-major + marlin shuffle unpacks to the same nibbles
+    assert torch.equal(int4.unpack_kmajor(t(g["w13_ipex"]), True), q13)
+    assert torch.equal(int4.unpack_kmajor(t(g["w2_ipex"]), True), q2)
+    assert torch.equal(t(g["s13_ipex"]).permute(0, 2, 1).contiguous(), t(g["s13"]))
+
+
 def test_route_is_a_stable_counting_sort():
     ids = torch.tensor([[3, 1], [1, 0], [3, 3], [7, 1]], dtype=torch.int32)
     off, tok, p2p, rows = moe.route(ids, 4)   # id 7 is outside [0, 4): dropped
