@@ -105,6 +105,16 @@ B2Q_API int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, in
 B2Q_API int b2q_resadd_rmsnorm(const void* hidden, void* residual, const void* norm_weight, void* normed_out,
                        int act_dtype, int64_t M, int64_t K, float eps, void* stream);
 
+/* The general form behind b2q_resadd_rmsnorm, for the two further members of the family:
+ *   v = hidden ? (hidden + residual) * scalar : residual        (fp32; with hidden, residual <- v)
+ *   out1 = v * rsqrt(mean(v^2) + eps) * w1;   out2 = v * rsqrt(mean(v^2) + eps) * w2   (w2 / out2 both NULL or both set)
+ * esimd_scaled_resadd_norm_gemv_fp8_pert (csrc/xpu/esimd_kernels/scaled_resadd_norm_gemv_fp8.h:70-95) is
+ * hidden + scalar + one output followed by the FP8 GEMV; esimd_norm_gemv_norm_fp16
+ * (csrc/xpu/esimd_kernels/norm_gemv_norm_fp16.h:56-98) is hidden = NULL with two weights, out1 feeding the
+ * router GEMV and out2 being the MoE input.                                                              */
+B2Q_API int b2q_rmsnorm_fused(const void* hidden, void* residual, float scalar, const void* w1, void* out1,
+                      const void* w2, void* out2, int act_dtype, int64_t M, int64_t K, float eps, void* stream);
+
 /* Gated RMSNorm, the step the reference fuses in front of the GDN out_proj GEMV
  * (esimd_norm_gemv_fp8_pert / _fp8_blockscale / _int4_pert, csrc/xpu/torch_extension.cc:117-121 and
  * csrc/xpu/esimd_kernels/norm_gemv_fused.h, norm_gemv_int4.h):  per row of x [rows, V]

@@ -26,7 +26,7 @@ int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, 
 int act_prep(const void*, bool, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
 int act_split_fp8(const void*, bool, int64_t, void*, float*, int64_t, int, cudaStream_t);
 int quantize_q4_0(const void*, bool, int64_t, void*, void*, int64_t, int64_t, cudaStream_t);
-int resadd_rmsnorm(const void*, void*, const void*, void*, bool, int64_t, int, float, cudaStream_t);
+int resadd_rmsnorm(const void*, void*, const void*, void*, const void*, void*, bool, int64_t, int, float, float, cudaStream_t);
 int gated_rmsnorm(const void*, const void*, const void*, void*, bool, int, int, float, cudaStream_t);
 int act_split_i8(const void*, bool, int64_t, void*, float*, float*, int64_t, int, cudaStream_t);
 
@@ -116,7 +116,21 @@ int b2q_resadd_rmsnorm(const void* hidden, void* residual, const void* norm_weig
   if (M < 0 || K <= 0 || (K % 8) != 0) return B2Q_ERR_SHAPE;
   if (M > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if (!aligned16(hidden) || !aligned16(residual) || !aligned16(norm_weight) || !aligned16(normed_out)) return B2Q_ERR_ALIGN;
-  return resadd_rmsnorm(hidden, residual, norm_weight, normed_out, act_dtype == B2Q_BF16, M, (int)K, eps, (cudaStream_t)stream);
+  return resadd_rmsnorm(hidden, residual, norm_weight, normed_out, nullptr, nullptr, act_dtype == B2Q_BF16, M, (int)K, eps,
+                        1.0f, (cudaStream_t)stream);
+}
+
+int b2q_rmsnorm_fused(const void* hidden, void* residual, float scalar, const void* w1, void* out1, const void* w2,
+                      void* out2, int act_dtype, int64_t M, int64_t K, float eps, void* stream) {
+  if (!residual || !w1 || !out1 || ((w2 == nullptr) != (out2 == nullptr))) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (M < 0 || K <= 0 || (K % 8) != 0) return B2Q_ERR_SHAPE;
+  if (M > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  if (!aligned16(residual) || !aligned16(w1) || !aligned16(out1) || (hidden && !aligned16(hidden)) ||
+      (w2 && (!aligned16(w2) || !aligned16(out2))))
+    return B2Q_ERR_ALIGN;
+  return resadd_rmsnorm(hidden, residual, w1, out1, w2, out2, act_dtype == B2Q_BF16, M, (int)K, eps, scalar,
+                        (cudaStream_t)stream);
 }
 
 int b2q_gated_rmsnorm(const void* x, const void* z, const void* norm_weight, void* out, int act_dtype, int64_t rows, int64_t V,

@@ -898,26 +898,45 @@ int act_split_i8(const void* x, bool in_bf16, int64_t ldx, void* xq, float* inv_
 // The norm is taken of the fp32 sum, not of its 16-bit rounding, as the reference's step-by-step check does
 // (tests/test_resadd_norm_gemv_int4.py:41-59).  One block per row; the GEMV's own pre-pass follows and overlaps
 // through programmatic dependent launch.
+// Generalised for the two further members of the family: `scalar` multiplies the sum before anything else
+// (esimd_scaled_resadd_norm_gemv_fp8_pert, csrc/xpu/esimd_kernels/scaled_resadd_norm_gemv_fp8.h:70-95); hidden == nullptr
+// skips the add and leaves the residual untouched, and a second weight writes a second normalised row from the same
+// 1/rms (esimd_norm_gemv_norm_fp16, csrc/xpu/esimd_kernels/norm_gemv_norm_fp16.h:56-98).
 template <bool BF16>
 __global__ void resadd_rmsnorm_kernel(const void* __restrict__ hidden, void* __restrict__ residual, const void* __restrict__ weight,
-                                      void* __restrict__ normed, int K, float eps) {
+                                      void* __restrict__ normed, const void* __restrict__ weight2, void* __restrict__ normed2,
+                                      int K, float eps, float scalar) {
   using T = typename Act<BF16>::T;
   __shared__ float red[32];
   __shared__ float inv_sh;
   grid_dep_wait();
   grid_dep_release();
   const int64_t r = blockIdx.x;
-  const T* h = reinterpret_cast<const T*>(hidden) + r * K;
+  const T* h = hidden ? reinterpret_cast<const T*>(hidden) + r * K : nullptr;
   T* res = reinterpret_cast<T*>(residual) + r * K;
   const T* w = reinterpret_cast<const T*>(weight);
+  const T* w2 = reinterpret_cast<const T*>(weight2);
   T* out = reinterpret_cast<T*>(normed) + r * K;
+  T* out2 = normed2 ? reinterpret_cast<T*>(normed2) + r * K : nullptr;
+  auto load8 = [&](int k, float* v) {
+    const uint4 rv = *reinterpret_cast<const uint4*>(res + k);
+    const T* re = reinterpret_cast<const T*>(&rv);
+    if (h) {
+      const uint4 hv = *reinterpret_cast<const uint4*>(h + k);
+      const T* he = reinterpret_cast<const T*>(&hv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = (Act<BF16>::to_f(he[j]) + Act<BF16>::to_f(re[j])) * scalar;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = Act<BF16>::to_f(re[j]);
+    }
+  };
   float ss = 0.f;
   for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-    const uint4 hv = *reinterpret_cast<const uint4*>(h + k), rv = *reinterpret_cast<const uint4*>(res + k);
-    const T* he = reinterpret_cast<const T*>(&hv);
-    const T* re = reinterpret_cast<const T*>(&rv);
+    float v[8];
+    load8(k, v);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) { const float v = Act<BF16>::to_f(he[j]) + Act<BF16>::to_f(re[j]); ss = fmaf(v, v, ss); }
+    for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
@@ -932,34 +951,39 @@ __global__ void resadd_rmsnorm_kernel(const void* __restrict__ hidden, void* __r
   const float inv = inv_sh;
   // second pass over the same (cache-resident) inputs: only now is the residual overwritten
   for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
-    const uint4 hv = *reinterpret_cast<const uint4*>(h + k), rv = *reinterpret_cast<const uint4*>(res + k);
+    float v[8];
+    load8(k, v);
     const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
-    const T* he = reinterpret_cast<const T*>(&hv);
-    const T* re = reinterpret_cast<const T*>(&rv);
     const T* we = reinterpret_cast<const T*>(&wv);
     uint4 so, no;
     T* se = reinterpret_cast<T*>(&so);
     T* ne = reinterpret_cast<T*>(&no);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float v = Act<BF16>::to_f(he[j]) + Act<BF16>::to_f(re[j]);
-      se[j] = Act<BF16>::from_f(v);
-      ne[j] = Act<BF16>::from_f(v * inv * Act<BF16>::to_f(we[j]));
+      se[j] = Act<BF16>::from_f(v[j]);
+      ne[j] = Act<BF16>::from_f(v[j] * inv * Act<BF16>::to_f(we[j]));
     }
-    *reinterpret_cast<uint4*>(res + k) = so;
+    if (h) *reinterpret_cast<uint4*>(res + k) = so;
     *reinterpret_cast<uint4*>(out + k) = no;
+    if (out2) {
+      const uint4 w2v = *reinterpret_cast<const uint4*>(w2 + k);
+      const T* w2e = reinterpret_cast<const T*>(&w2v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ne[j] = Act<BF16>::from_f(v[j] * inv * Act<BF16>::to_f(w2e[j]));
+      *reinterpret_cast<uint4*>(out2 + k) = no;
+    }
   }
 }
 
-int resadd_rmsnorm(const void* hidden, void* residual, const void* weight, void* normed, bool bf16, int64_t M, int K, float eps,
-                   cudaStream_t st) {
+int resadd_rmsnorm(const void* hidden, void* residual, const void* weight, void* normed, const void* weight2, void* normed2,
+                   bool bf16, int64_t M, int K, float eps, float scalar, cudaStream_t st) {
   if (M == 0) return B2Q_OK;
   int threads = (K / 8 + 31) / 32 * 32;
   threads = threads > 1024 ? 1024 : (threads < 32 ? 32 : threads);
   const bool overlap = tls().overlap_mode > 0;
   cudaError_t e;
-  if (bf16) e = launch_overlapped(resadd_rmsnorm_kernel<true>, dim3((unsigned)M), dim3(threads), 0, st, overlap, hidden, residual, weight, normed, K, eps);
-  else e = launch_overlapped(resadd_rmsnorm_kernel<false>, dim3((unsigned)M), dim3(threads), 0, st, overlap, hidden, residual, weight, normed, K, eps);
+  if (bf16) e = launch_overlapped(resadd_rmsnorm_kernel<true>, dim3((unsigned)M), dim3(threads), 0, st, overlap, hidden, residual, weight, normed, weight2, normed2, K, eps, scalar);
+  else e = launch_overlapped(resadd_rmsnorm_kernel<false>, dim3((unsigned)M), dim3(threads), 0, st, overlap, hidden, residual, weight, normed, weight2, normed2, K, eps, scalar);
   note_launch("resadd_rmsnorm");
   return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
 }

@@ -19,7 +19,7 @@ from .ops import (  # noqa: F401
     esimd_resadd_norm_gemv_fp8_pert, esimd_resadd_norm_gemv_int4_pert, esimd_resadd_norm_gemv2_fp8_pert, q4_0_quantize,
     esimd_norm_gemv_fp8_pert, esimd_norm_gemv_fp8_blockscale, esimd_norm_gemv_int4_pert,
     moe_router_forward_int4, moe_router_topk_int4, moe_forward_full_int4, moe_shared_expert_forward_int4_nmajor,
-    moe_forward_cutlass_nmajor_int4_full,
+    moe_forward_cutlass_nmajor_int4_full, esimd_scaled_resadd_norm_gemv_fp8_pert, esimd_norm_gemv_norm_fp16,
 )
 
 launch_count = _lib.launch_count

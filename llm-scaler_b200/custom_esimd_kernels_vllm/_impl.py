@@ -136,6 +136,28 @@ def resadd_rmsnorm(hidden_states, residual, norm_weight, normed_out, eps):
                                           L.dt(hidden_states), M, K, float(eps), L.stream(hidden_states)))
 
 
+def rmsnorm_fused(hidden_states, residual, scalar, w1, out1, w2, out2, eps):
+    """v = (hidden + residual) * scalar (residual <- v) or v = residual when hidden_states is None;
+    out1 = rmsnorm(v) * w1 and, when w2 / out2 are given, out2 = rmsnorm(v) * w2 (b2q_rmsnorm_fused)."""
+    L.require_cuda(residual, w1, out1)
+    _chk(residual.dim() == 2 and residual.dtype in (torch.bfloat16, torch.float16) and residual.is_contiguous(),
+         "residual must be a contiguous 2-D bf16 / fp16 tensor")
+    M, K = residual.shape
+    _chk(K % 8 == 0, "K must be a multiple of 8")
+    for t, what in ((hidden_states, "hidden_states"), (out1, "out1"), (out2, "out2")):
+        if t is not None:
+            _chk(t.dtype == residual.dtype and tuple(t.shape) == (M, K) and t.is_contiguous(),
+                 what + " must be a contiguous [M, K] tensor of the activation type")
+    for t, what in ((w1, "w1"), (w2, "w2")):
+        if t is not None:
+            _chk(t.dtype == residual.dtype and t.numel() == K and t.is_contiguous(), what + " must be a contiguous [K] tensor")
+    _chk((w2 is None) == (out2 is None), "w2 and out2 go together")
+    with L.on_device(residual):
+        L.check(L.lib.b2q_rmsnorm_fused(L.ptr(hidden_states), residual.data_ptr(), float(scalar), w1.data_ptr(),
+                                         out1.data_ptr(), L.ptr(w2), L.ptr(out2), L.dt(residual), M, K, float(eps),
+                                         L.stream(residual)))
+
+
 def gated_rmsnorm(x, z, norm_weight, eps):
     """rmsnorm(x) * norm_weight * silu(z) per row of x [rows, V]; returns a new [1, rows * V] tensor."""
     L.require_cuda(x, z, norm_weight)

@@ -204,6 +204,25 @@ def _resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s0, o0
     return o0
 
 
+def _scaled_resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, qkv_weight, qkv_scale, qkv_out, eps, scalar):
+    normed = torch.empty_like(residual)
+    I.rmsnorm_fused(hidden_states, residual, scalar, norm_weight, normed, None, None, eps)
+    I.linear_fp8(normed, qkv_weight, qkv_scale, qkv_out, L.SCALE_TENSOR)
+
+
+def _norm_gemv_norm_fp16(residual, scale_with_root, proj_w, pre_ff_w, router_logits, moe_input, eps):
+    # shared 1/rms, two post-norm scales in one launch; the 16-bit dense router projection is a plain library GEMM
+    router_in = torch.empty_like(residual)
+    I.rmsnorm_fused(None, residual, 1.0, scale_with_root, router_in, pre_ff_w, moe_input, eps)
+    torch.matmul(router_in, proj_w.t(), out=router_logits)
+
+
+_op(NS, "esimd_scaled_resadd_norm_gemv_fp8_pert(Tensor hidden_states, Tensor residual, "
+        "Tensor norm_weight, Tensor qkv_weight, Tensor qkv_scale, Tensor qkv_out, "
+        "float eps, float scalar) -> ()", _scaled_resadd_norm_gemv_fp8_pert)
+_op(NS, "esimd_norm_gemv_norm_fp16(Tensor residual, Tensor scale_with_root, "
+        "Tensor proj_w, Tensor pre_ff_w, Tensor router_logits, Tensor moe_input, "
+        "float eps) -> ()", _norm_gemv_norm_fp16)
 _op(NS, "esimd_resadd_norm_gemv_fp8_pert(Tensor hidden_states, Tensor residual, Tensor norm_weight, Tensor gemv_weight, "
         "Tensor gemv_scale, Tensor output, Tensor normed_out, float eps) -> Tensor", _resadd_norm_gemv_fp8_pert)
 _op(NS, "esimd_resadd_norm_gemv_int4_pert(Tensor hidden_states, Tensor residual, Tensor norm_weight, Tensor gemv_weight, "

@@ -249,6 +249,19 @@ def esimd_resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s
     return _ops.esimd_resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s0, o0, w1, s1, o1, eps)
 
 
+def esimd_scaled_resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, qkv_weight, qkv_scale, qkv_out, eps,
+                                           scalar):
+    """residual <- (hidden + residual) * scalar; qkv_out = FP8 GEMV of rmsnorm(residual) * norm_weight (ops.py:1832-1849)."""
+    return _ops.esimd_scaled_resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, qkv_weight, qkv_scale,
+                                                       qkv_out, eps, scalar)
+
+
+def esimd_norm_gemv_norm_fp16(residual, scale_with_root, proj_w, pre_ff_w, router_logits, moe_input, eps):
+    """router_logits = (rmsnorm(residual) * scale_with_root) @ proj_w^T and moe_input = rmsnorm(residual) * pre_ff_w from
+    one shared 1/rms (ops.py:1801-1829)."""
+    return _ops.esimd_norm_gemv_norm_fp16(residual, scale_with_root, proj_w, pre_ff_w, router_logits, moe_input, eps)
+
+
 def q4_0_quantize(input, out_qweight, out_scale):
     """GGML Q4_0 (group 128) on the device: fills out_qweight int32 [M, K/8] and out_scale fp16 [M, K/128]."""
     _ops.q4_0_quantize(input, out_qweight, out_scale)

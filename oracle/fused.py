@@ -21,3 +21,19 @@ def gated_rmsnorm(x: torch.Tensor, z: torch.Tensor, norm_weight: torch.Tensor, e
     n = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + eps)
     n = n * norm_weight.float() * torch.nn.functional.silu(z.float())
     return n.to(x.dtype).flatten().unsqueeze(0)
+
+
+def scaled_resadd_rmsnorm(hidden, residual, norm_weight, eps, scalar):
+    """v = (hidden + residual) * scalar in fp32; residual' = v -> 16 bit; normed = v * rsqrt(mean(v^2) + eps) * weight
+    (csrc/xpu/esimd_kernels/scaled_resadd_norm_gemv_fp8.h:70-95)."""
+    dt = hidden.dtype
+    v = (hidden.float() + residual.float()) * scalar
+    inv = torch.rsqrt(v.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return v.to(dt), (v * inv * norm_weight.float()).to(dt)
+
+
+def norm_two_scales(residual, w1, w2, eps):
+    """One 1/rms of the row, two post-norm scales (csrc/xpu/esimd_kernels/norm_gemv_norm_fp16.h:56-98)."""
+    v = residual.float()
+    n = v * torch.rsqrt(v.pow(2).mean(dim=-1, keepdim=True) + eps)
+    return (n * w1.float()).to(residual.dtype), (n * w2.float()).to(residual.dtype)

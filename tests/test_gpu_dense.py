@@ -332,3 +332,42 @@ def test_gated_norm_gemv_fused_ops(e, HV, V, N, dtype):
     q, s = _rand_int4(N, K, dtype, N)
     e.esimd_norm_gemv_int4_pert(core.to(DEV), gate.to(DEV), nw.to(DEV), int4.pack_nmajor_i32(q).to(DEV), s.to(DEV), out, HV, V, 1e-6)
     assert_close(out, int4.linear(normed_d, q, s), what="gated norm + int4")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("N,K,scalar", [(256, 512, 0.5), (1024, 2816, 1.7), (128, 4096, 1.0)])
+def test_scaled_resadd_norm_gemv_fp8(e, N, K, scalar, dtype):
+    """esimd_scaled_resadd_norm_gemv_fp8_pert: residual <- (h + r) * scalar in place, then norm and the per-tensor GEMV."""
+    from oracle import fused
+    g = torch.Generator().manual_seed(N + K)
+    hidden = torch.randn(1, K, generator=g).to(dtype)
+    residual = torch.randn(1, K, generator=g).to(dtype)
+    nw = (torch.randn(K, generator=g) * 0.1 + 1.0).to(dtype)
+    wq, ws = fp8.quantize_tensor(torch.randn(N, K, generator=g) * 0.05)
+    ref_res, ref_normed = fused.scaled_resadd_rmsnorm(hidden, residual, nw, 1e-6, scalar)
+    res_d = residual.to(DEV).clone()
+    out = torch.empty(1, N, dtype=dtype, device=DEV)
+    r = e.esimd_scaled_resadd_norm_gemv_fp8_pert(hidden.to(DEV), res_d, nw.to(DEV), wq.to(DEV), ws.to(DEV), out, 1e-6, scalar)
+    assert r is None
+    assert torch.equal(res_d.cpu(), ref_res)
+    assert_close(out, fp8.linear_tensor(ref_normed, wq, ws), what="scaled resadd + norm + fp8 gemv")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("N,K", [(128, 2816), (64, 512), (8, 1024)])
+def test_norm_gemv_norm_two_outputs(e, N, K, dtype):
+    """esimd_norm_gemv_norm_fp16: router logits and the MoE input from one shared 1/rms; the residual is not written."""
+    from oracle import fused
+    g = torch.Generator().manual_seed(N * K)
+    residual = torch.randn(1, K, generator=g).to(dtype)
+    sw = (torch.randn(K, generator=g) * 0.2 + 1.0).to(dtype)
+    pw = (torch.randn(K, generator=g) * 0.2 + 1.0).to(dtype)
+    proj = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    ref_in, ref_moe = fused.norm_two_scales(residual, sw, pw, 1e-6)
+    res_d = residual.to(DEV).clone()
+    logits = torch.empty(1, N, dtype=dtype, device=DEV)
+    moe_in = torch.empty(1, K, dtype=dtype, device=DEV)
+    e.esimd_norm_gemv_norm_fp16(res_d, sw.to(DEV), proj.to(DEV), pw.to(DEV), logits, moe_in, 1e-6)
+    assert torch.equal(res_d.cpu(), residual)
+    assert_close(moe_in, ref_moe, what="moe_input", tol=4e-3)
+    assert_close(logits, (ref_in.float() @ proj.float().T).to(dtype), what="router logits")
