@@ -131,6 +131,16 @@ B2Q_API int b2q_gated_rmsnorm(const void* x, const void* z, const void* norm_wei
 B2Q_API int b2q_quantize_q4_0(const void* x, int act_dtype, int64_t ldx, void* qweight, void* scale_f16,
                       int64_t M, int64_t K, void* stream);
 
+/* FP8 (e4m3) weight quantisation, the load-time step that produces b2q_linear_fp8's inputs:
+ *   scale = max(amax, 1e-12) / 448 (fp32) per 128 x 128 block / per output row / per tensor (scale_mode, with the
+ *   scale shapes of B2Q_SCALE_*), wq[n, k] = e4m3(w[n, k] / scale): fp32 division, one round-to-nearest-even.
+ * w is bf16, fp16 or fp32 [N, K] with row pitch ldw (elements); wq is contiguous [N, K] bytes.  Ragged edge
+ * blocks are allowed.  Follows the recipe of tests/test_fp8_blockscale_gemm.py:13-28 (block),
+ * tests/test_fp8_blockscale_moe_prefill.py:18-51 and the per-channel / per-tensor scale rules of
+ * vllm/patches/vllm_for_multi_arc.patch:477-580.                                                       */
+B2Q_API int b2q_quantize_fp8(const void* w, int w_dtype, int64_t ldw, void* wq, float* scale, int scale_mode,
+                     int64_t N, int64_t K, void* stream);
+
 /* ---- dense weight-only linear: out[M, N] = x[M, K] * dequant(W)[N, K]^T --
  * fp32 accumulate, one rounding to act_dtype (x and out share act_dtype).
  * Replaces esimd_gemv_int4 / esimd_gemm_int4_pgrp

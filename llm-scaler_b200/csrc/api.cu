@@ -20,6 +20,7 @@ int moe_route(const int32_t*, int64_t, int, int32_t*, int32_t*, int32_t*, int32_
 int moe_build_tiles(const int32_t*, int, int, int32_t*, cudaStream_t);
 int gather_rows(const void*, const int32_t*, int, void*, int64_t, int64_t, int, cudaStream_t);
 int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t, int64_t ld_in = 0);
+int quantize_fp8(const void*, int, int64_t, void*, float*, int, int64_t, int64_t, cudaStream_t);
 int shared_gate_add(const void*, const void*, const void*, const void*, void*, int, int64_t, int64_t, cudaStream_t);
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
@@ -107,6 +108,16 @@ int b2q_quantize_q4_0(const void* x, int act_dtype, int64_t ldx, void* qweight, 
   if (M > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if ((reinterpret_cast<uintptr_t>(x) & 7u) || ((ldx * 2) & 7u)) return B2Q_ERR_ALIGN;
   return quantize_q4_0(x, act_dtype == B2Q_BF16, ldx, qweight, scale_f16, M, K, (cudaStream_t)stream);
+}
+
+int b2q_quantize_fp8(const void* w, int w_dtype, int64_t ldw, void* wq, float* scale, int scale_mode, int64_t N, int64_t K,
+                     void* stream) {
+  if (!w || !wq || !scale) return B2Q_ERR_NULL;
+  if (w_dtype != B2Q_BF16 && w_dtype != B2Q_F16 && w_dtype != B2Q_F32) return B2Q_ERR_DTYPE;
+  if (scale_mode < 0 || scale_mode > 2) return B2Q_ERR_LAYOUT;
+  if (N < 0 || K < 0 || ldw < K) return B2Q_ERR_SHAPE;
+  if (N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
+  return quantize_fp8(w, w_dtype, ldw, wq, scale, scale_mode, N, K, (cudaStream_t)stream);
 }
 
 int b2q_resadd_rmsnorm(const void* hidden, void* residual, const void* norm_weight, void* normed_out, int act_dtype, int64_t M,

@@ -2,6 +2,7 @@
 // linear kernels consume.  HBM-bound elementwise work: one thread produces
 // eight consecutive k of one row and stores them with a single 16-byte (or
 // 32-byte for fp32) write.
+#include <cuda_fp8.h>
 #include "common.cuh"
 
 namespace b2q {
@@ -175,6 +176,112 @@ int quantize_q4_0(const void* x, bool in_bf16, int64_t ldx, void* qweight, void*
     quantize_q4_0_kernel<false><<<grid, wpb * 32, 0, st>>>(x, ldx, reinterpret_cast<uint32_t*>(qweight),
                                                            reinterpret_cast<__half*>(scale), M, (int)K);
   note_launch("quantize_q4_0");
+  return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// FP8 (e4m3) weight quantisers, the load-time step that produces the FP8 GEMMs' inputs:
+//   scale = max(amax, 1e-12) / 448 in fp32 over the scale's domain (a 128 x 128 block, an output row, the tensor),
+//   q = e4m3(w / scale): an IEEE fp32 division, then one round-to-nearest-even conversion
+// (tests/test_fp8_blockscale_gemm.py:13-28 for the block form).  Ragged edge blocks take their maximum over the
+// elements that exist.  Source types: bf16, fp16, fp32.
+__device__ __forceinline__ float load_src(const void* w, int64_t i, int dt) { return load_scalar(w, i, dt); }
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float a = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, red[i]);
+  __syncthreads();
+  return a;
+}
+
+__device__ __forceinline__ uint8_t to_e4m3(float v, float s) {
+  return (uint8_t)__nv_cvt_float_to_fp8(__fdiv_rn(v, s), __NV_SATFINITE, __NV_E4M3);
+}
+
+// one CTA of 256 threads per 128 x 128 block; thread t owns column t % 128 of rows t / 128, t / 128 + 2, ...
+__global__ void quantize_fp8_block_kernel(const void* __restrict__ w, int dt, int64_t ldw, uint8_t* __restrict__ wq,
+                                          float* __restrict__ scale, int64_t N, int64_t K) {
+  __shared__ float red[8];
+  const int64_t kb = blockIdx.x, nb = blockIdx.y;
+  const int c = threadIdx.x & 127, r0 = threadIdx.x >> 7;
+  const int64_t k = kb * 128 + c;
+  float amax = 0.f;
+  if (k < K)
+    for (int r = r0; r < 128; r += 2) {
+      const int64_t n = nb * 128 + r;
+      if (n < N) amax = fmaxf(amax, fabsf(load_src(w, n * ldw + k, dt)));
+    }
+  amax = block_max(amax, red);
+  const float s = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+  if (threadIdx.x == 0) scale[nb * gridDim.x + kb] = s;
+  if (k < K)
+    for (int r = r0; r < 128; r += 2) {
+      const int64_t n = nb * 128 + r;
+      if (n < N) wq[n * K + k] = to_e4m3(load_src(w, n * ldw + k, dt), s);
+    }
+}
+
+// one CTA per output row
+__global__ void quantize_fp8_channel_kernel(const void* __restrict__ w, int dt, int64_t ldw, uint8_t* __restrict__ wq,
+                                            float* __restrict__ scale, int64_t K) {
+  __shared__ float red[32];
+  const int64_t n = blockIdx.x;
+  float amax = 0.f;
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(load_src(w, n * ldw + k, dt)));
+  amax = block_max(amax, red);
+  const float s = __fdiv_rn(fmaxf(amax, 1e-12f), 448.0f);
+  if (threadIdx.x == 0) scale[n] = s;
+  for (int64_t k = threadIdx.x; k < K; k += blockDim.x) wq[n * K + k] = to_e4m3(load_src(w, n * ldw + k, dt), s);
+}
+
+// per tensor: the maximum is gathered in scale[0] as the bit pattern of a non-negative float (which orders like an
+// unsigned integer), the elements are quantised against it, and a last one-thread launch turns it into the scale
+__global__ void quantize_fp8_tensor_max_kernel(const void* __restrict__ w, int dt, int64_t ldw, float* scale, int64_t N,
+                                               int64_t K) {
+  __shared__ float red[32];
+  float amax = 0.f;
+  const int64_t total = N * K;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    amax = fmaxf(amax, fabsf(load_src(w, (i / K) * ldw + (i % K), dt)));
+  amax = block_max(amax, red);
+  if (threadIdx.x == 0) atomicMax(reinterpret_cast<unsigned int*>(scale), __float_as_uint(amax));
+}
+
+__global__ void quantize_fp8_tensor_kernel(const void* __restrict__ w, int dt, int64_t ldw, uint8_t* __restrict__ wq,
+                                           const float* scale, int64_t N, int64_t K) {
+  const float s = __fdiv_rn(fmaxf(scale[0], 1e-12f), 448.0f);
+  const int64_t total = N * K;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    wq[i] = to_e4m3(load_src(w, (i / K) * ldw + (i % K), dt), s);
+}
+
+__global__ void quantize_fp8_tensor_finish_kernel(float* scale) { scale[0] = __fdiv_rn(fmaxf(scale[0], 1e-12f), 448.0f); }
+
+int quantize_fp8(const void* w, int dt, int64_t ldw, void* wq, float* scale, int scale_mode, int64_t N, int64_t K,
+                 cudaStream_t st) {
+  if (N == 0 || K == 0) return B2Q_OK;
+  uint8_t* q = reinterpret_cast<uint8_t*>(wq);
+  if (scale_mode == B2Q_SCALE_BLOCK128) {
+    const dim3 grid((unsigned)((K + 127) / 128), (unsigned)((N + 127) / 128));
+    quantize_fp8_block_kernel<<<grid, 256, 0, st>>>(w, dt, ldw, q, scale, N, K);
+    note_launch("quantize_fp8_block");
+  } else if (scale_mode == B2Q_SCALE_CHANNEL) {
+    quantize_fp8_channel_kernel<<<(unsigned)N, 256, 0, st>>>(w, dt, ldw, q, scale, K);
+    note_launch("quantize_fp8_channel");
+  } else {
+    if (cudaMemsetAsync(scale, 0, sizeof(float), st) != cudaSuccess) return B2Q_ERR_CUDA;
+    const int64_t total = N * K;
+    int64_t g = (total + 1023) / 1024;
+    g = g > 148 * 8 ? 148 * 8 : g;
+    quantize_fp8_tensor_max_kernel<<<(unsigned)g, 256, 0, st>>>(w, dt, ldw, scale, N, K);
+    quantize_fp8_tensor_kernel<<<(unsigned)g, 256, 0, st>>>(w, dt, ldw, q, scale, N, K);
+    quantize_fp8_tensor_finish_kernel<<<1, 1, 0, st>>>(scale);
+    note_launch("quantize_fp8_tensor");
+  }
   return launch_status();
 }
 

@@ -230,6 +230,23 @@ def dequant_fp8(weight, weight_scale, scale_mode, out_dtype=torch.float32):
     return out
 
 
+def quantize_fp8(w, scale_mode):
+    """e4m3 weight quantisation on the device: (wq [N, K] float8_e4m3fn, scale fp32) with the scale shape of scale_mode:
+    [N] per channel, [1] per tensor, [ceil(N/128), ceil(K/128)] per block (b2q_quantize_fp8)."""
+    L.require_cuda(w)
+    _chk(w.dim() == 2 and w.stride(1) == 1 and w.dtype in (torch.bfloat16, torch.float16, torch.float32),
+         "weight must be a 2-D bf16 / fp16 / fp32 tensor with contiguous rows")
+    N, K = w.shape
+    shape = {L.SCALE_CHANNEL: (N,), L.SCALE_TENSOR: (1,), L.SCALE_BLOCK128: ((N + 127) // 128, (K + 127) // 128)}[scale_mode]
+    wq = torch.empty(N, K, dtype=torch.float8_e4m3fn, device=w.device)
+    scale = torch.empty(shape, dtype=torch.float32, device=w.device)
+    dt = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}[w.dtype]
+    with L.on_device(w):
+        L.check(L.lib.b2q_quantize_fp8(w.data_ptr(), dt, w.stride(0), wq.data_ptr(), scale.data_ptr(), scale_mode, N, K,
+                                        L.stream(w)))
+    return wq, scale
+
+
 def act_quant_fp8_1x128(x):
     L.require_cuda(x)
     M, K = x.shape

@@ -28,6 +28,7 @@ _SIGS = {
     "b2q_dequant_int4": (i32, [vp, i32, vp, i32, vp, i32, i64, i64, i32, vp]),
     "b2q_dequant_fp8": (i32, [vp, i32, vp, i32, i32, vp, i32, i64, i64, vp]),
     "b2q_resadd_rmsnorm": (i32, [vp, vp, vp, vp, i32, i64, i64, C.c_float, vp]),
+    "b2q_quantize_fp8": (i32, [vp, i32, i64, vp, vp, i32, i64, i64, vp]),
     "b2q_rmsnorm_fused": (i32, [vp, vp, C.c_float, vp, vp, vp, vp, i32, i64, i64, C.c_float, vp]),
     "b2q_gated_rmsnorm": (i32, [vp, vp, vp, vp, i32, i64, i64, C.c_float, vp]),
     "b2q_quantize_q4_0": (i32, [vp, i32, i64, vp, vp, i64, i64, vp]),

@@ -371,3 +371,31 @@ def test_norm_gemv_norm_two_outputs(e, N, K, dtype):
     assert torch.equal(res_d.cpu(), residual)
     assert_close(moe_in, ref_moe, what="moe_input", tol=4e-3)
     assert_close(logits, (ref_in.float() @ proj.float().T).to(dtype), what="router logits")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("N,K", [(256, 384), (300, 200), (1, 128), (129, 130), (1024, 5120)])
+def test_fp8_weight_quantisers_bit_exact(e, N, K, dtype, golden):
+    """b2q_quantize_fp8 in its three scale modes: scales and e4m3 codes identical to the oracle quantisers (which the
+    golden vectors pin to the reference's block recipe), ragged edge blocks, an all-zero block and a strided source."""
+    I_, L = e._impl, e._lib
+    g = torch.Generator().manual_seed(N * 3 + K)
+    w = (torch.randn(N, K, generator=g) * 0.07).to(dtype)
+    if N > 128:
+        w[128:, :min(K, 128)] = 0                      # a block of zeros: scale clamps at 1e-12 / 448
+    for mode, ref in ((L.SCALE_BLOCK128, fp8.quantize_block), (L.SCALE_CHANNEL, fp8.quantize_channel),
+                      (L.SCALE_TENSOR, fp8.quantize_tensor)):
+        rq, rs = ref(w)
+        q, s = I_.quantize_fp8(w.to(DEV), mode)
+        assert torch.equal(s.cpu().reshape(rs.shape), rs), f"scale, mode {mode}"
+        assert torch.equal(q.cpu().view(torch.uint8), rq.view(torch.uint8)), f"codes, mode {mode}"
+    wide = torch.zeros(N, K + 24, dtype=dtype)
+    wide[:, :K] = w
+    q2, s2 = I_.quantize_fp8(wide.to(DEV)[:, :K], L.SCALE_BLOCK128)
+    rq, rs = fp8.quantize_block(w)
+    assert torch.equal(s2.cpu(), rs) and torch.equal(q2.cpu().view(torch.uint8), rq.view(torch.uint8))
+    if (N, K) == (256, 384) and dtype == torch.float32:
+        gg = golden("fp8_block")                       # the reference recipe's own output
+        wq, ws = I_.quantize_fp8(torch.from_numpy(gg["w"]).to(DEV), L.SCALE_BLOCK128)
+        assert torch.equal(ws.cpu(), torch.from_numpy(gg["ws"]))
+        assert torch.equal(wq.cpu().view(torch.uint8), torch.from_numpy(gg["wq"]))
