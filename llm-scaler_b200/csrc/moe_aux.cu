@@ -685,9 +685,108 @@ __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const i
   }
 }
 
+// The same pre-pass with one WARP per row, for rows of at most MAXI * 256 values (K a multiple of 256): the lane keeps
+// its MAXI 16-byte pieces in registers between the maximum and the conversion, all loads are issued before the first
+// use, and the reduction is five shuffles.  Rows of a few KB were paying mostly for the block-wide barriers.
+template <bool IN_BF16, bool GATED, int MAXI>
+__global__ void __launch_bounds__(256) act_prep_warp_kernel(const void* __restrict__ x, int64_t ldx, const int32_t* __restrict__ idx,
+                                                            int div, __half* __restrict__ x16, float* __restrict__ inv_scale,
+                                                            int64_t rows, int K, int perm, int release_early) {
+  using A = Act<IN_BF16>;
+  using T = typename A::T;
+  if (release_early) grid_dep_release();
+  grid_dep_wait();
+  if (!release_early) grid_dep_release();
+  const int lane = threadIdx.x & 31;
+  const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int64_t srow = idx ? (int64_t)(idx[r] / div) : r;
+  const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + srow * ldx;
+  const int iters = K >> 8;
+  uint4 raw[MAXI], up[GATED ? MAXI : 1];
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i)
+    if (i < iters) {
+      raw[i] = *reinterpret_cast<const uint4*>(row + (i * 32 + lane) * 8);
+      if constexpr (GATED) up[i] = *reinterpret_cast<const uint4*>(row + K + (i * 32 + lane) * 8);
+    }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i)
+    if (i < iters) {
+      T* e = reinterpret_cast<T*>(&raw[i]);
+      if constexpr (GATED) {
+        const T* ue = reinterpret_cast<const T*>(&up[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float gv = A::to_f(e[j]);
+          const float sl = gv / (1.0f + expf(-gv));
+          e[j] = A::from_f(sl * A::to_f(ue[j]));               // the activated value, rounded as silu_mul stores it
+        }
+      }
+      if constexpr (IN_BF16) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(A::to_f(e[j])));
+      }
+    }
+  float sc = 1.f;
+  if constexpr (IN_BF16) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (amax > 0.f && amax < INFINITY) {
+      const int ex = (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127;
+      int sh = 14 - ex;
+      sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+      sc = __uint_as_float((uint32_t)(sh + 127) << 23);
+    }
+  }
+  if (lane == 0) inv_scale[r] = 1.0f / sc;
+#pragma unroll
+  for (int i = 0; i < MAXI; ++i)
+    if (i < iters) {
+      const T* e = reinterpret_cast<const T*>(&raw[i]);
+      __half h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) h[j] = __float2half_rn(A::to_f(e[j]) * sc);
+      uint4 o;
+      __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int src = perm == 1 ? ((j & 1) * 4 + (j >> 1)) : (perm == 2 ? ((j & 3) * 2 + (j >> 2)) : j);
+        oh[j] = h[src];
+      }
+      *reinterpret_cast<uint4*>(x16 + r * (int64_t)K + (i * 32 + lane) * 8) = o;
+    }
+}
+
+template <bool IN_BF16, bool GATED>
+static cudaError_t act_prep_warp_launch(const void* x, int64_t ldx, const int32_t* idx, int div, void* x16, float* inv_scale,
+                                        int64_t rows, int K, int perm, int mode, cudaStream_t st) {
+  const dim3 grid((unsigned)((rows + 7) / 8)), block(256);
+  const int iters = K >> 8;
+  auto go = [&](auto kern) {
+    return launch_overlapped(kern, grid, block, 0, st, mode > 0, x, ldx, idx, div > 0 ? div : 1,
+                             reinterpret_cast<__half*>(x16), inv_scale, rows, K, perm, mode == 2 ? 1 : 0);
+  };
+  if (iters <= 4) return go(act_prep_warp_kernel<IN_BF16, GATED, 4>);
+  if (iters <= 8) return go(act_prep_warp_kernel<IN_BF16, GATED, 8>);
+  return go(act_prep_warp_kernel<IN_BF16, GATED, GATED ? 8 : 16>);
+}
+
 int act_prep(const void* x, bool in_bf16, bool gated, int64_t ldx, const int32_t* idx, int div, void* x16,
              float* inv_scale, int64_t rows, int K, int perm, cudaStream_t st) {
   if (rows == 0) return B2Q_OK;
+  // many short rows (the grouped GEMMs' pre-pass): one warp per row
+  if (rows >= 1024 && (K & 255) == 0 && K <= (gated ? 2048 : 4096)) {
+    const int mode = tls().overlap_mode;
+    cudaError_t e;
+    if (in_bf16) e = gated ? act_prep_warp_launch<true, true>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st)
+                           : act_prep_warp_launch<true, false>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st);
+    else         e = gated ? act_prep_warp_launch<false, true>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st)
+                           : act_prep_warp_launch<false, false>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st);
+    note_launch("act_prep");
+    return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
+  }
   int threads = (K / 8 + 31) / 32 * 32;
   threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
   const int mode = tls().overlap_mode;
