@@ -364,7 +364,9 @@ inline int smallm_launch_one(const SmallMParams& p, int m_max, int n_tiles_cap, 
   dim3 grid((p.N + ROWS - 1) / ROWS, p.tiles ? n_tiles_cap : (m_max + NT * 8 - 1) / (NT * 8), 1);
   // overlap with the previous kernel only when the caller has declared the weights static (overlap mode 2): this
   // kernel has no pre-pass of its own in front of it that would order it behind whatever wrote them
-  const bool overlap = tls().overlap_mode == 2 && !p.tiles;
+  // (and only for weights of more than 2^25 elements: launches this short measured 6 % slower overlapped, their CTAs all
+  // reading the same activation rows at once)
+  const bool overlap = tls().overlap_mode == 2 && !p.tiles && (int64_t)p.N * p.K > ((int64_t)1 << 25);
   if (launch_overlapped(kern, grid, dim3(128), (size_t)smem, st, overlap, p) != cudaSuccess) return B2Q_ERR_CUDA;
   note_launch("smallm");
   return launch_status();
