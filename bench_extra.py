@@ -154,6 +154,26 @@ def case_c4(e, dev, g, pk):
             "bf16_peak_frac": round(fl / us / 1e6 / pk["bf16_tflops"], 3)}
 
 
+def case_c4_decode(e, dev, g, pk):
+    """The decode form of C4's pipeline: moe_forward_full_int4 on 16 tokens (128 experts, top-8, H=2048, I=768) with an
+    INT4 shared expert of the same width; N-major experts.  Weight bytes touched: up to 128 of the 128 experts."""
+    T, E, H, I, k = 16, 128, 2048, 768, 8
+    (w13,), s13 = _int4(2 * I, H, dev, g, lead=(E,))
+    (w2,), s2 = _int4(H, I, dev, g, lead=(E,))
+    (sgu,), sgu_s = _int4(2 * I, H, dev, g)
+    (sdn,), sdn_s = _int4(H, I, dev, g)
+    sgu_s, sdn_s = sgu_s.t().contiguous(), sdn_s.t().contiguous()          # [K/128, N], as the reference receives them
+    gate_w = (torch.randn(1, H, generator=g, device=dev) * 0.02).to(torch.bfloat16)
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=dev).to(torch.bfloat16)
+    fn = lambda i: e.moe_forward_full_int4(x, logits, w13, s13, sgu, sgu_s, w2, s2, sdn, sdn_s, gate_w, k, 1, E, True)
+    us = _time_graph(fn, 10)
+    us_eager = _time(fn, 10)
+    touched = min(E, T * k) * (3 * I * H // 2) + 3 * I * H // 2
+    return {"us": round(us, 1), "us_eager_python": round(us_eager, 1), "tokens_per_s": round(T / us * 1e6, 0),
+            "expert_weight_GBps": round(touched / us / 1e3, 1)}
+
+
 CASES = {
     "c1_int4_m16_4096": case_c1,
     "c3_fp8_block_w8a16_m4096": case_c3_w8a16,
@@ -163,6 +183,7 @@ CASES = {
     "c5_m64": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 64),
     "c5_m2048": lambda e, dev, g, pk: _case_c5(e, dev, g, pk, 2048),
     "c4_moe_int4_t4096": case_c4,
+    "c4_moe_decode_t16_shared": case_c4_decode,
 }
 
 
