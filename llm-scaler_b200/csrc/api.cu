@@ -482,7 +482,10 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
   ua.out = gemm_out; ua.ldo = gemm_ldo; ua.M = (int)rows; ua.N = (int)N; ua.K = (int)K;
   ua.expert_offsets = expert_offsets; ua.E = E; ua.out_map = gemm_out_map; ua.tiles = tiles;
   const int64_t avg = (rows + E - 1) / E;
-  const bool want_umma = force == 2 || (force == 0 && (kmajor || avg > 16));
+  // measured on 128 experts of [1536 x 2048] / [2048 x 768] at 1 to 256 tokens (top-8): the tcgen05 kernel behind its
+  // pre-pass beats the streaming kernel at every batch (49 / 76 / 139 / 205 / 284 us per pipeline pass against
+  // 60 / 94 / 177 / 286 / 467), so only experts too small to matter stay on the streaming kernel
+  const bool want_umma = force == 2 || (force == 0 && (kmajor || avg > 16 || N * K >= ((int64_t)1 << 20)));
   ua.out_bf16 = bf;
   if (umma_w4_supported(ua) && want_umma) {
     // gather (if any), fp16 re-scaling and pair permutation in one pre-pass over the rows
