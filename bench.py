@@ -1,6 +1,6 @@
 """Benchmark of the quantized-linear hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--extra] [--case NAME]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--no-configs] [--case NAME]
 
 Headline workload (config.workload = "c2_fp8_channel_gemv_sweep"): the FP8 e4m3 per-output-channel
 decode GEMV sweep, weights [27648, 5120], bf16 activations with M in {1, 8, 32}.  One step = one GEMV
@@ -9,10 +9,20 @@ L2 (3 copies x 141.6 MB > 126 MB L2).  metric = weight-streaming GB/s = algorith
 (N*K + 4*N + 2*M*K + 2*M*N per launch) / time.  With N > 1 GPUs every rank owns its own
 [27648, 5120] column-parallel shard (no collective on this path): weak scaling, value = sum over ranks.
 
+The same JSON line carries, beside the headline:
+  "configs"  (one GPU) the other benchmark configurations, each timed on the device and checked against the CPU oracle
+             on a seeded slice of its output first (bench_extra.py): INT4 linear M=16 (C1), FP8 block GEMM as W8A8 and
+             w8a16 (C3), the INT4 MoE pipeline (C4), the Llama-70B-shape INT4 decoder layer at M=64 and M=2048 (C5);
+             value, unit, roofline_frac, max_rel_err, median and p10/p90.  `--no-configs` leaves the block out.
+  "sharded"  (N > 1 GPUs) the forms of the path that need an exchange step (bench_parallel.py): the tensor-parallel
+             decoder layer at M=64 and M=2048 (all-reduce after o_proj and down) and the expert-parallel MoE pipeline
+             (all-to-all dispatch and combine), with the time spent in the exchange broken out and the one-GPU figure
+             of the same case measured in the same run.
+  "cpu_baselines"  the reference's CPU torch path (the oracle port) timed per configuration on a bounded sample.
+
 `--impl reference` times the reference's CPU path (torch dequantise-then-matmul, the oracle port) on
 the host cores for the same metric on a bounded sample of the same workload.
-`--extra` adds device-timed figures for the other benchmark configurations under "extra";
-`--case NAME` runs one of those configurations alone and prints its figures (the command the kernel
+`--case NAME` runs one of bench_extra's configurations alone and prints its figures (the command the kernel
 profiles of that configuration are captured with).
 Synthetic seeded data throughout; nothing here reads a dataset or a checkpoint.
 """
@@ -124,6 +134,10 @@ def run_b200(args):
     rank, world = dist_setup(args.gpus)
     dev = torch.device("cuda", torch.cuda.current_device())
     assert e._lib.lib.b2q_device_ok() == 0, "this build targets sm_100a (B200) only"
+    fp8_peak = None
+    if world == 1 and not args.no_configs:
+        import bench_extra
+        fp8_peak = bench_extra.measure_fp8_peak(dev)     # before anything else heats the package up
     copies, xs, outs = make_workload(dev, 1234 + rank)
     torch.cuda.synchronize()
     # decode serving: the weights are written once (above) and never again, which is what overlap mode 2 asks the
@@ -158,6 +172,19 @@ def run_b200(args):
     for i in range(3):
         step(i)                                    # eager first: one-time kernel attribute set-up cannot be captured
     torch.cuda.synchronize()
+    # the launches that are about to be timed, checked against the CPU oracle on a seeded slice of their output
+    # (one column out of every 96-row strip a CTA owns, all tokens); the oracle is the checker, nothing of it is timed
+    check = None
+    if rank == 0:
+        from oracle import slices
+        cols = slices.pick(N_W, 64, 11, every=96)
+        worst = 0.0
+        for j, M in enumerate(M_SWEEP):
+            wq, s = copies[j % N_COPIES]
+            op(xs[M], wq, s, outs[M], N_W, K_W)
+            worst = max(worst, slices.fp8_channel_linear(xs[M], wq, s, outs[M], cols)["max_rel_err"])
+        check = {"max_rel_err": worst, "how": "%d seeded output columns (one per 96-row strip) x all tokens at each M against "
+                                              "oracle.fp8.linear_channel" % cols.numel()}
     launches0 = e.launch_count()
     graph = capture(args.steps, warm)
     launches = e.launch_count() - launches0        # kernels recorded in the graph = kernels per replay
@@ -172,6 +199,16 @@ def run_b200(args):
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
+    # further replays of the same K-step graph, each one sample: the spread of the timed figure
+    reps_ms = []
+    for _ in range(30):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        reps_ms.append(a.elapsed_time(b))
+    reps_ms.sort()
     t = torch.tensor([ms], device=dev, dtype=torch.float64)
     if world > 1:
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -290,12 +327,24 @@ def run_b200(args):
                 "h2d_bytes_per_step": sum(2 * M * K_W for M in M_SWEEP),
                 "d2h_bytes_per_step": sum(2 * M * N_W for M in M_SWEEP)},
         "gpu_launches": int(launches), "clocks": cs.summary(),
+        "max_rel_err": check["max_rel_err"] if check else None, "check": check,
+        "replays": {"ms_per_step_median": round(reps_ms[len(reps_ms) // 2] / args.steps, 4),
+                    "ms_per_step_p10": round(reps_ms[len(reps_ms) // 10] / args.steps, 4),
+                    "ms_per_step_p90": round(reps_ms[(len(reps_ms) * 9) // 10] / args.steps, 4), "samples": len(reps_ms),
+                    "how": "30 further replays of the timed K-step graph, this rank"},
     }
-    if rank == 0 and world == 1:
-        line["cpu_baseline"] = cpu_baseline(budget_s=12.0)
-    if args.extra and world == 1:
+    if world == 1 and not args.no_configs:
         import bench_extra
-        line["extra"] = bench_extra.run(e, dev)
+        pk = dict(bench_extra.peaks(), **fp8_peak)
+        line["measured_fp8_peak"] = fp8_peak
+        line["configs"] = bench_extra.run(e, dev, names=bench_extra.DEFAULT, pk=pk)
+    if world > 1:
+        import bench_parallel
+        line["sharded"] = bench_parallel.run_cases(rank, world, dev)
+    if rank == 0 and world == 1:
+        line["cpu_baseline"] = cpu_baseline(budget_s=10.0)
+        if not args.no_configs:
+            line["cpu_baselines"] = cpu_baselines_per_config()
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
@@ -338,6 +387,62 @@ def cpu_baseline(budget_s=12.0, threads=None):
             "sample": "%d passes of dequant+matmul over a %d-row slice of the [27648,5120] weight at M=8" % (n, rows)}
 
 
+def _timed_cpu(fn, budget_s, max_iters=3):
+    fn()                                   # warm-up (allocations, thread pool)
+    ts = []
+    t_all = time.perf_counter()
+    while len(ts) < max_iters and (not ts or time.perf_counter() - t_all < budget_s):
+        t0 = time.perf_counter()
+        fn()
+        ts.append(time.perf_counter() - t0)
+    return statistics.median(ts), len(ts)
+
+
+def cpu_baselines_per_config(budget_s=6.0):
+    """The reference's CPU torch path (dequantise, then fp32 matmul: the oracle port) for the other configurations, in
+    each configuration's own unit, on all host threads.  Every sample is bounded: full width in N and K, a slice of the
+    rows (tokens / output rows / experts) sized to a few seconds, stated in `sample`; the figure is throughput, so it
+    does not depend on the slice length beyond cache effects."""
+    from oracle import configs, fp8, int4, moe
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    out = {"cores": threads, "kind": "port", "what": "dequantise + fp32 matmul per call (the reference's torch path), median of up to 3 calls"}
+    c = configs.c1(seed=0)
+    t, n = _timed_cpu(lambda: int4.linear(c["x"], c["q"], c["scale"]), budget_s)
+    byts = 4096 * 4096 // 2 + 4096 * 32 * 2 + 2 * 16 * 4096 * 2
+    out["c1_int4_m16_4096"] = {"value": round(byts / t / 1e9, 3), "unit": "GB/s", "sample": "full size, %d calls" % n}
+    c = configs.c3(seed=0, M=512, N=2048)
+    xq, xs = fp8.quantize_act_1x128(c["x"])
+    t, n = _timed_cpu(lambda: fp8.linear_block_w8a8(xq, xs, c["wq"], c["ws"]), budget_s)
+    out["c3_fp8_block_w8a8_m4096"] = {"value": round(2.0 * 512 * 2048 * 5120 / t / 1e12, 4), "unit": "TFLOP/s",
+                                      "sample": "512 tokens x 2048 output rows x K=5120 of the [4096 x 17408 x 5120] problem, %d calls" % n}
+    t, n = _timed_cpu(lambda: fp8.linear_block_w8a16(c["x"], c["wq"], c["ws"]), budget_s)
+    out["c3_fp8_block_w8a16_m4096"] = {"value": round(2.0 * 512 * 2048 * 5120 / t / 1e12, 4), "unit": "TFLOP/s",
+                                       "sample": "same slice, activation kept in 16 bit, %d calls" % n}
+    c = configs.c4(seed=0, T=512, E=16)
+    def moe_call():
+        return moe.forward(c["x"], c["logits"], int4.dequant(c["q13"], c["s13"], torch.bfloat16),
+                           int4.dequant(c["q2"], c["s2"], torch.bfloat16), 8)
+    t, n = _timed_cpu(moe_call, budget_s)
+    fl = 512 * 8 * (2.0 * 2048 * 1536 + 2.0 * 768 * 2048)
+    out["c4_moe_int4_t4096"] = {"value": round(fl / t / 1e12, 4), "unit": "TFLOP/s", "tokens_per_s": round(512 / t, 1),
+                                "sample": "512 tokens over 16 of the 128 experts (top-8, H=2048, I=768), dequantisation included, %d calls" % n}
+    for M in (64, 2048):
+        g = torch.Generator().manual_seed(M)
+        q, s = configs.int4_weight(2048, 8192, g)
+        x = torch.randn(min(M, 256), 8192, generator=g).to(torch.bfloat16)
+        t, n = _timed_cpu(lambda: int4.linear(x, q, s), budget_s)
+        rows = x.shape[0]
+        if M == 64:
+            byts = 2048 * 8192 // 2 + 2048 * 64 * 2
+            out["c5_m64"] = {"value": round(byts / t / 1e9, 3), "unit": "GB/s",
+                             "sample": "one [2048 x 8192] row block of the layer's weights at M=64 (the layer is 52 such blocks), %d calls" % n}
+        else:
+            out["c5_m2048"] = {"value": round(2.0 * rows * 2048 * 8192 / t / 1e12, 4), "unit": "TFLOP/s",
+                               "sample": "%d tokens x one [2048 x 8192] row block, %d calls" % (rows, n)}
+    return out
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -366,7 +471,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--extra", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="headline workload only")
+    ap.add_argument("--extra", action="store_true", help="accepted for compatibility; the configs block is on by default")
     ap.add_argument("--case", default=None, help="run one configuration of bench_extra.CASES alone")
     args = ap.parse_args()
     if args.case:

@@ -5,17 +5,22 @@ M = 64 and M = 2048) and the expert-parallel INT4 MoE pipeline (128 experts, top
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
         bench_parallel.py [--cases tp_m64,tp_m2048,ep]                  N ranks, one per GPU, NCCL
 
+`bench.py --gpus N` (N > 1) runs the same cases through run_cases() and puts them in its JSON line under "sharded".
+
 One process per GPU.  Tensor parallel: QKV and gate_up are split by output rows (no communication), o_proj and down by
-K in multiples of the 128-group, each followed by an all-reduce (sum) of the [M, 8192] partial results.  Expert
+K in multiples of the 128-group, each followed by a sum of the [M, 8192] partial results over the ranks.  Expert
 parallel: experts [r * E / G, (r + 1) * E / G) live on rank r, every rank starts with T / G tokens, rows travel by
 all-to-all to their experts' rank and back.  Timing: CUDA events on every rank around the same iterations between
-barriers, the maximum over ranks is reported.  Synthetic seeded weights (uniform nibbles, scales 0.002 + |N(0, 0.01)|);
-attention is replaced by the rank's q slice of the QKV output, as in the single-GPU layer case.  Rank 0 prints one
-JSON line per case.
+barriers, the maximum over ranks is reported.  Beside every sharded figure stand the figure of the same case on ONE GPU
+(unsharded weights, measured by rank 0 in the same run) and the time of the exchange step: for tensor parallel the
+difference to a run of the same sharded kernels with the sum skipped, for expert parallel CUDA events around the
+all-to-alls.  Synthetic seeded weights (uniform nibbles, scales 0.002 + |N(0, 0.01)|); attention is replaced by the
+rank's q slice of the QKV output, as in the single-GPU layer case.
 """
 import argparse
 import json
 import os
+import statistics
 import sys
 
 import torch
@@ -33,27 +38,33 @@ def _int4(N, K, dev, g, lead=()):
     return w, s
 
 
-def _timed(fn, reps, warm, world):
+def _max_over_ranks(v, world):
+    t = torch.tensor([v], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _timed(fn, iters, warm, world):
+    """Eager calls, one sample per iteration; median over iterations of the slowest rank's time."""
     for i in range(warm):
         fn(i)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    for i in range(reps):
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for i, (a, b) in enumerate(ev):
+        a.record()
         fn(i)
-    b.record()
+        b.record()
     torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(b) * 1e3 / reps], device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())          # microseconds per iteration, slowest rank
+    us = statistics.median(a.elapsed_time(b) * 1e3 for a, b in ev)
+    return _max_over_ranks(us, world)          # microseconds per iteration, slowest rank
 
 
-def _timed_graph(fn, reps, world):
-    """Decode shapes: reps iterations (their all-reduces included) captured into one CUDA graph, one replay timed,
-    as a serving engine's decode loop runs them; no Python dispatch between the launches."""
+def _timed_graph(fn, reps, iters, world):
+    """Decode shapes: reps iterations (their exchange steps included) captured into one CUDA graph, every replay one
+    sample, as a serving engine's decode loop runs them; no Python dispatch between the launches."""
     for i in range(3):
         fn(i)
     torch.cuda.synchronize()
@@ -63,46 +74,66 @@ def _timed_graph(fn, reps, world):
     with torch.cuda.graph(g):
         for i in range(reps):
             fn(i)
-    g.replay()
+    for _ in range(2):
+        g.replay()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
-    g.replay()
-    b.record()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+    for a, b in ev:
+        a.record()
+        g.replay()
+        b.record()
     torch.cuda.synchronize()
-    t = torch.tensor([a.elapsed_time(b) * 1e3 / reps], device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
+    us = statistics.median(a.elapsed_time(b) * 1e3 / reps for a, b in ev)
+    return _max_over_ranks(us, world)
+
+
+def _tp_stack(world, layers, dev, g, P):
+    return [P.TPLayer(qkv=_int4(QKV_N // world, HID, dev, g), o=_int4(HID, HID // world, dev, g),
+                      gate_up=_int4(2 * FFN // world, HID, dev, g), down=_int4(HID, FFN // world, dev, g))
+            for _ in range(layers)]
 
 
 def tp_case(M, rank, world, dev, P, be):
-    g = torch.Generator(device=dev).manual_seed(100 + rank)
     layers = 2 if M > 64 else 3          # distinct weights per layer: 428 MB / world each, nothing stays in L2
-    stack = [P.TPLayer(qkv=_int4(QKV_N // world, HID, dev, g), o=_int4(HID, HID // world, dev, g),
-                       gate_up=_int4(2 * FFN // world, HID, dev, g), down=_int4(HID, FFN // world, dev, g))
-             for _ in range(layers)]
     x = torch.randn(M, HID, generator=torch.Generator(device=dev).manual_seed(7), device=dev).to(torch.bfloat16)
+    reducer = P.make_reducer(M, HID, torch.bfloat16, dev) if world > 1 else None
 
-    def step(i):
-        h = x
-        for layer in stack:
-            h = P.tp_layer_forward(h, layer, be)
-        return h
+    def measure(stack, reduce_fn, w):
+        def step(i):
+            h = x
+            for layer in stack:
+                h = P.tp_layer_forward(h, layer, be, reduce=reduce_fn)
+            return h
+        if M <= 64:
+            return _timed_graph(step, 4, 10, w) / layers
+        return _timed(step, 6, 3, w) / layers
 
-    how = "eager calls through the public ops (an all-reduce follows o_proj and down)"
-    if M <= 64:
-        us = _timed_graph(step, 6, world) / layers
-        how = "six passes over the layers captured in one CUDA graph, all-reduces included; one replay timed"
-    else:
-        us = _timed(step, 4, 3, world) / layers
     params = QKV_N * HID + HID * HID + 2 * FFN * HID + HID * FFN
-    rec = {"case": f"tp_c5_m{M}", "n_gpus": world, "parallelism": f"tp{world}", "us_per_layer": round(us, 1),
-           "tokens_per_s_80_layers": round(M / (us * 80) * 1e6, 1),
-           "all_reduce_bytes_per_layer": 2 * M * HID * 2 if world > 1 else 0,
-           "launch": how}
+    rec = {"case": f"tp_c5_m{M}", "n_gpus": world, "parallelism": f"tp{world}",
+           "launch": "passes over the layers captured in one CUDA graph, exchange steps included; every replay one sample"
+                     if M <= 64 else "eager calls through the public ops"}
+    # the same case on one GPU: unsharded weights, no exchange (every rank runs it; ranks do not wait for each other here)
+    g1 = torch.Generator(device=dev).manual_seed(100)
+    one = _tp_stack(1, layers, dev, g1, P)
+    us1 = measure(one, lambda t, group=None: t, 1)
+    del one
+    torch.cuda.empty_cache()
+    rec["one_gpu_us_per_layer"] = round(us1, 1)
+    if world > 1:
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        stack = _tp_stack(world, layers, dev, g, P)
+        us = measure(stack, reducer.reduce, world)
+        us_nosum = measure(stack, lambda t, group=None: t, world)
+        rec.update(us_per_layer=round(us, 1), exchange_us_per_layer=round(max(0.0, us - us_nosum), 1),
+                   exchange="sum of the [M, 8192] partial results after o_proj and down: " + reducer.describe(),
+                   all_reduce_bytes_per_layer=2 * M * HID * 2, speedup_vs_one_gpu=round(us1 / us, 2),
+                   efficiency=round(us1 / us / world, 3))
+    else:
+        us = us1
+        rec["us_per_layer"] = round(us, 1)
+    rec["tokens_per_s_80_layers"] = round(M / (us * 80) * 1e6, 1)
     if M <= 64:
         rec["weight_GBps_all_gpus"] = round((params // 2 + params // 128 * 2) / us / 1e3, 1)
     else:
@@ -112,17 +143,68 @@ def tp_case(M, rank, world, dev, P, be):
 
 def ep_case(rank, world, dev, P, be):
     T, E, H, I, k = 4096, 128, 2048, 768, 8
-    g = torch.Generator(device=dev).manual_seed(200 + rank)
-    w13, s13 = _int4(2 * I, H, dev, g, lead=(E // world,))
-    w2, s2 = _int4(H, I, dev, g, lead=(E // world,))
-    x = torch.randn(T // world, H, generator=g, device=dev).to(torch.bfloat16)
-    logits = torch.randn(T // world, E, generator=g, device=dev).to(torch.bfloat16)
-    us = _timed(lambda i: P.ep_moe_forward(x, logits, w13, s13, w2, s2, k, E, be), 5, 2, world)
     fl = T * k * (2.0 * H * 2 * I + 2.0 * I * H)
-    return {"case": "ep_c4_moe_int4_t4096", "n_gpus": world, "parallelism": f"ep{world}", "us": round(us, 1),
-            "tokens_per_s": round(T / us * 1e6, 0), "TFLOPs_all_gpus": round(fl / us / 1e6, 1),
-            "all_to_all_bytes_per_pass": int(2 * T * k * H * 2 * (world - 1) / world),
-            "launch": "eager calls; the row counts of the all-to-all are read on the host (two syncs per pass)"}
+
+    def build(w, r):
+        g = torch.Generator(device=dev).manual_seed(200 + r)
+        w13, s13 = _int4(2 * I, H, dev, g, lead=(E // w,))
+        w2, s2 = _int4(H, I, dev, g, lead=(E // w,))
+        x = torch.randn(T // w, H, generator=g, device=dev).to(torch.bfloat16)
+        logits = torch.randn(T // w, E, generator=g, device=dev).to(torch.bfloat16)
+        return x, logits, w13, s13, w2, s2
+
+    a1 = build(1, 0)
+    us1 = _timed(lambda i: P.ep_moe_forward(*a1, k, E, be, world=1), 8, 3, 1)
+    del a1
+    torch.cuda.empty_cache()
+    rec = {"case": "ep_c4_moe_int4_t4096", "n_gpus": world, "parallelism": f"ep{world}", "one_gpu_us": round(us1, 1)}
+    if world > 1:
+        a = build(world, rank)
+        us = _timed(lambda i: P.ep_moe_forward(*a, k, E, be), 8, 3, world)
+        # time inside the exchange steps: events at the phase boundaries of a few further passes
+        spans = {"dispatch": [], "combine": []}
+        for _ in range(4):
+            evs = {}
+
+            def mark(label):
+                evs[label] = torch.cuda.Event(enable_timing=True)
+                evs[label].record()
+            P.ep_moe_forward(*a, k, E, be, marks=mark)
+            torch.cuda.synchronize()
+            spans["dispatch"].append(evs["dispatch_begin"].elapsed_time(evs["dispatch_end"]) * 1e3)
+            spans["combine"].append(evs["combine_begin"].elapsed_time(evs["combine_end"]) * 1e3)
+        ex = _max_over_ranks(statistics.median(spans["dispatch"]) + statistics.median(spans["combine"]), world)
+        rec.update(us=round(us, 1), exchange_us=round(ex, 1),
+                   exchange="counts exchange + all-to-all of rows and expert ids (dispatch), all-to-all of results (combine): " + P.EP_EXCHANGE,
+                   all_to_all_bytes_per_pass=int(2 * T * k * H * 2 * (world - 1) / world),
+                   speedup_vs_one_gpu=round(us1 / us, 2), efficiency=round(us1 / us / world, 3))
+    else:
+        us = us1
+        rec["us"] = round(us, 1)
+    rec.update(tokens_per_s=round(T / us * 1e6, 0), TFLOPs_all_gpus=round(fl / us / 1e6, 1))
+    return rec
+
+
+def run_cases(rank, world, dev, cases=("tp_m64", "tp_m2048", "ep")):
+    """Runs the sharded cases on an initialised process group (or on one GPU) and returns {case name: figures}."""
+    import custom_esimd_kernels_vllm as pkg                      # loads the library or fails loudly
+    from custom_esimd_kernels_vllm import parallel as P
+    be = P.CudaBackend()
+    # the weights never change during the run: launches may overlap their predecessors' tails (see b2q_set_overlap_mode)
+    pkg.set_overlap_mode(int(os.environ.get("B2Q_OVERLAP_MODE", "2")))
+    out = {}
+    for c in cases:
+        if c == "tp_m64":
+            rec = tp_case(64, rank, world, dev, P, be)
+        elif c == "tp_m2048":
+            rec = tp_case(2048, rank, world, dev, P, be)
+        elif c == "ep":
+            rec = ep_case(rank, world, dev, P, be)
+        else:
+            raise SystemExit(f"unknown case {c}")
+        out[rec["case"]] = rec
+        torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -136,23 +218,10 @@ def main():
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    import custom_esimd_kernels_vllm as pkg                      # noqa: F401  (loads the library or fails loudly)
-    from custom_esimd_kernels_vllm import parallel as P
-    be = P.CudaBackend()
-    # the weights never change during the run: launches may overlap their predecessors' tails (see b2q_set_overlap_mode)
-    pkg.set_overlap_mode(int(os.environ.get("B2Q_OVERLAP_MODE", "2")))
-    for c in args.cases.split(","):
-        if c == "tp_m64":
-            rec = tp_case(64, rank, world, dev, P, be)
-        elif c == "tp_m2048":
-            rec = tp_case(2048, rank, world, dev, P, be)
-        elif c == "ep":
-            rec = ep_case(rank, world, dev, P, be)
-        else:
-            raise SystemExit(f"unknown case {c}")
-        if rank == 0:
+    res = run_cases(rank, world, dev, tuple(args.cases.split(",")))
+    if rank == 0:
+        for rec in res.values():
             print(json.dumps(rec), flush=True)
-        torch.cuda.empty_cache()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -72,6 +72,7 @@ extern "C" {
 /* ---- activation functions fused into grouped GEMM epilogues ------------- */
 #define B2Q_ACT_NONE      0
 #define B2Q_ACT_SILU_MUL  1    /* out[:, j] = silu(g[:, j]) * g[:, I + j]    */
+#define B2Q_ACT_GELU_TANH_MUL 3 /* FP8 grouped GEMM only: out[:, j] = gelu_tanh(g[:, j]) * g[:, I + j]          */
 #define B2Q_ACT_SILU_MUL_IN 2  /* INT4 grouped GEMM only: x has 2K columns (gate, then up; ldx >= 2K) and the
                                   GEMM's input row is silu(x[:, :K]) * x[:, K:], rounded to the activation type as
                                   B2Q_ACT_SILU_MUL would have stored it.  No output activation, no row_map.     */
@@ -153,6 +154,9 @@ B2Q_API int b2q_quantize_fp8(const void* w, int w_dtype, int64_t ldw, void* wq, 
  * scratch the tensor-core kernel first rewrites the activations as fp16 times a per-token power
  * of two in the element order its nibble decode produces; the dequantised weight is then
  * (q - 8) * scale rounded once to fp16 (11 significant bits) instead of to the activation type.
+ * Scales of any magnitude are safe on that route: bf16 / fp32 scales are brought into fp16's normal
+ * range by a power of two per output row (chosen from the row's largest scale) that is taken out
+ * of the fp32 accumulator again; a group more than 2^22 below its row's largest scale loses bits.
  * Without scratch the weight is rounded exactly as the torch reference rounds it.  For M <= 64
  * the scratch also holds partial sums: layers with few output rows are cut along K over several CTAs
  * per strip of rows so that they still occupy every SM; the partial sums are added in a fixed order,
@@ -246,7 +250,15 @@ B2Q_API int b2q_gather_rows(const void* src, const int32_t* idx, int div, void* 
  * Replaces esimd_moe_silu_mul (moe_ops.h:576-621).                            */
 B2Q_API int b2q_silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, void* stream);
 
+/* out[r, j] = gelu_tanh(in[r, j]) * in[r, I + j] with gelu_tanh(g) = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))),
+ * fp32 math, one rounding.  Replaces esimd_moe_gelu_tanh_mul (csrc/xpu/torch_extension_moe.cc:30-34,
+ * csrc/xpu/esimd_kernels/moe_ops.h:678-740).                                  */
+B2Q_API int b2q_gelu_tanh_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, void* stream);
+
 /* out[t, :] = sum_s w[t, s] * y[perm ? perm[t*k+s] : t*k+s, :], fp32 sum.
+ * w == NULL adds the rows unweighted (moe_ops.moe_accumulate, csrc/moe_batch/moe.sycl:1177-1230);
+ * with top_k == 1, perm == NULL and out == y it scales row t by w[t] in place (the routing-weight
+ * multiply of moe_down_fp8_grouped, csrc/moe_batch/moe_fp8_grouped.h:293-335).
  * w_by_row != 0 reads the weight at the row position instead of at (t, s).
  * Replaces moe_prefill_accumulate{,_permuted}_forward_v2 (:398-454) and
  * esimd_moe_gather (moe_ops.h:627-676).                                       */
@@ -292,7 +304,10 @@ B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
 /* Code of the first bounded device-side wait that expired since the library was loaded
  * (0 = none).  Synchronises the device; meant for tests and post-mortems.       */
 B2Q_API int b2q_device_status(int* out);
-/* Clears that code (after a post-mortem, or after the self-test below).                        */
+/* Clears that code on the current device: the status words of every kernel family, and the arrival
+ * counters of strips cut between CTAs (a CTA that gave up never delivered its arrival, so a stale
+ * counter would make a later launch finish that strip early).  Synchronises the device first; call
+ * it with no launch of this library in flight, once per device that reported a code.           */
 B2Q_API int b2q_device_status_reset(void);
 /* Self-test of the bounded waits: launches one CTA that waits, with a limit of about a millisecond,
  * on a barrier nobody arrives on.  The wait gives up, records `code` (> 0) as the device status and

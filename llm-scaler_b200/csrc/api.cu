@@ -19,7 +19,7 @@ size_t moe_route_workspace_bytes(int64_t, int);
 int moe_route(const int32_t*, int64_t, int, int32_t*, int32_t*, int32_t*, int32_t*, void*, cudaStream_t);
 int moe_build_tiles(const int32_t*, int, int, int32_t*, cudaStream_t);
 int gather_rows(const void*, const int32_t*, int, void*, int64_t, int64_t, int, cudaStream_t);
-int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t, int64_t ld_in = 0);
+int silu_mul(const void*, void*, int, int64_t, int64_t, const int32_t*, cudaStream_t, int64_t ld_in = 0, bool gelu = false);
 int quantize_fp8(const void*, int, int64_t, void*, float*, int, int64_t, int64_t, cudaStream_t);
 int shared_gate_add(const void*, const void*, const void*, const void*, void*, int, int64_t, int64_t, cudaStream_t);
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
@@ -389,9 +389,17 @@ int b2q_silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, 
   return silu_mul(in, out, dtype, rows, I, nullptr, (cudaStream_t)stream);
 }
 
+int b2q_gelu_tanh_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, void* stream) {
+  if (!in || !out) return B2Q_ERR_NULL;
+  if (!is16(dtype)) return B2Q_ERR_DTYPE;
+  if (rows < 0 || I < 0 || (I % 8) != 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(in) || !aligned16(out)) return B2Q_ERR_ALIGN;
+  return silu_mul(in, out, dtype, rows, I, nullptr, (cudaStream_t)stream, 0, true);
+}
+
 int b2q_moe_combine(const void* y, const void* w, int w_dtype, const int32_t* perm, void* out, int dtype, int64_t T,
                     int top_k, int64_t H, int w_by_row, void* stream) {
-  if (!y || !w || !out) return B2Q_ERR_NULL;
+  if (!y || !out) return B2Q_ERR_NULL;
   if (!is16(dtype) || w_dtype < 0 || w_dtype > 2) return B2Q_ERR_DTYPE;
   if (T < 0 || top_k <= 0 || H < 0 || (H % 8) != 0) return B2Q_ERR_SHAPE;
   if (!aligned16(y) || !aligned16(out)) return B2Q_ERR_ALIGN;
@@ -413,7 +421,7 @@ size_t b2q_moe_gemm_workspace_bytes(int64_t rows, int E, int64_t N, int64_t K, i
   (void)gather;
   size_t b = tile_list_bytes(rows, E, 8);
   b += align_up((size_t)rows * (size_t)K * 2, 256) + align_up((size_t)rows * 4, 256);
-  if (act == B2Q_ACT_SILU_MUL) b += align_up((size_t)rows * (size_t)N * 2, 256);
+  if (act == B2Q_ACT_SILU_MUL || act == B2Q_ACT_GELU_TANH_MUL) b += align_up((size_t)rows * (size_t)N * 2, 256);
   return b;
 }
 
@@ -537,8 +545,8 @@ int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx, const int32_t* r
   if (scale_mode == B2Q_SCALE_BLOCK128 && fp8_format != B2Q_E4M3) return B2Q_ERR_DTYPE;
   if (rows < 0 || N <= 0 || K <= 0 || (K % 16) != 0 || E <= 0 || ldx < K) return B2Q_ERR_SHAPE;
   if (scale_mode == B2Q_SCALE_BLOCK128 && ((K % 128) != 0 || (N % 128) != 0)) return B2Q_ERR_SHAPE;
-  if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL) return B2Q_ERR_UNSUPPORTED;
-  if (act == B2Q_ACT_SILU_MUL && ((N % 16) != 0 || ldo != N / 2)) return B2Q_ERR_SHAPE;
+  if (act != B2Q_ACT_NONE && act != B2Q_ACT_SILU_MUL && act != B2Q_ACT_GELU_TANH_MUL) return B2Q_ERR_UNSUPPORTED;
+  if (act != B2Q_ACT_NONE && ((N % 16) != 0 || ldo != N / 2)) return B2Q_ERR_SHAPE;
   if (act == B2Q_ACT_NONE && ldo < N) return B2Q_ERR_SHAPE;
   if (E > 1024 || rows > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return B2Q_ERR_LIMIT;
   if (row_map && row_div <= 0) return B2Q_ERR_SHAPE;
@@ -592,7 +600,7 @@ int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx, const int32_t* r
     rc = bf ? smallm_fp8_bf16(p, fp8_format, smode, tile, cap, st) : smallm_fp8_f16(p, fp8_format, smode, tile, cap, st);
   }
   if (rc || act == B2Q_ACT_NONE) return rc;
-  return silu_mul(pl.g, out, act_dtype, rows, N / 2, out_map, st);
+  return silu_mul(pl.g, out, act_dtype, rows, N / 2, out_map, st, 0, act == B2Q_ACT_GELU_TANH_MUL);
 }
 
 }  // extern "C"

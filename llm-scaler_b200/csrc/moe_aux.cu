@@ -271,7 +271,9 @@ int gather_rows(const void* src, const int32_t* idx, int div, void* dst, int64_t
 }
 
 // ---------------------------------------------------------------------------
-template <bool BF16>
+// out[r, j] = act(in[r, j]) * in[r, I + j] in fp32, one rounding.  GELU: the tanh form
+// 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) of csrc/xpu/esimd_kernels/moe_ops.h:678-723.
+template <bool BF16, bool GELU>
 __global__ void silu_mul_kernel(const uint4* __restrict__ in, uint4* __restrict__ out, int64_t rows, int64_t I8,
                                 const int32_t* __restrict__ out_map, int64_t ld8) {
   using A = Act<BF16>;
@@ -289,7 +291,9 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ in, uint4* __restrict_
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float gv = A::to_f(gp[j]);
-      const float s = gv / (1.0f + expf(-gv));
+      float s;
+      if constexpr (GELU) s = 0.5f * gv * (1.0f + tanhf(0.7978845608f * (gv + 0.044715f * gv * gv * gv)));
+      else s = gv / (1.0f + expf(-gv));
       op[j] = A::from_f(s * A::to_f(up[j]));
     }
     out[(out_map ? (int64_t)out_map[r] : r) * I8 + c] = o;
@@ -297,17 +301,22 @@ __global__ void silu_mul_kernel(const uint4* __restrict__ in, uint4* __restrict_
 }
 
 int silu_mul(const void* in, void* out, int dtype, int64_t rows, int64_t I, const int32_t* out_map, cudaStream_t st,
-             int64_t ld_in) {
+             int64_t ld_in, bool gelu) {
   if (rows == 0) return B2Q_OK;
   const int64_t ld8 = (ld_in > 0 ? ld_in : 2 * I) / 8;       // source row pitch in 16-byte units
   const int64_t total = rows * (I / 8);
   int64_t g = (total + 255) / 256;
   if (g > 148 * 16) g = 148 * 16;
-  if (dtype == B2Q_BF16)
-    silu_mul_kernel<true><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map, ld8);
-  else
-    silu_mul_kernel<false><<<(int)g, 256, 0, st>>>(reinterpret_cast<const uint4*>(in), reinterpret_cast<uint4*>(out), rows, I / 8, out_map, ld8);
-  note_launch("silu_mul");
+  auto ci = reinterpret_cast<const uint4*>(in);
+  auto co = reinterpret_cast<uint4*>(out);
+  if (dtype == B2Q_BF16) {
+    if (gelu) silu_mul_kernel<true, true><<<(int)g, 256, 0, st>>>(ci, co, rows, I / 8, out_map, ld8);
+    else silu_mul_kernel<true, false><<<(int)g, 256, 0, st>>>(ci, co, rows, I / 8, out_map, ld8);
+  } else {
+    if (gelu) silu_mul_kernel<false, true><<<(int)g, 256, 0, st>>>(ci, co, rows, I / 8, out_map, ld8);
+    else silu_mul_kernel<false, false><<<(int)g, 256, 0, st>>>(ci, co, rows, I / 8, out_map, ld8);
+  }
+  note_launch(gelu ? "gelu_tanh_mul" : "silu_mul");
   return launch_status();
 }
 
@@ -382,7 +391,7 @@ __global__ void moe_combine_kernel(const uint4* __restrict__ y, const void* __re
       const int64_t pair = t * top_k + s;
       const int64_t row = perm ? (int64_t)perm[pair] : pair;
       if (row < 0) continue;
-      const float wt = load_scalar(w, w_by_row ? row : pair, wdt);
+      const float wt = w ? load_scalar(w, w_by_row ? row : pair, wdt) : 1.0f;
       const uint4 v = y[row * H8 + c];
       const Ty* vp = reinterpret_cast<const Ty*>(&v);
 #pragma unroll

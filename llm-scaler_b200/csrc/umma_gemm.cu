@@ -28,6 +28,8 @@ namespace b2q {
 using namespace sm100;
 
 __device__ int g_umma_status = 0;
+constexpr int SK_BANKS = 64, SK_MAX_STRIPS = 1024;
+__device__ int g_sk_counters[SK_BANKS * SK_MAX_STRIPS];     // arrival counters of cut strips (see "balanced mode" below)
 #ifdef B2Q_UMMA_PROF
 // Wait-time accounting for one CTA, accumulated in registers and flushed once per role so the
 // measurement does not sit on the critical path.
@@ -393,6 +395,26 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       else
         return blockscale ? reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * kblocks + ((c_begin + c) >> 1)] : 0.f;
     };
+    // fp16 magic route with bf16 / fp32 scales: the group scale is rounded to fp16, whose normal range starts at
+    // 6.1e-5.  Every row therefore carries its own power of two: the row's scales are multiplied by 2^row_e so that
+    // the largest lands in [2^8, 2^9) (a group 2^22 below it is still a normal fp16; (q - 8) * s needs 11 bits at
+    // most, so the operand stays exact), and the fp32 accumulator row is multiplied by 2^-row_e when it is read.
+    float row_mul = 1.f, row_post = 1.f;
+    if constexpr ((WK == WK_W4N || WK == WK_W4K) && !BF16 && FAST) {
+      if (p.magic && p.scale_dtype != B2Q_F16) {
+        float smax = 0.f;
+        const int G = p.K >> 7;
+        const int64_t rbase = sbase + (int64_t)nrow * p.s_stride_n;
+        for (int g = 0; g < G; ++g) smax = fmaxf(smax, fabsf(load_scalar(p.scale, rbase + (int64_t)g * p.s_stride_g, p.scale_dtype)));
+        const int ex = (int)((__float_as_uint(smax) >> 23) & 0xFFu);          // biased exponent; 0 = zero / subnormal, 255 = inf / nan
+        if (ex != 0 && ex != 255) {
+          int k = 8 - (ex - 127);
+          k = k > 120 ? 120 : (k < -120 ? -120 : k);
+          row_mul = __uint_as_float((uint32_t)(127 + k) << 23);
+          row_post = __uint_as_float((uint32_t)(127 - k) << 23);
+        }
+      }
+    }
     float sc_a = chunk_scale(grp), sc_b = chunk_scale(grp + NG);
 #pragma unroll 1
     for (int c = grp; c < nk; c += NG) {
@@ -434,7 +456,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           if constexpr (!BF16 && FAST) {
             if (p.magic) {
               // fp16 magic-number path: the activation pre-pass stored x in the pair order this produces
-              const __half hs = __float2half_rn(sc_cur);
+              const __half hs = __float2half_rn(sc_cur * row_mul);
               const uint32_t hv = __half_as_ushort(hs);
               const uint32_t m2 = hv | (hv << 16);
 #pragma unroll
@@ -553,6 +575,12 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
+      }
+      if constexpr ((WK == WK_W4N || WK == WK_W4K) && !BF16 && FAST) {
+        if (row_post != 1.f) {
+#pragma unroll
+          for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * row_post);
+        }
       }
       // balanced mode has one column block per thread at most: the accumulators are free for the next segment now
       if (BAL && balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); freed = true; }
@@ -686,10 +714,26 @@ int umma_selftest_bounded_wait(int code, int* gave_up_dev, cudaStream_t st) {
   return launch_status();
 }
 
+int w8a8_reset_state();
+int w8d_reset_state();
+int w4i_reset_state();
+
+// Clears, on the current device, the status word of every tcgen05 kernel family and the arrival counters of cut
+// strips.  A CTA that gave up on a wait never delivered its arrival, so its strip's counter is left non-zero and the
+// next launch that takes the same bank would finish that strip one arrival early: status and counters go together.
+// The device must be idle (the call synchronises it first).
 int umma_reset_status() {
   int* p = status_ptr();
   if (!p) return B2Q_ERR_CUDA;
-  return cuda_status(cudaMemset(p, 0, sizeof(int)));
+  if (cudaDeviceSynchronize() != cudaSuccess) return B2Q_ERR_CUDA;
+  if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return B2Q_ERR_CUDA;
+  void* c = nullptr;
+  if (cudaGetSymbolAddress(&c, g_sk_counters) != cudaSuccess) return B2Q_ERR_CUDA;
+  if (cudaMemset(c, 0, sizeof(int) * SK_BANKS * SK_MAX_STRIPS) != cudaSuccess) return B2Q_ERR_CUDA;
+  int rc = w8a8_reset_state();
+  if (!rc) rc = w8d_reset_state();
+  if (!rc) rc = w4i_reset_state();
+  return rc;
 }
 
 int umma_read_status(int* out) {
@@ -717,8 +761,6 @@ extern "C" __attribute__((visibility("default"))) int b2q_debug_prof(long long* 
 // Arrival counters of cut strips.  They are zero whenever no launch is in flight (the last arriver of a
 // strip resets its counter), so nothing has to be cleared per launch; launches take one of 64 banks in turn
 // so that launches overlapping in time (other streams, programmatic dependent launch) do not share counters.
-constexpr int SK_BANKS = 64, SK_MAX_STRIPS = 1024;
-__device__ int g_sk_counters[SK_BANKS * SK_MAX_STRIPS];
 
 static int* sk_counter_bank() {
   static thread_local int* basep[16] = {nullptr};

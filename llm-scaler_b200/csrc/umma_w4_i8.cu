@@ -498,6 +498,13 @@ extern "C" __attribute__((visibility("default"))) int b2q_debug_prof_w4i(long lo
 }
 #endif
 
+int w4i_reset_state() {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_w4i_status) != cudaSuccess) return B2Q_ERR_CUDA;
+  if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return B2Q_ERR_CUDA;
+  if (cudaGetSymbolAddress(&p, g_w4i_counters) != cudaSuccess) return B2Q_ERR_CUDA;
+  return cuda_status(cudaMemset(p, 0, sizeof(int) * W4I_BANKS * W4I_MAX_STRIPS));
+}
 int w4i_read_status(int* out) { return cuda_status(cudaMemcpyFromSymbol(out, g_w4i_status, sizeof(int))); }
 
 }  // namespace b2q

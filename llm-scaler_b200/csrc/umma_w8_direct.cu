@@ -386,6 +386,13 @@ int umma_w8_direct_linear(const UmmaW8DirectArgs& a, cudaStream_t st) {
   }
 }
 
+int w8d_reset_state() {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_w8d_status) != cudaSuccess) return B2Q_ERR_CUDA;
+  if (cudaMemset(p, 0, sizeof(int)) != cudaSuccess) return B2Q_ERR_CUDA;
+  if (cudaGetSymbolAddress(&p, g_w8d_counters) != cudaSuccess) return B2Q_ERR_CUDA;
+  return cuda_status(cudaMemset(p, 0, sizeof(int) * W8D_BANKS * W8D_MAX_STRIPS));
+}
 int w8d_read_status(int* out) { return cuda_status(cudaMemcpyFromSymbol(out, g_w8d_status, sizeof(int))); }
 
 }  // namespace b2q

@@ -401,6 +401,11 @@ int umma_w8a8_block(const UmmaW8A8Args& a, cudaStream_t st) {
   return launch_w8a8<128>(a, p, st);
 }
 
+int w8a8_reset_state() {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, g_w8a8_status) != cudaSuccess) return B2Q_ERR_CUDA;
+  return cuda_status(cudaMemset(p, 0, sizeof(int)));
+}
 int w8a8_read_status(int* out) {
   return cuda_status(cudaMemcpyFromSymbol(out, g_w8a8_status, sizeof(int)));
 }

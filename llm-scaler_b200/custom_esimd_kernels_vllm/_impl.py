@@ -330,15 +330,28 @@ def silu_mul(gate_up, out=None):
     return out
 
 
+def gelu_tanh_mul(gate_up, out=None):
+    L.require_cuda(gate_up)
+    _chk(gate_up.dim() == 2 and gate_up.is_contiguous(), "gate_up must be contiguous [rows, 2I]")
+    rows, two_i = gate_up.shape
+    if out is None:
+        out = torch.empty(rows, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+    with L.on_device(gate_up):
+        L.check(L.lib.b2q_gelu_tanh_mul(gate_up.data_ptr(), out.data_ptr(), L.dt(gate_up), rows, two_i // 2,
+                                         L.stream(gate_up)))
+    return out
+
+
 def moe_combine(y, weights, perm, T, top_k, out=None, w_by_row=False):
+    """out[t] = sum_s weights[t, s] * y[row(t, s)] in fp32; weights=None adds the rows unweighted."""
     L.require_cuda(y, weights)
-    _chk(y.dim() == 2 and y.is_contiguous() and weights.is_contiguous(), "combine operands must be contiguous")
+    _chk(y.dim() == 2 and y.is_contiguous() and (weights is None or weights.is_contiguous()), "combine operands must be contiguous")
     H = y.shape[1]
     if out is None:
         out = torch.empty(T, H, dtype=y.dtype, device=y.device)
     with L.on_device(y):
-        L.check(L.lib.b2q_moe_combine(y.data_ptr(), weights.data_ptr(), L.dt(weights), L.ptr(perm), out.data_ptr(),
-                                       L.dt(y), T, top_k, H, 1 if w_by_row else 0, L.stream(y)))
+        L.check(L.lib.b2q_moe_combine(y.data_ptr(), L.ptr(weights), L.dt(weights) if weights is not None else 0, L.ptr(perm),
+                                       out.data_ptr(), L.dt(y), T, top_k, H, 1 if w_by_row else 0, L.stream(y)))
     return out
 
 
@@ -393,7 +406,7 @@ def moe_gemm_fp8(x, weight, scale, expert_offsets, rows, scale_mode, *, out=None
     if expert_offsets.dtype != torch.int32:
         expert_offsets = expert_offsets.view(torch.int32) if expert_offsets.element_size() == 4 else expert_offsets.to(torch.int32)
     _chk(expert_offsets.numel() == E + 1, "expert_idx must have E+1 entries")
-    n_out = N // 2 if act == L.ACT_SILU_MUL else N
+    n_out = N // 2 if act in (L.ACT_SILU_MUL, L.ACT_GELU_TANH_MUL) else N
     if out is None:
         out = torch.empty(rows, n_out, dtype=x.dtype, device=x.device)
     wsb = L.lib.b2q_moe_gemm_workspace_bytes(rows, E, N, K, act, 1 if row_map is not None else 0)
@@ -520,3 +533,69 @@ def moe_forward_cutlass_nmajor_int4_full(x, logits, w13, w13_scales, w2, w2_scal
     g = torch.nn.functional.linear(x, sg.to(x.dtype))
     y = torch.nn.functional.linear(silu_mul(g), sd.to(x.dtype)).contiguous()
     return moe_shared_gate_add(x, sw.to(x.dtype).contiguous(), y, routed, out=routed)
+
+
+# --------------------------------------------------------------------------- FP8 grouped MoE (moe_ops namespace)
+def _offsets_closed(expert_offsets, total):
+    """The reference's gather returns E exclusive-prefix entries; the grouped GEMM wants the closing E+1-th too."""
+    tail = torch.full((1,), total, dtype=torch.int32, device=expert_offsets.device)
+    return torch.cat([expert_offsets.to(torch.int32), tail])
+
+
+def _fp8_experts(w):
+    _chk(w.dim() == 3 and w.is_contiguous(), "expert weights must be contiguous [E, N, K]")
+    return w.view(torch.float8_e4m3fn) if w.dtype in (torch.uint8, torch.int8) else w
+
+
+def moe_up_fp8_grouped(x, gate_up_weight, gate_up_scale, expert_offsets, expert_tokens, top_k, n_routed_experts):
+    """moe_ops.moe_up_fp8_grouped (csrc/moe_batch/moe_fp8_grouped.h:247-291): e4m3 [E, 2I, H] weights with one fp32
+    scale per expert, token rows gathered through expert_tokens (pair = token * top_k + slot), GELU-tanh(gate) * up,
+    result rows indexed by pair: [T * top_k, I]."""
+    L.require_cuda(x, gate_up_weight, gate_up_scale, expert_offsets, expert_tokens)
+    w = _fp8_experts(gate_up_weight)
+    _chk(w.shape[0] == n_routed_experts and gate_up_scale.numel() == n_routed_experts, "one scale per expert")
+    total = x.shape[0] * top_k
+    _chk(expert_tokens.numel() == total and expert_tokens.dtype == torch.int32, "expert_tokens must be int32 [T * top_k]")
+    off = _offsets_closed(expert_offsets, total)
+    return moe_gemm_fp8(x.contiguous(), w, gate_up_scale.float().contiguous(), off, total, L.SCALE_TENSOR,
+                        row_map=expert_tokens, row_div=top_k, out_map=expert_tokens, act=L.ACT_GELU_TANH_MUL)
+
+
+def moe_down_fp8_grouped(intermediate, down_weight, down_scale, routing_weights, expert_offsets, expert_tokens, top_k,
+                         n_routed_experts, weighted=True):
+    """moe_ops.moe_down_fp8_grouped (csrc/moe_batch/moe_fp8_grouped.h:293-335): per-route output rows [T * top_k, H],
+    indexed by pair and multiplied by the pair's routing weight."""
+    L.require_cuda(intermediate, down_weight, down_scale, expert_offsets, expert_tokens)
+    w = _fp8_experts(down_weight)
+    total = intermediate.shape[0]
+    off = _offsets_closed(expert_offsets, total)
+    y = moe_gemm_fp8(intermediate.contiguous(), w, down_scale.float().contiguous(), off, total, L.SCALE_TENSOR,
+                     row_map=expert_tokens, row_div=1, out_map=expert_tokens)
+    if weighted:
+        rw = routing_weights.reshape(-1).contiguous()
+        _chk(rw.numel() == total, "routing_weights must hold one weight per (token, slot) pair")
+        moe_combine(y, rw, None, total, 1, out=y)            # row t scaled by rw[t], in place
+    return y
+
+
+def moe_forward_full_fp8_grouped(x, gate_up_weight, gate_up_scale, down_weight, down_scale, routing_weights,
+                                 expert_offsets, expert_tokens, top_k, n_routed_experts):
+    """moe_ops.moe_forward_full_fp8_grouped (csrc/moe_batch/moe_fp8_grouped.h:370-400): up, down and the sum over a
+    token's top_k routes in one call.  The routing weight is applied inside the fp32 sum (one rounding) instead of
+    to the 16-bit per-route rows."""
+    T = x.shape[0]
+    inter = moe_up_fp8_grouped(x, gate_up_weight, gate_up_scale, expert_offsets, expert_tokens, top_k, n_routed_experts)
+    y = moe_down_fp8_grouped(inter, down_weight, down_scale, None, expert_offsets, expert_tokens, top_k,
+                             n_routed_experts, weighted=False)
+    rw = routing_weights.reshape(-1).contiguous()
+    _chk(rw.numel() == T * top_k, "routing_weights must hold one weight per (token, slot) pair")
+    return moe_combine(y, rw, None, T, top_k)
+
+
+def moe_accumulate(partials, top_k, num_shared_experts):
+    """moe_ops.moe_accumulate (csrc/moe_batch/moe.sycl:1177-1230): out[t] = sum of the token's top_k + num_shared
+    consecutive rows of partials, fp32 sum, one rounding."""
+    L.require_cuda(partials)
+    rpt = top_k + num_shared_experts
+    _chk(partials.dim() == 2 and partials.is_contiguous() and partials.shape[0] % rpt == 0, "partials must be [T * rows_per_token, H]")
+    return moe_combine(partials, None, None, partials.shape[0] // rpt, rpt)

@@ -44,6 +44,7 @@ _SIGS = {
     "b2q_moe_route_static": (i32, [vp, i64, i32, vp, vp, vp, vp, vp]),
     "b2q_gather_rows": (i32, [vp, vp, i32, vp, i64, i64, i32, vp]),
     "b2q_silu_mul": (i32, [vp, vp, i32, i64, i64, vp]),
+    "b2q_gelu_tanh_mul": (i32, [vp, vp, i32, i64, i64, vp]),
     "b2q_moe_combine": (i32, [vp, vp, i32, vp, vp, i32, i64, i32, i64, i32, vp]),
     "b2q_moe_gemm_workspace_bytes": (sz, [i64, i32, i64, i64, i32, i32]),
     "b2q_moe_shared_gate_add": (i32, [vp, vp, vp, vp, vp, i32, i64, i64, vp]),
@@ -71,7 +72,7 @@ BF16, F16, F32 = 0, 1, 2
 W4_NMAJOR, W4_KMAJOR, W4_KMAJOR_MARLIN, W4_NMAJOR_S4 = 0, 1, 2, 3
 E4M3, E5M2 = 0, 1
 SCALE_CHANNEL, SCALE_TENSOR, SCALE_BLOCK128 = 0, 1, 2
-ACT_NONE, ACT_SILU_MUL, ACT_SILU_MUL_IN = 0, 1, 2
+ACT_NONE, ACT_SILU_MUL, ACT_SILU_MUL_IN, ACT_GELU_TANH_MUL = 0, 1, 2, 3
 
 _DT = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
 

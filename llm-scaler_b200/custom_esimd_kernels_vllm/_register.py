@@ -15,6 +15,7 @@ from . import _impl as I
 from . import _lib as L
 
 _LIBS = {}
+IMPLEMENTED = {}      # namespace -> names of the ops registered with an implementation
 
 
 def _lib(ns):
@@ -27,6 +28,7 @@ def _op(ns, schema, fn, meta=None):
     lib = _lib(ns)
     lib.define(schema)
     name = schema.split("(", 1)[0]
+    IMPLEMENTED.setdefault(ns, []).append(name)
     lib.impl(name, fn, "CUDA")
     if meta is not None:
         lib.impl(name, meta, "Meta")
@@ -417,5 +419,117 @@ _op(INS, "moe_forward_cutlass_nmajor_int4_full(Tensor x, Tensor logits, "
     "Tensor w13, Tensor w13_scales, Tensor w2, Tensor w2_scales, "
     "Tensor shared_gu_w, Tensor shared_d_w, Tensor shared_gate_w, "
     "int top_k, int num_shared_experts, int n_routed_experts) -> Tensor", I.moe_forward_cutlass_nmajor_int4_full)
+
+
+
+# ---------------------------------------------------------------- GELU-tanh activation; block FP8 + 16-bit dual GEMV
+def _moe_gelu_tanh_mul(input, output, N_gate_up, N_half, total_rows):
+    I._chk(N_gate_up == 2 * N_half, "N_gate_up must be 2 * N_half")
+    I.gelu_tanh_mul(input[:total_rows], output[:total_rows])
+    return output
+
+
+def _fp8_block_fp16_fused2(input, w0, s0, o0, w1, o1, block_n, block_k):
+    """o0 = input @ dequant(w0, s0)^T through the block-scaled FP8 GEMV; o1 = input @ w1^T with a dense 16-bit w1
+    (csrc/xpu/esimd_kernel_gemm.sycl:184-216).  The dense 16-bit half is a plain library GEMM: the reference's
+    16-bit GEMV (esimd_gemv_fp16) is outside this library's quantized-linear scope."""
+    _fp8_block(input, w0, s0, o0.view(input.shape[0], -1), block_n, block_k)
+    I._chk(w1.dtype == input.dtype and w1.shape[1] == input.shape[1], "w1 must be a 16-bit [N1, K] matrix of the input's type")
+    torch.matmul(input, w1.t(), out=o1.view(input.shape[0], -1))
+    return o0
+
+
+_op(NS, "esimd_moe_gelu_tanh_mul(Tensor input, Tensor output, int N_gate_up, int N_half, int total_rows) -> Tensor",
+    _moe_gelu_tanh_mul)
+_op(NS, "esimd_gemv_fp8_blockscale_fp16_fused2(Tensor input, Tensor w0, Tensor s0, Tensor(a!) o0, Tensor w1, Tensor(b!) o1, "
+        "int block_n, int block_k) -> Tensor(a!)", _fp8_block_fp16_fused2)
+
+
+# ---------------------------------------------------------------- moe_ops: FP8 (e4m3, one scale per expert) grouped MoE
+MNS = "moe_ops"
+
+
+def _moe_ops_topk(logits, top_k, norm):
+    w, ids = I.moe_topk(logits.contiguous(), top_k, bool(norm))
+    return ids, w                     # the reference returns (indices, weights) here (csrc/moe_batch/moe.sycl:1309-1345)
+
+
+def _routed_fp8(x, topk_weights, topk_indices, gu_w, gu_s, dn_w, dn_s, top_k, accumulate=True):
+    """Caller-supplied routing -> stable sort by expert -> grouped up (GELU-tanh * up) -> grouped down -> weighted sum
+    (csrc/moe_batch/moe.sycl:2249-2340)."""
+    E = gu_w.shape[0]
+    ids = topk_indices.to(torch.int32).contiguous()
+    offsets, tokens, _, _ = I.moe_route(ids, E)
+    if accumulate:
+        return I.moe_forward_full_fp8_grouped(x, gu_w, gu_s, dn_w, dn_s, topk_weights, offsets[:E], tokens, top_k, E)
+    inter = I.moe_up_fp8_grouped(x, gu_w, gu_s, offsets[:E], tokens, top_k, E)
+    return I.moe_down_fp8_grouped(inter, dn_w, dn_s, topk_weights, offsets[:E], tokens, top_k, E)
+
+
+def _full_gelu_tanh(x, logits, gu_w, gu_s, dn_w, dn_s, top_k, n_routed_experts):
+    w, ids = I.moe_topk(logits.contiguous(), top_k, True, weight_dtype=x.dtype)
+    return _routed_fp8(x, w, ids, gu_w, gu_s, dn_w, dn_s, top_k)
+
+
+def _full_gelu_tanh_routed(x, topk_weights, topk_indices, gu_w, gu_s, dn_w, dn_s, top_k, n_routed_experts):
+    return _routed_fp8(x, topk_weights, topk_indices, gu_w, gu_s, dn_w, dn_s, top_k)
+
+
+def _full_gelu_tanh_routed_no_accum(x, topk_weights, topk_indices, gu_w, gu_s, dn_w, dn_s, top_k, n_routed_experts):
+    return _routed_fp8(x, topk_weights, topk_indices, gu_w, gu_s, dn_w, dn_s, top_k, accumulate=False)
+
+
+def _full_gelu_tanh_decode(x, logits, gu_w, gu_s, dn_w, dn_s, per_expert_scale, top_k, n_routed_experts):
+    # routing weight times the chosen expert's scale, rounded to the activation type as the reference's fold kernel
+    # stores it (csrc/moe_batch/moe.sycl:2194-2201); a handful of elements, index plumbing only
+    w, ids = I.moe_topk(logits.contiguous(), top_k, True, weight_dtype=x.dtype)
+    w = (w.float() * per_expert_scale.float()[ids.long()]).to(x.dtype)
+    return _routed_fp8(x, w, ids, gu_w, gu_s, dn_w, dn_s, top_k)
+
+
+_op(MNS, "moe_accumulate(Tensor partials, int top_k, int num_shared_experts) -> Tensor", I.moe_accumulate)
+_op(MNS, "moe_topk(Tensor logits, int top_k, bool norm) -> (Tensor, Tensor)", _moe_ops_topk)
+_op(MNS, "moe_up_fp8_grouped(Tensor x, Tensor gate_up_weight, Tensor gate_up_scale, Tensor expert_offsets, "
+         "Tensor expert_tokens, int top_k, int n_routed_experts) -> Tensor", I.moe_up_fp8_grouped)
+_op(MNS, "moe_down_fp8_grouped(Tensor intermediate, Tensor down_weight, Tensor down_scale, Tensor routing_weights, "
+         "Tensor expert_offsets, Tensor expert_tokens, int top_k, int n_routed_experts) -> Tensor", I.moe_down_fp8_grouped)
+_op(MNS, "moe_forward_full_fp8_grouped(Tensor x, Tensor gate_up_weight, Tensor gate_up_scale, Tensor down_weight, "
+         "Tensor down_scale, Tensor routing_weights, Tensor expert_offsets, Tensor expert_tokens, int top_k, "
+         "int n_routed_experts) -> Tensor", I.moe_forward_full_fp8_grouped)
+_op(MNS, "moe_forward_full_gelu_tanh(Tensor x, Tensor logits, Tensor gate_up_weight, Tensor gate_up_scale, "
+         "Tensor down_weight, Tensor down_scale, int top_k, int n_routed_experts) -> Tensor", _full_gelu_tanh)
+_op(MNS, "moe_forward_full_gelu_tanh_routed_no_accum(Tensor x, Tensor topk_weights, Tensor topk_indices, "
+         "Tensor gate_up_weight, Tensor gate_up_scale, Tensor down_weight, Tensor down_scale, int top_k, "
+         "int n_routed_experts) -> Tensor", _full_gelu_tanh_routed_no_accum)
+_op(MNS, "moe_forward_full_gelu_tanh_routed(Tensor x, Tensor topk_weights, Tensor topk_indices, Tensor gate_up_weight, "
+         "Tensor gate_up_scale, Tensor down_weight, Tensor down_scale, int top_k, int n_routed_experts) -> Tensor",
+    _full_gelu_tanh_routed)
+_op(MNS, "moe_forward_full_gelu_tanh_routed_decode(Tensor x, Tensor topk_weights, Tensor topk_indices, "
+         "Tensor gate_up_weight, Tensor gate_up_scale, Tensor down_weight, Tensor down_scale, int top_k, "
+         "int n_routed_experts) -> Tensor", _full_gelu_tanh_routed)
+_op(MNS, "moe_forward_full_gelu_tanh_decode(Tensor x, Tensor logits, Tensor gate_up_weight, Tensor gate_up_scale, "
+         "Tensor down_weight, Tensor down_scale, Tensor per_expert_scale, int top_k, int n_routed_experts) -> Tensor",
+    _full_gelu_tanh_decode)
+
+
+# ---------------------------------------------------------------- the rest of the reference's op surface
+def _not_implemented(qualname):
+    def fn(*args, **kwargs):
+        raise RuntimeError("b2q: %s not implemented" % qualname)
+    return fn
+
+
+def _register_unimplemented():
+    from ._surface import UNIMPLEMENTED
+    for ns, schemas in UNIMPLEMENTED.items():
+        lib = _lib(ns)
+        for schema in schemas:
+            name = schema.split("(", 1)[0]
+            lib.define(schema)
+            # every backend key: a call must reach the message whatever device the arguments live on
+            lib.impl(name, _not_implemented("%s::%s" % (ns, name)), "CompositeExplicitAutograd")
+
+
+_register_unimplemented()
 
 REGISTERED = {ns: lib for ns, lib in _LIBS.items()}

@@ -280,3 +280,66 @@ def esimd_norm_gemv_fp8_blockscale(x, z, norm_weight, gemv_weight, gemv_scale, o
 def esimd_norm_gemv_int4_pert(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps):
     """As esimd_norm_gemv_fp8_pert with INT4 g=128 weights."""
     return _ops.esimd_norm_gemv_int4_pert(x, z, norm_weight, gemv_weight, gemv_scale, output, HV, V, eps)
+
+
+# ---- GELU-tanh activation and the block-FP8 + 16-bit dual GEMV (ops.py:117-128, :718-726 of the reference) ----
+def esimd_moe_gelu_tanh_mul(input, output, N_gate_up, N_half, total_rows):
+    """GELU_tanh(gate) * up over [rows, 2 * N_half] -> [rows, N_half]."""
+    return _ops.esimd_moe_gelu_tanh_mul(input, output, N_gate_up, N_half, total_rows)
+
+
+def esimd_gemv_fp8_blockscale_fp16_fused2(input, w0, s0, o0, w1, o1, block_n=128, block_k=128):
+    """Block-scaled e4m3 w0 and dense 16-bit w1 applied to the same input; results in o0 / o1, returns o0."""
+    return _ops.esimd_gemv_fp8_blockscale_fp16_fused2(input, w0, s0, o0, w1, o1, block_n, block_k)
+
+
+# ---- moe_ops: FP8 (e4m3, one fp32 scale per expert) MoE with GELU-tanh (ops.py:1693-1790 of the reference) ----
+_moe_batch = torch.ops.moe_ops
+
+
+class _MoeOpsNamespace:
+    """`custom_esimd_kernels_vllm.moe_ops.<op>`: the attribute callers of the reference use
+    (vllm/patches/vllm_for_multi_arc.patch:3168); every name forwards to torch.ops.moe_ops."""
+
+    def __getattr__(self, name):
+        return getattr(_moe_batch, name)
+
+
+moe_ops = _MoeOpsNamespace()
+
+
+def moe_forward_full_fp8_grouped(x, gate_up_weight, gate_up_scale, down_weight, down_scale, routing_weights,
+                                 expert_offsets, expert_tokens, top_k, n_routed_experts):
+    return _moe_batch.moe_forward_full_fp8_grouped(x, gate_up_weight, gate_up_scale, down_weight, down_scale,
+                                                   routing_weights, expert_offsets, expert_tokens, top_k, n_routed_experts)
+
+
+def moe_forward_full_gelu_tanh(x, logits, gate_up_weight, gate_up_scale, down_weight, down_scale, top_k, n_routed_experts):
+    return _moe_batch.moe_forward_full_gelu_tanh(x, logits, gate_up_weight, gate_up_scale, down_weight, down_scale,
+                                                 top_k, n_routed_experts)
+
+
+def moe_forward_full_gelu_tanh_routed(x, topk_weights, topk_indices, gate_up_weight, gate_up_scale, down_weight,
+                                      down_scale, top_k, n_routed_experts):
+    return _moe_batch.moe_forward_full_gelu_tanh_routed(x, topk_weights, topk_indices, gate_up_weight, gate_up_scale,
+                                                        down_weight, down_scale, top_k, n_routed_experts)
+
+
+def moe_forward_full_gelu_tanh_routed_decode(x, topk_weights, topk_indices, gate_up_weight, gate_up_scale, down_weight,
+                                             down_scale, top_k, n_routed_experts):
+    return _moe_batch.moe_forward_full_gelu_tanh_routed_decode(x, topk_weights, topk_indices, gate_up_weight,
+                                                               gate_up_scale, down_weight, down_scale, top_k,
+                                                               n_routed_experts)
+
+
+def moe_forward_full_gelu_tanh_routed_no_accum(x, topk_weights, topk_indices, gate_up_weight, gate_up_scale, down_weight,
+                                               down_scale, top_k, n_routed_experts):
+    return _moe_batch.moe_forward_full_gelu_tanh_routed_no_accum(x, topk_weights, topk_indices, gate_up_weight,
+                                                                 gate_up_scale, down_weight, down_scale, top_k,
+                                                                 n_routed_experts)
+
+
+def moe_forward_full_gelu_tanh_decode(x, logits, gate_up_weight, gate_up_scale, down_weight, down_scale,
+                                      per_expert_scale, top_k, n_routed_experts):
+    return _moe_batch.moe_forward_full_gelu_tanh_decode(x, logits, gate_up_weight, gate_up_scale, down_weight,
+                                                        down_scale, per_expert_scale, top_k, n_routed_experts)

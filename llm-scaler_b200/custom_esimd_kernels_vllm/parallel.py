@@ -95,18 +95,34 @@ def all_reduce(t: torch.Tensor, group=None) -> torch.Tensor:
     return t
 
 
-def tp_layer_forward(x: torch.Tensor, layer: TPLayer, backend, group=None) -> torch.Tensor:
+def tp_layer_forward(x: torch.Tensor, layer: TPLayer, backend, group=None, reduce=all_reduce) -> torch.Tensor:
     """x [M, hidden] (replicated) -> [M, hidden] (replicated).
 
     QKV (column) -> the rank's q slice stands in for the attention output -> o_proj (row, all-reduce)
-    -> gate_up (column) -> SiLU*mul -> down (row, all-reduce).  Attention itself is outside this path."""
+    -> gate_up (column) -> SiLU*mul -> down (row, all-reduce).  Attention itself is outside this path.
+    `reduce(t, group)` sums the partial results over the ranks (default: the process group's all-reduce)."""
     qkv = backend.linear_int4(x, *layer.qkv)
     k_local = layer.o[1].shape[1] * GROUP
     attn = qkv[:, :k_local].contiguous()
-    h = all_reduce(backend.linear_int4(attn, *layer.o), group)
+    h = reduce(backend.linear_int4(attn, *layer.o), group)
     gu = backend.linear_int4(h, *layer.gate_up)
     act = backend.silu_mul(gu)
-    return all_reduce(backend.linear_int4(act, *layer.down), group)
+    return reduce(backend.linear_int4(act, *layer.down), group)
+
+
+class NcclReducer:
+    """Sum of row-parallel partial results through the process group's all-reduce (NCCL over NVLink on GPUs)."""
+
+    def reduce(self, t, group=None):
+        return all_reduce(t, group)
+
+    def describe(self):
+        return "torch.distributed all_reduce (NCCL)"
+
+
+def make_reducer(M, N, dtype, device, group=None):
+    """The object whose reduce(t) sums a [M, N] partial result over the ranks of `group`."""
+    return NcclReducer()
 
 
 # ----------------------------------------------------------------------------- expert parallel
@@ -121,19 +137,26 @@ def ep_plan(ids: torch.Tensor, experts_per_rank: int, world: int, backend):
     return rows.tolist(), order, p2s, local_e
 
 
-def ep_moe_forward(x, logits, w13, s13, w2, s2, top_k: int, num_experts: int, backend, group=None):
+EP_EXCHANGE = "torch.distributed all_to_all_single (NCCL send/recv), row counts read on the host"
+
+
+def ep_moe_forward(x, logits, w13, s13, w2, s2, top_k: int, num_experts: int, backend, group=None, marks=None, world=None):
     """Expert-parallel MoE forward for this rank's tokens.
 
     x [T_local, H], logits [T_local, E]; w13 / s13 / w2 / s2 hold this rank's experts
     [E/world, ...].  Steps: top-k -> plan by destination rank -> exchange counts -> all-to-all rows and
     local expert ids -> route + grouped up GEMM + SiLU*mul + grouped down GEMM on the owner -> all-to-all back
-    -> weighted combine at the source.  Returns [T_local, H]."""
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    -> weighted combine at the source.  Returns [T_local, H].
+    `marks`, if given, is called with a label at the phase boundaries (a benchmark records CUDA events there)."""
+    mark = marks if marks is not None else (lambda label: None)
+    if world is None:
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
     T, H = x.shape
     e_local = num_experts // world
     wts, ids = backend.topk(logits, top_k, x.dtype)
     send_counts, order, p2s, local_e = ep_plan(ids, e_local, world, backend)
     send_rows = backend.gather_rows(x, order, top_k)                       # [n_pairs, H] grouped by destination
+    mark("dispatch_begin")
 
     if world > 1:
         sc = torch.tensor(send_counts, dtype=torch.int64, device=x.device)
@@ -148,15 +171,18 @@ def ep_moe_forward(x, logits, w13, s13, w2, s2, top_k: int, num_experts: int, ba
     else:
         recv_counts, n_recv, recv_rows, recv_e = send_counts, send_rows.shape[0], send_rows, local_e
 
+    mark("dispatch_end")
     if n_recv > 0:
         offsets, tokens, _, _ = backend.route(recv_e.reshape(-1, 1), e_local)
         y_recv = backend.expert_mlp(recv_rows, w13, s13, w2, s2, offsets, tokens, n_recv)
     else:
         y_recv = torch.empty(0, H, dtype=x.dtype, device=x.device)
 
+    mark("combine_begin")
     if world > 1:
         y_send = torch.empty(send_rows.shape[0], H, dtype=x.dtype, device=x.device)
         dist.all_to_all_single(y_send, y_recv, send_counts, recv_counts, group=group)
     else:
         y_send = y_recv
+    mark("combine_end")
     return backend.combine(y_send, wts, p2s, T, top_k)

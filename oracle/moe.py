@@ -120,3 +120,43 @@ def combine(y: torch.Tensor, wts: torch.Tensor, perm=None) -> torch.Tensor:
     ok = idx >= 0
     rows = y.float()[idx.clamp(min=0)] * (wts.reshape(-1).float() * ok)[:, None]
     return _ordered_sum(rows.reshape(T, k, -1)).to(y.dtype)
+
+
+def gelu_tanh_mul(g: torch.Tensor) -> torch.Tensor:
+    """gelu_tanh(gate) * up in fp32, cast back: 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+    (csrc/xpu/esimd_kernels/moe_ops.h:678-723; tests/test_moe_fp8_grouped.py:5)."""
+    I = g.shape[-1] // 2
+    gf = g[..., :I].float()
+    act = 0.5 * gf * (1.0 + torch.tanh(0.7978845608028654 * (gf + 0.044715 * gf ** 3)))
+    return (act * g[..., I:].float()).to(g.dtype)
+
+
+def forward_fp8_grouped(x, topk_w, topk_ids, w13q, s13, w2q, s2, accumulate=True):
+    """FP8 MoE with one fp32 scale per expert and GELU-tanh, routing supplied by the caller
+    (tests/test_moe_fp8_grouped.py:6-15, evaluated per expert instead of per token):
+        g = x @ (decode(w13[e]) * s13[e]).T ; mid = gelu_tanh(gate) * up -> 16 bit ;
+        y = (mid @ (decode(w2[e]) * s2[e]).T) * routing weight ; out[t] = sum over the token's routes.
+    w13q [E, 2I, H], w2q [E, H, I] e4m3; topk_w [T, k]; topk_ids int32 [T, k].  With accumulate=False returns the
+    weighted per-route rows [T * k, H] (pair order), rounded to x.dtype as the reference stores them."""
+    from . import fp8
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    E = w13q.shape[0]
+    offsets, expert_tokens, p2p, _ = route(topk_ids, E)
+    tok = (expert_tokens // k).long()
+    xs = x[tok].float()
+    inter = torch.zeros(T * k, w13q.shape[1] // 2, dtype=x.dtype)
+    y = torch.zeros(T * k, H, dtype=torch.float32)
+    for e in range(E):
+        a, b = int(offsets[e]), int(offsets[e + 1])
+        if b <= a:
+            continue
+        g = (xs[a:b] @ (fp8.decode(w13q[e]) * float(s13[e])).T).to(x.dtype)
+        mid = gelu_tanh_mul(g)
+        inter[a:b] = mid
+        y[a:b] = mid.float() @ (fp8.decode(w2q[e]) * float(s2[e])).T
+    wflat = topk_w.reshape(-1).float()
+    y_pair = y[p2p.long()]                                     # back to pair order
+    if not accumulate:
+        return (y_pair * wflat[:, None]).to(x.dtype)
+    return _ordered_sum((y_pair.to(x.dtype).float() * wflat[:, None]).reshape(T, k, H)).to(x.dtype)

@@ -1,6 +1,7 @@
 """Tensor-parallel and expert-parallel schedules on two gloo ranks (CPU).  The collectives and the sharding
 arithmetic are the product's (custom_esimd_kernels_vllm.parallel); the compute backend is the CPU oracle, so
 the test checks that sharded execution reproduces the unsharded oracle."""
+import datetime
 import os
 import socket
 
@@ -52,7 +53,7 @@ def _free_port():
 
 def _worker(rank, world, port, what, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
-    dist.init_process_group("gloo", rank=rank, world_size=world)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=120))
     try:
         from custom_esimd_kernels_vllm import parallel as P
         be = OracleBackend()
@@ -70,7 +71,7 @@ def _worker(rank, world, port, what, q):
                               gate_up=P.shard_column(*packed["gate_up"], rank, world, fused_halves=2),
                               down=P.shard_row(*packed["down"], rank, world))
             out = P.tp_layer_forward(full["x"], layer, be)
-            q.put((rank, out))
+            q.put((rank, _pack(out)))
         else:
             c = configs.c4(seed=5, T=24, E=8, top_k=2, H=128, I=128)
             T = c["x"].shape[0] // world
@@ -80,9 +81,20 @@ def _worker(rank, world, port, what, q):
             out = P.ep_moe_forward(c["x"][sl].contiguous(), c["logits"][sl].contiguous(),
                                    int4.pack_nmajor_i32(c["q13"][es]), c["s13"][es].contiguous(),
                                    int4.pack_nmajor_i32(c["q2"][es]), c["s2"][es].contiguous(), 2, 8, be)
-            q.put((rank, out))
+            q.put((rank, _pack(out)))
     finally:
         dist.destroy_process_group()
+
+
+def _pack(t):
+    """Results cross the process boundary by value: a tensor in a multiprocessing queue travels as a shared-memory
+    handle that dies with the sending process."""
+    assert t.dtype == torch.bfloat16
+    return t.contiguous().view(torch.int16).numpy().copy()
+
+
+def _unpack(a):
+    return torch.from_numpy(a).view(torch.bfloat16)
 
 
 def _run(what):
@@ -93,10 +105,19 @@ def _run(what):
     procs = [ctx.Process(target=_worker, args=(r, world, port, what, q)) for r in range(world)]
     for p in procs:
         p.start()
-    outs = dict(q.get(timeout=120) for _ in range(world))
-    for p in procs:
-        p.join(timeout=60)
-        assert p.exitcode == 0
+    try:
+        outs = {r: _unpack(a) for r, a in (q.get(timeout=120) for _ in range(world))}
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+    finally:
+        # a rank that raised leaves its peer inside a collective: never leave it running
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
     return outs
 
 

@@ -1,5 +1,6 @@
 """Tensor-parallel and expert-parallel schedules on two GPUs over NCCL, CUDA kernels underneath, against the
 unsharded CPU oracle.  Skipped when fewer than two GPUs are visible."""
+import datetime
 import os
 import socket
 
@@ -24,7 +25,7 @@ def _worker(rank, world, port, what, q):
                       NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
     try:
         from custom_esimd_kernels_vllm import parallel as P
         be = P.CudaBackend()
@@ -51,7 +52,7 @@ def _worker(rank, world, port, what, q):
                                    int4.pack_nmajor_i32(c["q13"][es]).to(dev), c["s13"][es].contiguous().to(dev),
                                    int4.pack_nmajor_i32(c["q2"][es]).to(dev), c["s2"][es].contiguous().to(dev), 2, 8, be)
         torch.cuda.synchronize()
-        q.put((rank, out.cpu()))
+        q.put((rank, out.cpu().contiguous().view(torch.int16).numpy().copy()))   # by value: a shared-memory handle dies with the sender
     finally:
         dist.destroy_process_group()
 
@@ -64,10 +65,19 @@ def _run(what):
     procs = [ctx.Process(target=_worker, args=(r, world, port, what, q)) for r in range(world)]
     for p in procs:
         p.start()
-    outs = dict(q.get(timeout=300) for _ in range(world))
-    for p in procs:
-        p.join(timeout=120)
-        assert p.exitcode == 0
+    try:
+        outs = {r: torch.from_numpy(a).view(torch.bfloat16) for r, a in (q.get(timeout=300) for _ in range(world))}
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+    finally:
+        # a rank that raised leaves its peer inside an NCCL collective holding a GPU: never leave it running
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+                p.join(10)
+                if p.is_alive():
+                    p.kill()
     return outs
 
 

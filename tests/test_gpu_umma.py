@@ -258,10 +258,21 @@ def test_bounded_wait_gives_up_and_reports(e):
     and the context is still usable for the next launch."""
     L = e._lib
     assert L.device_status() == 0
+    # a decode launch whose strips are cut along K (few strips, many SMs): it relies on the arrival counters that the
+    # reset below clears together with the status words of every kernel family
+    qb, sb = _int4(2048, 4096, torch.bfloat16, 5)
+    xb = torch.randn(40, 4096, generator=torch.Generator().manual_seed(5)).to(torch.bfloat16).to(DEV)
+    wb, sbd = int4.pack_nmajor_u8(qb).to(DEV), sb.to(DEV)
+    before = torch.empty(40, 2048, dtype=torch.bfloat16, device=DEV)
+    e.esimd_gemm_int4_pgrp(xb, wb, sbd, before)
     assert L.selftest_bounded_wait(code=777) is True
     assert L.device_status() == 777
     L.device_status_reset()
     assert L.device_status() == 0
+    after = torch.empty_like(before)
+    e.esimd_gemm_int4_pgrp(xb, wb, sbd, after)
+    assert torch.equal(before, after), "a cut-strip launch after the reset differs from the one before it"
+    assert_close(after, int4.linear(xb.cpu(), qb, sb), what="cut-strip launch after the reset")
     q, s = _int4(256, 512, torch.bfloat16, 3)
     x = torch.randn(40, 512).to(torch.bfloat16)
     out = torch.empty(40, 256, dtype=torch.bfloat16, device=DEV)
