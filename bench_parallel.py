@@ -100,11 +100,11 @@ def tp_case(M, rank, world, dev, P, be):
     x = torch.randn(M, HID, generator=torch.Generator(device=dev).manual_seed(7), device=dev).to(torch.bfloat16)
     reducer = P.make_reducer(M, HID, torch.bfloat16, dev) if world > 1 else None
 
-    def measure(stack, reduce_fn, w):
+    def measure(stack, reduce_fn, w, row_linear=None):
         def step(i):
             h = x
             for layer in stack:
-                h = P.tp_layer_forward(h, layer, be, reduce=reduce_fn)
+                h = P.tp_layer_forward(h, layer, be, reduce=reduce_fn, row_linear=row_linear)
             return h
         if M <= 64:
             return _timed_graph(step, 4, 10, w) / layers
@@ -124,8 +124,14 @@ def tp_case(M, rank, world, dev, P, be):
     if world > 1:
         g = torch.Generator(device=dev).manual_seed(100 + rank)
         stack = _tp_stack(world, layers, dev, g, P)
-        us = measure(stack, reducer.reduce, world)
+        us = measure(stack, reducer.reduce, world, getattr(reducer, "row_linear", None))
         us_nosum = measure(stack, lambda t, group=None: t, world)
+        if isinstance(reducer, P.PeerReducer):
+            # for comparison: the same sharded kernels with the process group's all-reduce, and with this library's
+            # reduction kernel run after the GEMM instead of being fed by its epilogue
+            rec["us_per_layer_nccl_all_reduce"] = round(measure(stack, P.NcclReducer().reduce, world), 1)
+            rec["us_per_layer_unfused_peer_reduce"] = round(measure(stack, reducer.reduce, world), 1)
+            rec["reduction_status"] = reducer.status()
         rec.update(us_per_layer=round(us, 1), exchange_us_per_layer=round(max(0.0, us - us_nosum), 1),
                    exchange="sum of the [M, 8192] partial results after o_proj and down: " + reducer.describe(),
                    all_reduce_bytes_per_layer=2 * M * HID * 2, speedup_vs_one_gpu=round(us1 / us, 2),

@@ -301,6 +301,52 @@ B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
                      int64_t rows, int64_t N, int64_t K, int act,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---- sum of row-parallel partial results over the GPUs of one box ----------------------------
+ * The exchange step behind a row-parallel linear (o_proj, down) of a tensor-parallel decoder layer; the
+ * reference calls the serving framework's all-reduce there (vllm/patches/vllm_for_multi_arc.patch:10185,
+ * :10199, :8006-8010).  One communicator per rank and per tile shape bound (max_rows x max_cols 16-bit
+ * values).  b2q_comm_create allocates the rank's buffer (cudaMalloc: set-up time only, the one place this
+ * library allocates) and returns its 64-byte CUDA IPC handle; the caller gathers the handles of all ranks
+ * (rank order) and passes them to b2q_comm_connect.  b2q_allreduce_sum then launches ONE kernel on the
+ * caller's stream: partial columns go to their owner rank by plain peer stores, the owner adds the `world`
+ * partial tiles in rank order in fp32 (all ranks get bit-identical results), rounds once and stores the
+ * sum into every rank's buffer; flags with a call epoch order the steps, every wait on a flag is bounded
+ * by wait_limit_ms (<= 0: two seconds) and an expired wait is reported by b2q_comm_status (the
+ * communicator must then be re-created on all ranks).  *out receives the DEVICE address of the [M, N]
+ * result inside this rank's buffer (row pitch N); it stays valid until the next call but one.
+ * All ranks must call with the same M, N, dtype, in the same order.  N % (8 * world) == 0, N / world <=
+ * 65536, M <= max_rows <= 4096.  No multicast, no library collective, no allocation per call.        */
+B2Q_API int b2q_comm_create(int rank, int world, int64_t max_rows, int64_t max_cols, void** comm, void* ipc_handle_out);
+B2Q_API int b2q_comm_connect(void* comm, const void* all_ipc_handles /* world x 64 bytes */);
+B2Q_API int b2q_comm_destroy(void* comm);
+B2Q_API int b2q_comm_status(void* comm, int* out);
+/* Device address of result area `which` (0 or 1; calls alternate between the two, starting with 0).  */
+B2Q_API int b2q_comm_result_ptr(void* comm, int which, void** out);
+B2Q_API int b2q_allreduce_sum(void* comm, const void* in, int dtype, int64_t ldi, int64_t M, int64_t N,
+                      double wait_limit_ms, void** out, void* stream);
+/* Row-parallel INT4 linear and the sum of its partial results as one call: out = sum over ranks of
+ * x_r[M, K_r] * dequant(W_r)[N, K_r]^T.  Same arguments as b2q_linear_int4; `partial` is [M, N] scratch in
+ * act_dtype (row pitch ldp).  For decode tiles (8 < M <= 64, N % (128 * world) == 0) the GEMM's epilogue
+ * itself stores each 128-column strip of its result into the owner rank's reduction slot over NVLink and
+ * raises that strip's flag, so the exchange starts while other strips are still being computed and the
+ * partial tile never goes through local memory; the reduction kernel that follows only adds and
+ * publishes.  Other shapes run the plain GEMM into `partial` followed by b2q_allreduce_sum.  *out as in
+ * b2q_allreduce_sum.  Replaces the row-parallel linear + all-reduce pairs of
+ * vllm/patches/vllm_for_multi_arc.patch:10185, :10199.                                                   */
+B2Q_API int b2q_linear_int4_allreduce(const void* x, int act_dtype, int64_t ldx, const void* w, int w_layout,
+                              const void* scale, int scale_dtype, int64_t s_stride_n, int64_t s_stride_g,
+                              void* partial, int64_t ldp, int64_t M, int64_t N, int64_t K, int group,
+                              void* workspace, size_t workspace_bytes, void* comm, double wait_limit_ms,
+                              void** out, void* stream);
+/* The same protocol with all `world` ranks living in ONE process on ONE device, for tests on a single GPU:
+ * b2q_comm_connect_local wires communicators created with ipc_handle_out == NULL to one another, and
+ * b2q_allreduce_sum_emulated runs the first n_present ranks as one cooperative launch (ranks wait for one
+ * another, so they may not be separate launches on one GPU).  n_present < world makes the present ranks'
+ * waits run out after wait_limit_ms: the give-up path, exercised without a hang.                      */
+B2Q_API int b2q_comm_connect_local(void** comms, int world);
+B2Q_API int b2q_allreduce_sum_emulated(void** comms, int world, int n_present, const void* const* ins, int dtype,
+                               int64_t ldi, int64_t M, int64_t N, double wait_limit_ms, void** outs, void* stream);
+
 /* Code of the first bounded device-side wait that expired since the library was loaded
  * (0 = none).  Synchronises the device; meant for tests and post-mortems.       */
 B2Q_API int b2q_device_status(int* out);

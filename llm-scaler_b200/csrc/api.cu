@@ -3,6 +3,7 @@
 #include "common.cuh"
 #include "smallm.cuh"
 #include "umma_gemm.cuh"
+#include "peer_reduce.cuh"
 
 namespace b2q {
 
@@ -182,9 +183,14 @@ int b2q_dequant_fp8(const void* w, int fp8_format, const void* scale, int scale_
   return dequant_fp8(w, fp8_format, scale, scale_dtype, scale_mode, out, out_dtype, N, K, (cudaStream_t)stream);
 }
 
-int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, int w_layout, const void* scale,
-                    int scale_dtype, int64_t s_stride_n, int64_t s_stride_g, void* out, int64_t ldo, int64_t M,
-                    int64_t N, int64_t K, int group, void* workspace, size_t workspace_bytes, void* stream) {
+}  // extern "C"
+
+// peer != nullptr: the output tile is delivered to the reduction slots of its owner ranks instead of to `out`
+// (tcgen05 decode kernel only; B2Q_ERR_UNSUPPORTED, with nothing launched, when another kernel would be chosen).
+static int linear_int4_core(const void* x, int act_dtype, int64_t ldx, const void* w, int w_layout, const void* scale,
+                            int scale_dtype, int64_t s_stride_n, int64_t s_stride_g, void* out, int64_t ldo, int64_t M,
+                            int64_t N, int64_t K, int group, void* workspace, size_t workspace_bytes, void* stream,
+                            const PeerEpilogue* peer) {
   if (!x || !w || !scale || !out) return B2Q_ERR_NULL;
   if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
   if (scale_dtype < 0 || scale_dtype > 2) return B2Q_ERR_DTYPE;
@@ -204,9 +210,16 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   ua.s_stride_n = s_stride_n; ua.s_stride_g = s_stride_g;
   ua.out = out; ua.ldo = ldo; ua.M = (int)M; ua.N = (int)N; ua.K = (int)K;
   const bool umma_ok = umma_w4_supported(ua);
+  if (peer) {
+    const bool tiny_p = M <= 32 && N * K <= (int64_t)1 << 25;
+    const bool umma_p = force >= 2 || (force == 0 && (kmajor || (M > 8 && !tiny_p)));
+    if (!umma_ok || !umma_p || M > 64 || (N % 128) != 0 || force == 5 || (force == 0 && umma_w4_i8_preferred(M, N, K) && M <= 16))
+      return B2Q_ERR_UNSUPPORTED;
+    ua.peer = peer;
+  }
   // the int8 tensor-core path (umma_w4_i8.cu): decode shapes, N-major nibbles, scratch available; on request, or
   // where it measured fastest
-  if ((force == 5 || (force == 0 && umma_w4_i8_preferred(M, N, K))) && umma_ok && !kmajor && M <= 16 && workspace && aligned16(workspace) &&
+  if (!peer && (force == 5 || (force == 0 && umma_w4_i8_preferred(M, N, K))) && umma_ok && !kmajor && M <= 16 && workspace && aligned16(workspace) &&
       workspace_bytes >= b2q_linear_workspace_bytes(M, N, K)) {
     uint8_t* wsb = reinterpret_cast<uint8_t*>(workspace);
     float* inv = reinterpret_cast<float*>(wsb + align_up((size_t)umma_w4_i8_rows(M) * (size_t)K, 256));
@@ -252,6 +265,38 @@ int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, in
   p.out = out; p.ldo = ldo; p.M = (int)M; p.N = (int)N; p.K = (int)K;
   p.xor_mask = (w_layout == B2Q_W4_NMAJOR_S4) ? 0x88888888u : 0u;
   return smallm_int4(p, act_dtype == B2Q_BF16, (int)M, 0, st);
+}
+
+extern "C" {
+
+int b2q_allreduce_sum(void* comm, const void* in, int dtype, int64_t ldi, int64_t M, int64_t N, double wait_limit_ms,
+                      void** out, void* stream);
+
+int b2q_linear_int4(const void* x, int act_dtype, int64_t ldx, const void* w, int w_layout, const void* scale,
+                    int scale_dtype, int64_t s_stride_n, int64_t s_stride_g, void* out, int64_t ldo, int64_t M,
+                    int64_t N, int64_t K, int group, void* workspace, size_t workspace_bytes, void* stream) {
+  return linear_int4_core(x, act_dtype, ldx, w, w_layout, scale, scale_dtype, s_stride_n, s_stride_g, out, ldo, M, N, K,
+                          group, workspace, workspace_bytes, stream, nullptr);
+}
+
+int b2q_linear_int4_allreduce(const void* x, int act_dtype, int64_t ldx, const void* w, int w_layout, const void* scale,
+                              int scale_dtype, int64_t s_stride_n, int64_t s_stride_g, void* partial, int64_t ldp,
+                              int64_t M, int64_t N, int64_t K, int group, void* workspace, size_t workspace_bytes,
+                              void* comm, double wait_limit_ms, void** out, void* stream) {
+  if (!comm || !out || !partial) return B2Q_ERR_NULL;
+  PeerEpilogue pe;
+  int rc = peer_epilogue(comm, M, N, &pe);
+  if (rc == B2Q_OK) {
+    rc = linear_int4_core(x, act_dtype, ldx, w, w_layout, scale, scale_dtype, s_stride_n, s_stride_g, partial, ldp, M, N, K,
+                          group, workspace, workspace_bytes, stream, &pe);
+    if (rc == B2Q_OK) return b2q_allreduce_sum(comm, nullptr, act_dtype, 0, M, N, wait_limit_ms, out, stream);
+  }
+  if (rc != B2Q_ERR_UNSUPPORTED && rc != B2Q_ERR_SHAPE) return rc;
+  // another kernel serves this shape: GEMM into `partial`, then the reduction delivers the tile itself
+  rc = linear_int4_core(x, act_dtype, ldx, w, w_layout, scale, scale_dtype, s_stride_n, s_stride_g, partial, ldp, M, N, K,
+                        group, workspace, workspace_bytes, stream, nullptr);
+  if (rc) return rc;
+  return b2q_allreduce_sum(comm, partial, act_dtype, ldp, M, N, wait_limit_ms, out, stream);
 }
 
 size_t b2q_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {

@@ -69,6 +69,17 @@ __device__ __forceinline__ float load_scalar(const void* p, int64_t i, int dt) {
   if (dt == B2Q_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
   return __half2float(reinterpret_cast<const __half*>(p)[i]);
 }
+// The same load split in two: the raw bits now, the fp32 value where it is needed.  A scale fetched from DRAM well
+// ahead of its use must stay raw in between, or the warp waits for it at the load.
+__device__ __forceinline__ uint32_t load_scalar_raw(const void* p, int64_t i, int dt) {
+  if (dt == B2Q_F32) return __ldg(reinterpret_cast<const uint32_t*>(p) + i);
+  return (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p) + i);
+}
+__device__ __forceinline__ float scalar_from_raw(uint32_t raw, int dt) {
+  if (dt == B2Q_F32) return __uint_as_float(raw);
+  if (dt == B2Q_BF16) return __uint_as_float(raw << 16);
+  return __half2float(__ushort_as_half((unsigned short)raw));
+}
 __device__ __forceinline__ void store_scalar(void* p, int64_t i, int dt, float v) {
   if (dt == B2Q_F32) reinterpret_cast<float*>(p)[i] = v;
   else if (dt == B2Q_BF16) reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);

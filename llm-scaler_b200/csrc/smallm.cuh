@@ -191,14 +191,28 @@ __global__ void __launch_bounds__(128) smallm_kernel(const SmallMParams p) {
         const int kg = slab * 2 + h;
         const int k0 = slab * 256 + h * 128 + t * 32;
         if (kg * 128 < K) {
-          float sc[RT][2];
+          // group scales: requested here as raw bits, decoded only where they are used (after the MMAs of this half
+          // slab): decoding at the load would make the warp wait for DRAM right here, once per half slab
+          uint32_t scr[RT][2];
 #pragma unroll
           for (int mt = 0; mt < RT; ++mt)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
               int row = row0 + mt * 16 + g + hh * 8; row = row < N ? row : N - 1;
-              sc[mt][hh] = load_scalar(p.scale, sbase + (int64_t)row * p.s_stride_n + (int64_t)kg * p.s_stride_g, p.scale_dtype);
+              scr[mt][hh] = load_scalar_raw(p.scale, sbase + (int64_t)row * p.s_stride_n + (int64_t)kg * p.s_stride_g, p.scale_dtype);
             }
+          // activation fragments of the whole half slab in flight at once (few token tiles only: registers)
+          constexpr bool XPRE = NT <= 2;
+          uint4 xpre[XPRE ? 4 : 1][XPRE ? NT : 1];
+          if constexpr (XPRE) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                xpre[i][nt] = make_uint4(0, 0, 0, 0);
+                if (xok[nt]) xpre[i][nt] = ldg128(xptr[nt] + k0 + i * 8);
+              }
+          }
           float tmp[RT][NT][4];
 #pragma unroll
           for (int a = 0; a < RT; ++a)
@@ -220,7 +234,8 @@ __global__ void __launch_bounds__(128) smallm_kernel(const SmallMParams p) {
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
               uint4 xv = make_uint4(0, 0, 0, 0);
-              if (xok[nt]) xv = ldg128(xptr[nt] + k0 + i * 8);
+              if constexpr (XPRE) xv = xpre[i][nt];
+              else if (xok[nt]) xv = ldg128(xptr[nt] + k0 + i * 8);
               bfr[nt][0] = __byte_perm(xv.x, xv.z, 0x5410);  // (x0, x4)
               bfr[nt][1] = __byte_perm(xv.x, xv.z, 0x7632);  // (x1, x5)
               bfr[nt][2] = __byte_perm(xv.y, xv.w, 0x5410);  // (x2, x6)
@@ -245,10 +260,11 @@ __global__ void __launch_bounds__(128) smallm_kernel(const SmallMParams p) {
           for (int mt = 0; mt < RT; ++mt)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              acc[mt][nt][0] += sc[mt][0] * tmp[mt][nt][0];
-              acc[mt][nt][1] += sc[mt][0] * tmp[mt][nt][1];
-              acc[mt][nt][2] += sc[mt][1] * tmp[mt][nt][2];
-              acc[mt][nt][3] += sc[mt][1] * tmp[mt][nt][3];
+              const float s0 = scalar_from_raw(scr[mt][0], p.scale_dtype), s1 = scalar_from_raw(scr[mt][1], p.scale_dtype);
+              acc[mt][nt][0] += s0 * tmp[mt][nt][0];
+              acc[mt][nt][1] += s0 * tmp[mt][nt][1];
+              acc[mt][nt][2] += s1 * tmp[mt][nt][2];
+              acc[mt][nt][3] += s1 * tmp[mt][nt][3];
             }
         }
       }

@@ -22,6 +22,7 @@
 #include "umma_gemm.cuh"
 #include "sm100.cuh"
 #include "smallm.cuh"   // nib2_to_act / fp8x2_to_act / lds128
+#include "peer_reduce.cuh"
 
 namespace b2q {
 
@@ -33,20 +34,22 @@ __device__ int g_sk_counters[SK_BANKS * SK_MAX_STRIPS];     // arrival counters 
 #ifdef B2Q_UMMA_PROF
 // Wait-time accounting for one CTA, accumulated in registers and flushed once per role so the
 // measurement does not sit on the critical path.
-__device__ long long g_umma_prof[32];
-#define PROF_DECL long long _pa[4] = {0, 0, 0, 0}
+__device__ long long g_umma_prof[128];
+#define PROF_DECL long long _pa[8] = {0, 0, 0, 0, 0, 0, 0, 0}
 #define PROF_T0 const long long _pt = clock64()
-#define PROF_ADD(i) _pa[(i) & 3] += clock64() - _pt
+#define PROF_ADD(i) _pa[(i) & 7] += clock64() - _pt
 #define PROF_FLUSH(base) if (blockIdx.y == 7 && blockIdx.x == 0) { for (int _i = 0; _i < 4; ++_i) g_umma_prof[(base) + _i] += _pa[_i]; }
+#define PROF_FLUSH8(base) if (blockIdx.y == 7 && blockIdx.x == 0) { for (int _i = 0; _i < 8; ++_i) g_umma_prof[(base) + _i] += _pa[_i]; }
 #else
 #define PROF_DECL
 #define PROF_T0
 #define PROF_ADD(i)
 #define PROF_FLUSH(base)
+#define PROF_FLUSH8(base)
 #endif
 
 enum { WK_W4N = 0, WK_W4K = 1, WK_W8 = 2 };
-enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWEMPTY = 105, ST_ACCUM = 106, ST_ACCEMPTY = 107, ST_FIXUP = 108 };
+enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWEMPTY = 105, ST_ACCUM = 106, ST_ACCEMPTY = 107, ST_FIXUP = 108, ST_SCALERANGE = 109 };
 
 // One piece of a CTA's work: 64-k chunks [c_begin, c_begin + nk) of the strip of 128 weight rows at n0.
 // part = the strip's other chunks belong to other CTAs; slot = which of the CTA's two partial-sum slots it uses.
@@ -70,6 +73,8 @@ struct UmmaWoParams {
   int out_bf16;              // output element type (may differ from the MMA input type)
   int overlap_ok;            // host side only: launch with programmatic stream serialization
   int* status;
+  int peer_on;               // decode tiles only: the output tile goes to the owner ranks' reduction slots (peer memory)
+  PeerEpilogue peer;
 };
 
 template <bool BF16> __device__ __forceinline__ uint32_t pack2f(float a, float b) {
@@ -385,46 +390,61 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     while (ok && next_segment(sg)) {
     const int n0 = sg.n0, nk = sg.nk, c_begin = sg.c_begin;
     int nrow = n0 + t; if (nrow >= p.N) nrow = p.N - 1;
-    // The scale of a chunk (one per weight row for INT4, one per CTA for block-scaled FP8) comes from global memory
-    // and its line rarely survives in the small L1 left beside 100+ KB of shared memory, so it is requested two
-    // chunks ahead of its use: an L2 round trip on every chunk was what bounded the transform.
-    auto chunk_scale = [&](int c) -> float {
-      if (c >= nk) return 0.f;
-      if constexpr (WK == WK_W4N || WK == WK_W4K)
-        return load_scalar(p.scale, sbase + (int64_t)nrow * p.s_stride_n + (int64_t)((c_begin + c) >> 1) * p.s_stride_g, p.scale_dtype);
-      else
-        return blockscale ? reinterpret_cast<const float*>(p.scale)[sbase + (int64_t)(n0 >> 7) * kblocks + ((c_begin + c) >> 1)] : 0.f;
+    // The scale of a chunk (one per weight row for INT4, one per CTA for block-scaled FP8) comes from global memory,
+    // usually from DRAM (scales are read once per launch): about a thousand cycles.  It is requested four of this
+    // group's chunks ahead and kept as RAW BITS until its chunk is converted: decoding it to fp32 where it is loaded
+    // would make the warp wait for the load right there, on every chunk (measured: 1800 of the 2800 cycles a chunk
+    // cost a transform group).
+    auto chunk_scale_raw = [&](int c) -> uint32_t {
+      if (c >= nk) return 0u;
+      if constexpr (WK == WK_W4N || WK == WK_W4K) {
+        const int64_t i = sbase + (int64_t)nrow * p.s_stride_n + (int64_t)((c_begin + c) >> 1) * p.s_stride_g;
+        if (p.scale_dtype == B2Q_F32) return __ldg(reinterpret_cast<const uint32_t*>(p.scale) + i);
+        return (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p.scale) + i);
+      } else {
+        return blockscale ? __ldg(reinterpret_cast<const uint32_t*>(p.scale) + sbase + (int64_t)(n0 >> 7) * kblocks + ((c_begin + c) >> 1)) : 0u;
+      }
     };
+    auto scale_value = [&](uint32_t raw) -> float {
+      if constexpr (WK == WK_W4N || WK == WK_W4K) {
+        if (p.scale_dtype == B2Q_F32) return __uint_as_float(raw);
+        if (p.scale_dtype == B2Q_BF16) return __uint_as_float(raw << 16);
+        return __half2float(__ushort_as_half((unsigned short)raw));
+      } else {
+        return __uint_as_float(raw);
+      }
+    };
+    uint32_t sr0 = chunk_scale_raw(grp), sr1 = chunk_scale_raw(grp + NG), sr2 = chunk_scale_raw(grp + 2 * NG),
+             sr3 = chunk_scale_raw(grp + 3 * NG);
     // fp16 magic route with bf16 / fp32 scales: the group scale is rounded to fp16, whose normal range starts at
-    // 6.1e-5.  Every row therefore carries its own power of two: the row's scales are multiplied by 2^row_e so that
-    // the largest lands in [2^8, 2^9) (a group 2^22 below it is still a normal fp16; (q - 8) * s needs 11 bits at
-    // most, so the operand stays exact), and the fp32 accumulator row is multiplied by 2^-row_e when it is read.
+    // 6.1e-5.  Every row of a segment therefore carries its own power of two, taken from the scale of the segment's
+    // first group: the row's scales are multiplied by 2^row_e so that this first one lands in [0.5, 1), and the fp32
+    // accumulator row is multiplied by 2^-row_e when it is read ((q - 8) * s needs 11 bits at most, so the fp16
+    // operand stays exact).  Groups within 2^13 of the first one, either way, are exact; one further above would
+    // overflow fp16 and is saturated and reported through the status word (ST_SCALERANGE).
     float row_mul = 1.f, row_post = 1.f;
     if constexpr ((WK == WK_W4N || WK == WK_W4K) && !BF16 && FAST) {
       if (p.magic && p.scale_dtype != B2Q_F16) {
-        float smax = 0.f;
-        const int G = p.K >> 7;
-        const int64_t rbase = sbase + (int64_t)nrow * p.s_stride_n;
-        for (int g = 0; g < G; ++g) smax = fmaxf(smax, fabsf(load_scalar(p.scale, rbase + (int64_t)g * p.s_stride_g, p.scale_dtype)));
-        const int ex = (int)((__float_as_uint(smax) >> 23) & 0xFFu);          // biased exponent; 0 = zero / subnormal, 255 = inf / nan
+        const int ex = (int)((__float_as_uint(scale_value(chunk_scale_raw(0))) >> 23) & 0xFFu);   // biased exponent; 0 = zero / subnormal, 255 = inf / nan
         if (ex != 0 && ex != 255) {
-          int k = 8 - (ex - 127);
+          int k = 126 - ex;
           k = k > 120 ? 120 : (k < -120 ? -120 : k);
           row_mul = __uint_as_float((uint32_t)(127 + k) << 23);
           row_post = __uint_as_float((uint32_t)(127 - k) << 23);
         }
       }
     }
-    float sc_a = chunk_scale(grp), sc_b = chunk_scale(grp + NG);
 #pragma unroll 1
     for (int c = grp; c < nk; c += NG) {
-      const float sc_cur = sc_a;
-      sc_a = sc_b;
-      sc_b = chunk_scale(c + 2 * NG);
+      const uint32_t sr_cur = sr0;
+      sr0 = sr1; sr1 = sr2; sr2 = sr3;
+      sr3 = chunk_scale_raw(c + 4 * NG);
       const int r = c / CPR, j = c % CPR;
       const int gr = grb + r, rs = gr % RS;
       { PROF_T0; ok = mbar_wait(raw_full + 8 * rs, (gr / RS) & 1, abort_flag, p.status, ST_RAWFULL); PROF_ADD(0); }
       if (!ok) break;
+      float sc_cur;
+      { PROF_T0; sc_cur = scale_value(sr_cur); asm volatile("" :: "f"(sc_cur)); PROF_ADD(4); }
       const uint32_t rawrow = raw_smem + rs * Cfg::RAW_BYTES + t * 128;     // N-major / fp8: this thread's row
       const uint32_t rawcol = raw_smem + rs * Cfg::RAW_BYTES + t * 4;       // K-major: this thread's column
       {
@@ -456,7 +476,12 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           if constexpr (!BF16 && FAST) {
             if (p.magic) {
               // fp16 magic-number path: the activation pre-pass stored x in the pair order this produces
-              const __half hs = __float2half_rn(sc_cur * row_mul);
+              float ss = sc_cur * row_mul;
+              if (fabsf(ss) > 8188.f) {            // 8 * scale would leave fp16: saturate, and say so
+                ss = copysignf(8188.f, ss);
+                atomicCAS(p.status, 0, ST_SCALERANGE);
+              }
+              const __half hs = __float2half_rn(ss);
               const uint32_t hv = __half_as_ushort(hs);
               const uint32_t m2 = hv | (hv << 16);
 #pragma unroll
@@ -520,7 +545,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (!ok) break;
 
     // ---------------- epilogue of this segment ----------------
-    ok = mbar_wait(accum_full, si & 1, abort_flag, p.status, ST_ACCUM);
+    { PROF_T0; ok = mbar_wait(accum_full, si & 1, abort_flag, p.status, ST_ACCUM); PROF_ADD(5); }
     if (!ok) break;
     tc_fence_after();
     const int quad = warp & 3;                   // tensor-memory lane quadrant this warp may read
@@ -536,6 +561,20 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
     constexpr int CB = TOK >= 32 ? 32 : 16;
+    // Row-parallel layer of a tensor-parallel stack: this strip of 128 output columns belongs to one owner rank and
+    // one 128-column block of that rank's slice; the tile is stored into this rank's slot of the owner's buffer
+    // ([block][row][128 columns]) with plain peer stores, and the owner is told through flag1 when the strip is done.
+    uint16_t* peer_dst = nullptr;
+    uint32_t* peer_flag = nullptr;
+    if constexpr (BAL) {
+      if (p.peer_on) {
+        const int owner = n0 / p.peer.slice, blk = (n0 - owner * p.peer.slice) >> 7;
+        uint8_t* ob = p.peer.bufs[owner];
+        peer_dst = reinterpret_cast<uint16_t*>(ob + p.peer.slot_off + (size_t)p.peer.rank * p.peer.slot_bytes +
+                                               (size_t)blk * p.peer.M * (PR_CB * 2)) + quad * 32 + lane;
+        peer_flag = &reinterpret_cast<PeerCtrl*>(ob)->flag1[p.peer.rank][blk];
+      }
+    }
     auto write_out = [&](const uint32_t (&r)[32], int cb) {
       // per-token scales of this column block: one load per lane, read past L1 (it may still hold the previous
       // call's scales at this address), handed round the warp by shuffle
@@ -549,8 +588,9 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           int64_t orow = xrow0 + tok;
           if (p.out_map) orow = p.out_map[orow];
           const float v = __uint_as_float(r[i]) * post * ts;
-          outp[orow * p.ldo + n] = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v))
-                                              : __half_as_ushort(__float2half_rn(v));
+          uint16_t* dst = outp + orow * p.ldo + n;
+          if constexpr (BAL) { if (peer_dst) dst = peer_dst + (size_t)tok * PR_CB; }
+          *dst = p.out_bf16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
         }
       }
     };
@@ -593,6 +633,18 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       }
     }
     if (BAL && balanced && !freed) { tc_fence_before(); mbar_arrive(accum_empty); }
+    if constexpr (BAL) {
+      if (peer_flag && !sg.part) {
+        // all epilogue threads have issued their stores of this strip; one of them publishes it
+        mbar_arrive(fix_bar);
+        ok = mbar_wait(fix_bar, fixn & 1, abort_flag, p.status, ST_FIXUP); ++fixn;
+        if (!ok) break;
+        if (threadIdx.x == Cfg::CW * 32) {
+          __threadfence_system();
+          st_release_sys(peer_flag, reinterpret_cast<const PeerCtrl*>(p.peer.bufs[p.peer.rank])->epoch + 1);
+        }
+      }
+    }
     if (BAL && sg.part) {
       // Whoever delivers a strip's last partial sums adds all of them up, always in CTA order, and writes the
       // result: no CTA ever waits for another one, and the sum does not depend on who came last.
@@ -628,12 +680,22 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
         write_out(r, cb);
       }
+      if (*last_flag && peer_flag) {
+        mbar_arrive(fix_bar);
+        ok = mbar_wait(fix_bar, fixn & 1, abort_flag, p.status, ST_FIXUP); ++fixn;
+        if (!ok) break;
+        if (threadIdx.x == Cfg::CW * 32) {
+          __threadfence_system();
+          st_release_sys(peer_flag, reinterpret_cast<const PeerCtrl*>(p.peer.bufs[p.peer.rank])->epoch + 1);
+        }
+      }
     }
     gb += nk; grb += (nk + CPR - 1) / CPR; ++si;
     }   // segments
 #ifdef B2Q_UMMA_PROF
     _pa[3] = clock64() - _loop0;
     if (threadIdx.x == Cfg::CW * 32) { PROF_FLUSH(4); }
+    if (lane == 0) { PROF_FLUSH8(32 + (warp - Cfg::CW) * 8); }
 #endif
   }
 
@@ -751,8 +813,8 @@ int umma_read_status(int* out) {
 #ifdef B2Q_UMMA_PROF
 extern "C" __attribute__((visibility("default"))) int b2q_debug_prof(long long* out, int reset) {
   cudaDeviceSynchronize();
-  if (out && cudaMemcpyFromSymbol(out, g_umma_prof, sizeof(long long) * 32) != cudaSuccess) return -1;
-  if (reset) { long long z[32] = {0}; cudaMemcpyToSymbol(g_umma_prof, z, sizeof(z)); }
+  if (out && cudaMemcpyFromSymbol(out, g_umma_prof, sizeof(long long) * 128) != cudaSuccess) return -1;
+  if (reset) { long long z[128] = {0}; cudaMemcpyToSymbol(g_umma_prof, z, sizeof(z)); }
   return 0;
 }
 #endif
@@ -903,6 +965,10 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.status = status_ptr();
   p.overlap_ok = (a.after_prep || tls().overlap_mode == 2) ? 1 : 0;
   p.sk_grid = plan_balanced(p, a, a.M, a.N, a.K, 4, tok);
+  if (a.peer) {
+    if (tok > 64 || grouped || (a.N % 128) != 0 || (a.peer->slice % 128) != 0 || a.peer->M != a.M) return B2Q_ERR_UNSUPPORTED;
+    p.peer_on = 1; p.peer = *a.peer;
+  }
   const bool fast = a.magic || (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
   return kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)

@@ -30,6 +30,7 @@ struct UmmaW4Args : UmmaGroupArgs {
   const void* scale; int scale_dtype; int64_t s_stride_n, s_stride_g;
   void* out; int64_t ldo;
   int M, N, K;
+  const struct PeerEpilogue* peer = nullptr;   // decode tiles: deliver the output to the owner ranks' reduction slots
 };
 
 struct UmmaW8Args : UmmaGroupArgs {
@@ -93,3 +94,8 @@ int umma_reset_status();
 int umma_selftest_bounded_wait(int code, int* gave_up_dev, cudaStream_t st);
 
 }  // namespace b2q
+
+namespace b2q {
+struct PeerEpilogue;
+int peer_epilogue(void* comm, int64_t M, int64_t N, PeerEpilogue* out);
+}

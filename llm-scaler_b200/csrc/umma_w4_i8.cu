@@ -274,21 +274,22 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
 #pragma unroll
       for (int i = 0; i < MPMAX; ++i) acc[i] = 0.f;
       // group scales of this row, fetched four groups ahead of their use
-      float sc_nxt[4];
+      // (as raw bits: decoding a value at its load would make the warp wait for DRAM there, once per group)
+      uint32_t sc_nxt[4];
       const int ng = sg.g_end - sg.g_begin;
-      auto group_scale = [&](int j) -> float {      // scale of the j-th group in processing order
-        if (j >= ng) return 0.f;
+      auto group_scale = [&](int j) -> uint32_t {   // raw scale of the j-th group in processing order
+        if (j >= ng) return 0u;
         const int g = sg.g_begin + (j + sg.rot) % ng;
-        return load_scalar(p.scale, (int64_t)nn * p.s_stride_n + (int64_t)g * p.s_stride_g, p.scale_dtype);
+        return load_scalar_raw(p.scale, (int64_t)nn * p.s_stride_n + (int64_t)g * p.s_stride_g, p.scale_dtype);
       };
 #pragma unroll
       for (int j = 0; j < 4; ++j) sc_nxt[j] = group_scale(j);
 #pragma unroll 1
       for (int gb = 0; gb < ng && ok; gb += 4) {
-        float sc_cur[4];
+        uint32_t sc_raw[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          sc_cur[j] = sc_nxt[j];
+          sc_raw[j] = sc_nxt[j];
           sc_nxt[j] = group_scale(gb + 4 + j);
         }
 #pragma unroll
@@ -312,6 +313,7 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
             if (ok) {
               WP_T0;
               tc_fence_after();
+              const float scj = scalar_from_raw(sc_raw[j], p.scale_dtype);
 #pragma unroll
               for (int mb = 0; mb < MPMAX / 8; ++mb) {
                 if (mb * 8 < p.Mp) {
@@ -324,7 +326,7 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                   for (int i = 0; i < 8; ++i) {
                     const float v = (float)(int)a[i] + (float)(int)b[i] * 0.0078125f + (float)(int)c[i] * 6.103515625e-05f -
                                     8.f * xv[mb * 8 + i];
-                    acc[mb * 8 + i] = fmaf(sc_cur[j], v, acc[mb * 8 + i]);
+                    acc[mb * 8 + i] = fmaf(scj, v, acc[mb * 8 + i]);
                   }
                 }
               }

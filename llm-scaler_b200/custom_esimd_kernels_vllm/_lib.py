@@ -55,6 +55,16 @@ _SIGS = {
                                 i64, i64, i64, i32, i32, vp, sz, vp]),
     "b2q_moe_gemm_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
                                i64, i64, i64, i32, vp, sz, vp]),
+    "b2q_comm_create": (i32, [i32, i32, i64, i64, vp, vp]),
+    "b2q_comm_connect": (i32, [vp, vp]),
+    "b2q_comm_connect_local": (i32, [vp, i32]),
+    "b2q_comm_destroy": (i32, [vp]),
+    "b2q_comm_status": (i32, [vp, vp]),
+    "b2q_comm_result_ptr": (i32, [vp, i32, vp]),
+    "b2q_allreduce_sum": (i32, [vp, vp, i32, i64, i64, i64, C.c_double, vp, vp]),
+    "b2q_linear_int4_allreduce": (i32, [vp, i32, i64, vp, i32, vp, i32, i64, i64, vp, i64, i64, i64, i64, i32, vp, sz, vp,
+                                        C.c_double, vp, vp]),
+    "b2q_allreduce_sum_emulated": (i32, [vp, i32, i32, vp, i32, i64, i64, i64, C.c_double, vp, vp]),
     "b2q_set_force_kernel": (None, [i32]),
     "b2q_set_overlap_mode": (None, [i32]),
     "b2q_last_kernel": (C.c_char_p, []),
@@ -165,3 +175,19 @@ def set_overlap_mode(mode: int) -> None:
     """0 = no kernel overlap, 1 = pre-pass/GEMM overlap (default), 2 = also declare weights static
     (a GEMM may stream weights while earlier kernels of the stream are still draining)."""
     lib.b2q_set_overlap_mode(int(mode))
+
+
+class DeviceView:
+    """Exposes a range of device memory owned by libb2q.so to torch through the CUDA array interface."""
+
+    def __init__(self, ptr: int, nbytes: int, owner=None):
+        self.owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+
+
+def view_as_tensor(ptr: int, shape, dtype: torch.dtype, device, owner=None) -> torch.Tensor:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    nbytes = n * torch.empty((), dtype=dtype).element_size()
+    return torch.as_tensor(DeviceView(ptr, nbytes, owner), device=device).view(dtype).view(*shape)

@@ -95,19 +95,20 @@ def all_reduce(t: torch.Tensor, group=None) -> torch.Tensor:
     return t
 
 
-def tp_layer_forward(x: torch.Tensor, layer: TPLayer, backend, group=None, reduce=all_reduce) -> torch.Tensor:
+def tp_layer_forward(x: torch.Tensor, layer: TPLayer, backend, group=None, reduce=all_reduce, row_linear=None) -> torch.Tensor:
     """x [M, hidden] (replicated) -> [M, hidden] (replicated).
 
     QKV (column) -> the rank's q slice stands in for the attention output -> o_proj (row, all-reduce)
     -> gate_up (column) -> SiLU*mul -> down (row, all-reduce).  Attention itself is outside this path.
-    `reduce(t, group)` sums the partial results over the ranks (default: the process group's all-reduce)."""
+    `reduce(t, group)` sums the partial results over the ranks (default: the process group's all-reduce);
+    `row_linear(x, w, s)`, if given, computes a row-parallel linear AND the sum in one call (PeerReducer.row_linear)."""
     qkv = backend.linear_int4(x, *layer.qkv)
     k_local = layer.o[1].shape[1] * GROUP
-    attn = qkv[:, :k_local].contiguous()
-    h = reduce(backend.linear_int4(attn, *layer.o), group)
+    attn = qkv[:, :k_local]
+    h = row_linear(attn, *layer.o) if row_linear else reduce(backend.linear_int4(attn, *layer.o), group)
     gu = backend.linear_int4(h, *layer.gate_up)
     act = backend.silu_mul(gu)
-    return reduce(backend.linear_int4(act, *layer.down), group)
+    return row_linear(act, *layer.down) if row_linear else reduce(backend.linear_int4(act, *layer.down), group)
 
 
 class NcclReducer:
@@ -120,8 +121,97 @@ class NcclReducer:
         return "torch.distributed all_reduce (NCCL)"
 
 
-def make_reducer(M, N, dtype, device, group=None):
-    """The object whose reduce(t) sums a [M, N] partial result over the ranks of `group`."""
+class PeerReducer:
+    """Sum of [M, N] row-parallel partial results through this library's own kernel over peer memory
+    (b2q_allreduce_sum in include/b2q.h): one launch per call, plain peer stores over NVLink, bounded flag waits.
+    For the decode shapes (M <= 64), where a library all-reduce costs more than the GEMM it follows.
+
+    reduce(t) returns a view of the communicator's result area, valid until the next call but one."""
+
+    def __init__(self, M, N, dtype, device, group=None):
+        import ctypes as C
+        from . import _lib as L
+        self.L, self.C = L, C
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.M, self.N, self.dtype, self.device = M, N, dtype, torch.device(device)
+        self.comm = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        with torch.cuda.device(self.device):
+            L.check(L.lib.b2q_comm_create(self.rank, self.world, M, N, C.byref(self.comm), handle))
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+            every = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(every, mine, group=group)
+            blob = bytes(torch.cat(every).cpu().tolist())
+            L.check(L.lib.b2q_comm_connect(self.comm, blob))
+            dist.barrier(group)
+        self.views = []
+        for which in (0, 1):
+            ptr = C.c_void_p()
+            L.check(L.lib.b2q_comm_result_ptr(self.comm, which, C.byref(ptr)))
+            self.views.append(L.view_as_tensor(ptr.value, (M, N), dtype, self.device, owner=self))
+        self.calls = 0
+
+    def reduce(self, t, group=None):
+        L, C = self.L, self.C
+        if tuple(t.shape) != (self.M, self.N) or t.dtype != self.dtype or t.stride(1) != 1:
+            raise RuntimeError("b2q: partial tile does not match the communicator's shape")
+        out = C.c_void_p()
+        L.check(L.lib.b2q_allreduce_sum(self.comm, t.data_ptr(), L.dt(t), t.stride(0), self.M, self.N, 0.0, C.byref(out),
+                                         L.stream(t)))
+        view = self.views[self.calls & 1]
+        self.calls += 1
+        assert view.data_ptr() == out.value
+        return view
+
+    def row_linear(self, x, w, s):
+        """x [M, K_local] @ dequant(w [N, K_local/8] int32 / [N, K_local/2] uint8, scales s [N, K_local/128])^T summed
+        over the ranks, as ONE library call (b2q_linear_int4_allreduce): the GEMM's epilogue delivers its strips
+        straight into the owner ranks' reduction slots."""
+        from . import _impl as I
+        L, C = self.L, self.C
+        wt, layout, N, K, sn, sg = I._int4_view(w, s)
+        M = x.shape[0]
+        if (M, N) != (self.M, self.N) or x.dtype != self.dtype or x.shape[1] != K or x.stride(1) != 1:
+            raise RuntimeError("b2q: operands do not match the communicator's tile")
+        wsb = L.lib.b2q_linear_workspace_bytes(M, N, K)
+        ws = torch.empty(wsb, dtype=torch.uint8, device=x.device)
+        partial = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        out = C.c_void_p()
+        L.check(L.lib.b2q_linear_int4_allreduce(x.data_ptr(), L.dt(x), x.stride(0), wt.data_ptr(), layout, s.data_ptr(), L.dt(s),
+                                                 sn, sg, partial.data_ptr(), N, M, N, K, GROUP, L.ptr(ws), wsb, self.comm, 0.0,
+                                                 C.byref(out), L.stream(x)))
+        view = self.views[self.calls & 1]
+        self.calls += 1
+        assert view.data_ptr() == out.value
+        return view
+
+    def status(self):
+        v = self.C.c_int(0)
+        self.L.check(self.L.lib.b2q_comm_status(self.comm, self.C.byref(v)))
+        return int(v.value)
+
+    def describe(self):
+        return "b2q_allreduce_sum: one kernel, peer stores over NVLink, partial tiles added in rank order (fp32), bounded flag waits"
+
+    def close(self):
+        if self.comm:
+            self.views = []
+            self.L.lib.b2q_comm_destroy(self.comm)
+            self.comm = None
+
+
+def make_reducer(M, N, dtype, device, group=None, kind=None):
+    """The object whose reduce(t) sums a [M, N] partial result over the ranks of `group`: this library's peer-memory
+    kernel for decode-sized tiles on CUDA devices, the process group's all-reduce otherwise (kind / B2Q_REDUCER =
+    "peer" or "nccl" forces one)."""
+    import os
+    kind = kind or os.environ.get("B2Q_REDUCER")
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    cuda = torch.device(device).type == "cuda"
+    if kind is None:
+        kind = "peer" if (cuda and world > 1 and world <= 8 and M <= 64 and N % (8 * world) == 0) else "nccl"
+    if kind == "peer" and cuda and world > 1:
+        return PeerReducer(M, N, dtype, device, group)
     return NcclReducer()
 
 

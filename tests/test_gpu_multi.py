@@ -29,7 +29,7 @@ def _worker(rank, world, port, what, q):
     try:
         from custom_esimd_kernels_vllm import parallel as P
         be = P.CudaBackend()
-        if what == "tp":
+        if what in ("tp", "tp_peer", "tp_fused"):
             full = configs.c5_layer(seed=3, M=40, tp=1, rank=0, scale=1 / 16)
             packed = {n: (int4.pack_nmajor_i32(full[n][0]), full[n][1]) for n in ("qkv", "o", "gate_up", "down")}
             hidden = full["x"].shape[1]
@@ -42,7 +42,23 @@ def _worker(rank, world, port, what, q):
                               o=to(P.shard_row(*packed["o"], rank, world)),
                               gate_up=to(P.shard_column(*packed["gate_up"], rank, world, fused_halves=2)),
                               down=to(P.shard_row(*packed["down"], rank, world)))
-            out = P.tp_layer_forward(full["x"].to(dev), layer, be)
+            if what == "tp":
+                out = P.tp_layer_forward(full["x"].to(dev), layer, be)
+            else:
+                # the library's own exchange: peer-memory reduction kernel, alone ("tp_peer") or fed directly by the GEMM
+                # epilogue ("tp_fused"); three passes so that the flag epochs and both result areas are exercised
+                red = P.make_reducer(40, hidden, torch.bfloat16, dev, kind="peer")
+                assert isinstance(red, P.PeerReducer)
+                x = full["x"].to(dev)
+                for _ in range(3):
+                    out = P.tp_layer_forward(x, layer, be, reduce=red.reduce,
+                                             row_linear=red.row_linear if what == "tp_fused" else None).clone()
+                torch.cuda.synchronize()
+                assert red.status() == 0, "a bounded wait of the reduction expired"
+                from custom_esimd_kernels_vllm import _lib
+                assert _lib.device_status() == 0
+                dist.barrier()
+                red.close()
         else:
             c = configs.c4(seed=5, T=256, E=8, top_k=2, H=256, I=128)
             T = c["x"].shape[0] // world
@@ -101,6 +117,21 @@ def test_tensor_parallel_layer_two_gpus(two_gpus):
     h = lin(lin(x, "qkv")[:, :x.shape[1]].contiguous(), "o")
     ref = lin(moe.silu_mul(lin(h, "gate_up")), "down")
     assert _err(outs[0], ref) < 3e-2          # four chained GEMMs with 16-bit tensors between them
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("what", ["tp_peer", "tp_fused"])
+def test_tensor_parallel_layer_two_gpus_own_exchange(two_gpus, what):
+    """The same layer with the sum of the row-parallel partial results done by this library's kernels over peer
+    memory instead of the process group's all-reduce; every rank must hold bit-identical results."""
+    outs = _run(what)
+    assert torch.equal(outs[0], outs[1])
+    full = configs.c5_layer(seed=3, M=40, tp=1, rank=0, scale=1 / 16)
+    x = full["x"]
+    lin = lambda t, name: int4.linear(t, *full[name]).to(x.dtype)
+    h = lin(lin(x, "qkv")[:, :x.shape[1]].contiguous(), "o")
+    ref = lin(moe.silu_mul(lin(h, "gate_up")), "down")
+    assert _err(outs[0], ref) < 3e-2
 
 
 @pytest.mark.timeout(600)
