@@ -191,6 +191,19 @@ B2Q_API int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx,
                    int64_t M, int64_t N, int64_t K,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* Residual add + RMSNorm + FP8 weight-only linear as one call (esimd_resadd_norm_gemv_fp8_pert,
+ * esimd_scaled_resadd_norm_gemv_fp8_pert: csrc/xpu/esimd_kernels/norm_gemv_fused.h,
+ * scaled_resadd_norm_gemv_fp8.h:70-95):
+ *   v = (hidden + residual) * scalar;  residual <- v;  normed_out <- v * rsqrt(mean(v^2) + eps) * norm_weight;
+ *   out = normed_out * dequant(W)^T            (normed_out as stored, i.e. rounded to act_dtype).
+ * hidden, residual, normed_out are contiguous [M, K], norm_weight [K]; the rest as b2q_linear_fp8.  On the decode
+ * path (M <= 64, per-channel or per-tensor scale, scratch given) the norm runs inside the GEMV's own activation
+ * pre-pass: two launches in all (pre-pass, GEMV) instead of three; elsewhere the norm is its own launch.          */
+B2Q_API int b2q_resadd_norm_linear_fp8(const void* hidden, void* residual, const void* norm_weight, void* normed_out,
+                               float eps, float scalar, int act_dtype, const void* w, int fp8_format,
+                               const void* scale, int scale_dtype, int scale_mode, void* out, int64_t ldo,
+                               int64_t M, int64_t N, int64_t K, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Per-token, per-128-column dynamic e4m3 quantisation of activations:
  * xs[m, kb] = max(amax(x[m, 128kb:128kb+128]), 1e-12) / 448 ; xq = e4m3(x / xs).
  * (the (1,128) dynamic activation key of

@@ -31,6 +31,7 @@ int quantize_q4_0(const void*, bool, int64_t, void*, void*, int64_t, int64_t, cu
 int resadd_rmsnorm(const void*, void*, const void*, void*, const void*, void*, bool, int64_t, int, float, float, cudaStream_t);
 int gated_rmsnorm(const void*, const void*, const void*, void*, bool, int, int, float, cudaStream_t);
 int act_split_i8(const void*, bool, int64_t, void*, float*, float*, int64_t, int, cudaStream_t);
+int resadd_norm_split_fp8(const void*, void*, const void*, void*, bool, float, float, void*, float*, int64_t, int, cudaStream_t);
 
 static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -309,9 +310,14 @@ size_t b2q_linear_fp8_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   return a > b ? a : b;
 }
 
-int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
-                   int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
-                   void* workspace, size_t workspace_bytes, void* stream) {
+}  // extern "C"
+
+// Residual add + RMSNorm in front of the GEMV: when `nf` is given, x is the normed_out buffer the front end fills.
+struct NormFront { const void* hidden; void* residual; const void* norm_weight; float eps, scalar; };
+
+static int linear_fp8_core(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
+                           int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                           void* workspace, size_t workspace_bytes, void* stream, const NormFront* nf) {
   if (!x || !w || !scale || !out) return B2Q_ERR_NULL;
   if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
   if (fp8_format != B2Q_E4M3 && fp8_format != B2Q_E5M2) return B2Q_ERR_DTYPE;
@@ -339,7 +345,10 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
   if (force == 0 && have_ws && M <= 64 && scale_mode != B2Q_SCALE_BLOCK128 && umma_ok) {
     float* inv = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) +
                                           align_up((size_t)umma_w8_direct_rows(M, false) * (size_t)K, 256));
-    int rc = act_split_fp8(x, act_dtype == B2Q_BF16, ldx, workspace, inv, M, (int)K, st);
+    // with a norm front end, ONE pre-pass launch does residual add, RMSNorm (normed_out = x) and the term split
+    int rc = nf ? resadd_norm_split_fp8(nf->hidden, nf->residual, nf->norm_weight, const_cast<void*>(x), act_dtype == B2Q_BF16,
+                                        nf->eps, nf->scalar, workspace, inv, M, (int)K, st)
+                : act_split_fp8(x, act_dtype == B2Q_BF16, ldx, workspace, inv, M, (int)K, st);
     if (rc) return rc;
     UmmaW8DirectArgs da{};
     da.xq = workspace; da.inv_scale = inv; da.terms = act_dtype == B2Q_BF16 ? 2 : 3;
@@ -348,6 +357,11 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
     da.partials = reinterpret_cast<uint8_t*>(inv) + align_up((size_t)M * 4, 256);
     da.partial_bytes = umma_w8_direct_partial_bytes(M);
     return umma_w8_direct_linear(da, st);
+  }
+  if (nf) {      // every other kernel family: the norm as its own launch, then the ordinary path on normed_out
+    int rc = resadd_rmsnorm(nf->hidden, nf->residual, nf->norm_weight, const_cast<void*>(x), nullptr, nullptr,
+                            act_dtype == B2Q_BF16, M, (int)K, nf->eps, nf->scalar, st);
+    if (rc) return rc;
   }
   const bool prep = act_dtype == B2Q_BF16 && have_ws && (K % 8) == 0;
   const bool want_umma = force >= 2 || (force == 0 && (M > 4 || prep || act_dtype == B2Q_F16));
@@ -371,6 +385,28 @@ int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int
   const int smode = scale_mode == B2Q_SCALE_BLOCK128 ? SM_BLOCK : SM_POST;
   return act_dtype == B2Q_BF16 ? smallm_fp8_bf16(p, fp8_format, smode, (int)M, 0, st)
                                : smallm_fp8_f16(p, fp8_format, smode, (int)M, 0, st);
+}
+
+extern "C" {
+
+int b2q_linear_fp8(const void* x, int act_dtype, int64_t ldx, const void* w, int fp8_format, const void* scale,
+                   int scale_dtype, int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K,
+                   void* workspace, size_t workspace_bytes, void* stream) {
+  return linear_fp8_core(x, act_dtype, ldx, w, fp8_format, scale, scale_dtype, scale_mode, out, ldo, M, N, K, workspace,
+                         workspace_bytes, stream, nullptr);
+}
+
+int b2q_resadd_norm_linear_fp8(const void* hidden, void* residual, const void* norm_weight, void* normed_out, float eps,
+                               float scalar, int act_dtype, const void* w, int fp8_format, const void* scale, int scale_dtype,
+                               int scale_mode, void* out, int64_t ldo, int64_t M, int64_t N, int64_t K, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  if (!hidden || !residual || !norm_weight || !normed_out) return B2Q_ERR_NULL;
+  if (!is16(act_dtype)) return B2Q_ERR_DTYPE;
+  if (K <= 0 || (K % 16) != 0) return B2Q_ERR_SHAPE;
+  if (!aligned16(hidden) || !aligned16(residual) || !aligned16(norm_weight) || !aligned16(normed_out)) return B2Q_ERR_ALIGN;
+  const NormFront nf{hidden, residual, norm_weight, eps, scalar};
+  return linear_fp8_core(normed_out, act_dtype, K, w, fp8_format, scale, scale_dtype, scale_mode, out, ldo, M, N, K, workspace,
+                         workspace_bytes, stream, &nf);
 }
 
 int b2q_act_quant_fp8_1x128(const void* x, int act_dtype, int64_t ldx, void* xq, float* xs, int64_t M, int64_t K,

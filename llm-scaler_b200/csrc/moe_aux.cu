@@ -1097,6 +1097,128 @@ int resadd_rmsnorm(const void* hidden, void* residual, const void* weight, void*
 }
 
 // ---------------------------------------------------------------------------
+// Residual add + RMSNorm and the FP8 decode GEMV's activation pre-pass in ONE launch (the reference fuses the norm
+// into the GEMV kernel itself: csrc/xpu/esimd_kernels/norm_gemv_fused.h, scaled_resadd_norm_gemv_fp8.h:70-95).
+// Per row:  v = (hidden + residual) * scalar;  residual <- v;  n = v * rsqrt(mean(v^2) + eps) * weight, rounded to
+// the activation type and stored to normed_out exactly as resadd_rmsnorm_kernel stores it; then the row of ROUNDED
+// values is scaled by a power of two and split into e4m3 terms exactly as act_split_fp8_kernel splits it.  Every
+// thread reads back only what it wrote itself, so the three sweeps over the row need no grid-wide ordering.
+template <bool BF16>
+__global__ void resadd_norm_split_fp8_kernel(const void* __restrict__ hidden, void* __restrict__ residual,
+                                             const void* __restrict__ weight, void* __restrict__ normed, float eps, float scalar,
+                                             uint8_t* __restrict__ xq, float* __restrict__ inv_scale, int Mp, int K, int release_early) {
+  using T = typename Act<BF16>::T;
+  __shared__ float red[32];
+  __shared__ float bc_sh;
+  if (release_early) grid_dep_release();
+  grid_dep_wait();
+  if (!release_early) grid_dep_release();
+  const int64_t r = blockIdx.x;
+  const T* h = reinterpret_cast<const T*>(hidden) + r * K;
+  T* res = reinterpret_cast<T*>(residual) + r * K;
+  const T* w = reinterpret_cast<const T*>(weight);
+  T* out = reinterpret_cast<T*>(normed) + r * K;
+  auto load8 = [&](int k, float* v) {
+    const uint4 rv = *reinterpret_cast<const uint4*>(res + k);
+    const uint4 hv = *reinterpret_cast<const uint4*>(h + k);
+    const T* re = reinterpret_cast<const T*>(&rv);
+    const T* he = reinterpret_cast<const T*>(&hv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = (Act<BF16>::to_f(he[j]) + Act<BF16>::to_f(re[j])) * scalar;
+  };
+  auto block_reduce = [&](float v, bool is_max) -> float {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float u = __shfl_xor_sync(0xffffffffu, v, o);
+      v = is_max ? fmaxf(v, u) : v + u;
+    }
+    __syncthreads();                                    // red[] may still be read from the previous reduction
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = is_max ? 0.f : 0.f;
+      for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t = is_max ? fmaxf(t, red[i]) : t + red[i];
+      bc_sh = t;
+    }
+    __syncthreads();
+    return bc_sh;
+  };
+  float ss = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    float v[8];
+    load8(k, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss = fmaf(v[j], v[j], ss);
+  }
+  const float inv = rsqrtf(block_reduce(ss, false) / (float)K + eps);
+  float amax = 0.f;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    float v[8];
+    load8(k, v);
+    const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+    const T* we = reinterpret_cast<const T*>(&wv);
+    uint4 so, no;
+    T* se = reinterpret_cast<T*>(&so);
+    T* ne = reinterpret_cast<T*>(&no);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      se[j] = Act<BF16>::from_f(v[j]);
+      ne[j] = Act<BF16>::from_f(v[j] * inv * Act<BF16>::to_f(we[j]));
+      amax = fmaxf(amax, fabsf(Act<BF16>::to_f(ne[j])));
+    }
+    *reinterpret_cast<uint4*>(res + k) = so;
+    *reinterpret_cast<uint4*>(out + k) = no;
+  }
+  const float a = block_reduce(amax, true);
+  float sc = 1.f;
+  if (a > 0.f && a < INFINITY) {
+    int ex = (int)((__float_as_uint(a) >> 23) & 0xFF) - 127;
+    if (ex < -126) ex = -126;
+    int sh = 7 - ex;
+    sh = sh > 126 ? 126 : (sh < -126 ? -126 : sh);
+    sc = __uint_as_float((uint32_t)(sh + 127) << 23);
+  }
+  if (threadIdx.x == 0) inv_scale[r] = 1.0f / sc;
+  constexpr int NT = BF16 ? 2 : 3;
+  for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(out + k);          // this thread's own stores of the sweep above
+    const T* e = reinterpret_cast<const T*>(&v);
+    uint8_t t[NT][8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float rem = Act<BF16>::to_f(e[j]) * sc;
+#pragma unroll
+      for (int q = 0; q < NT; ++q) {
+        const uint8_t b = (uint8_t)__nv_cvt_float_to_fp8(rem, __NV_SATFINITE, __NV_E4M3);
+        t[q][j] = b;
+        rem = (rem - fp8_to_float(b, false)) * 16.f;
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < NT; ++q)
+      *reinterpret_cast<uint2*>(xq + ((int64_t)q * Mp + r) * K + k) = *reinterpret_cast<const uint2*>(t[q]);
+  }
+}
+
+int resadd_norm_split_fp8(const void* hidden, void* residual, const void* weight, void* normed, bool bf16, float eps, float scalar,
+                          void* xq, float* inv_scale, int64_t M, int K, cudaStream_t st) {
+  if (M == 0) return B2Q_OK;
+  int threads = (K / 8 + 31) / 32 * 32;
+  threads = threads > 512 ? 512 : (threads < 32 ? 32 : threads);
+  const int mode = tls().overlap_mode;
+  const int mp = (int)((M + 7) / 8 * 8);
+  cudaError_t e;
+  if (bf16)
+    e = launch_overlapped(resadd_norm_split_fp8_kernel<true>, dim3((unsigned)M), dim3(threads), 0, st, mode > 0, hidden, residual, weight,
+                          normed, eps, scalar, reinterpret_cast<uint8_t*>(xq), inv_scale, mp, K, mode == 2 ? 1 : 0);
+  else
+    e = launch_overlapped(resadd_norm_split_fp8_kernel<false>, dim3((unsigned)M), dim3(threads), 0, st, mode > 0, hidden, residual, weight,
+                          normed, eps, scalar, reinterpret_cast<uint8_t*>(xq), inv_scale, mp, K, mode == 2 ? 1 : 0);
+  note_launch("resadd_norm_split_fp8");
+  return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
 // Gated RMSNorm in front of a decode GEMV (first half of the reference's esimd_norm_gemv_* kernels,
 // csrc/xpu/esimd_kernels/norm_gemv_fused.h, norm_gemv_int4.h):  per row of x [rows, V]
 //   out = x * rsqrt(mean(x^2) + eps) * weight * silu(z),   all in fp32, one rounding to the activation type

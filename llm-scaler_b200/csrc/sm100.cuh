@@ -31,15 +31,28 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 // first.  Measured on B200 the wake-up on completion is as fast as with the default (much shorter) limit, and a
 // waiting warp executes a few instructions per 20 us instead of spinning through the issue slots its CTA's
 // working warps need.
+#ifndef B2Q_WAIT_HINT_NS
+#define B2Q_WAIT_HINT_NS 20000
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+#if B2Q_WAIT_HINT_NS > 0
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(20000u)
+      : "r"(bar), "r"(parity), "r"((uint32_t)B2Q_WAIT_HINT_NS)
       : "memory");
+#else
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+#endif
   return ok != 0;
 }
 

@@ -31,22 +31,6 @@ using namespace sm100;
 __device__ int g_umma_status = 0;
 constexpr int SK_BANKS = 64, SK_MAX_STRIPS = 1024;
 __device__ int g_sk_counters[SK_BANKS * SK_MAX_STRIPS];     // arrival counters of cut strips (see "balanced mode" below)
-#ifdef B2Q_UMMA_PROF
-// Wait-time accounting for one CTA, accumulated in registers and flushed once per role so the
-// measurement does not sit on the critical path.
-__device__ long long g_umma_prof[128];
-#define PROF_DECL long long _pa[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define PROF_T0 const long long _pt = clock64()
-#define PROF_ADD(i) _pa[(i) & 7] += clock64() - _pt
-#define PROF_FLUSH(base) if (blockIdx.y == 7 && blockIdx.x == 0) { for (int _i = 0; _i < 4; ++_i) g_umma_prof[(base) + _i] += _pa[_i]; }
-#define PROF_FLUSH8(base) if (blockIdx.y == 7 && blockIdx.x == 0) { for (int _i = 0; _i < 8; ++_i) g_umma_prof[(base) + _i] += _pa[_i]; }
-#else
-#define PROF_DECL
-#define PROF_T0
-#define PROF_ADD(i)
-#define PROF_FLUSH(base)
-#define PROF_FLUSH8(base)
-#endif
 
 enum { WK_W4N = 0, WK_W4K = 1, WK_W8 = 2 };
 enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWEMPTY = 105, ST_ACCUM = 106, ST_ACCEMPTY = 107, ST_FIXUP = 108, ST_SCALERANGE = 109 };
@@ -54,6 +38,10 @@ enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWE
 // One piece of a CTA's work: 64-k chunks [c_begin, c_begin + nk) of the strip of 128 weight rows at n0.
 // part = the strip's other chunks belong to other CTAs; slot = which of the CTA's two partial-sum slots it uses.
 struct Segment { int n0, c_begin, nk, strip, part, slot; };
+
+// constants of the fp16 magic-number nibble decode, handed to the kernel as parameters (see w4_word_magic)
+struct MagicConsts { uint32_t m_lo, m_hi, magic, c1032, r16, m72; };
+__host__ __device__ inline MagicConsts magic_consts() { return MagicConsts{0x000F000Fu, 0x00F000F0u, 0x64006400u, 0x64086408u, 0x2C002C00u, 0xD480D480u}; }
 
 struct UmmaWoParams {
   const void* scale; int scale_dtype; int scale_mode;      // scale_mode: B2Q_SCALE_* (fp8) ; ignored for int4
@@ -73,6 +61,7 @@ struct UmmaWoParams {
   int out_bf16;              // output element type (may differ from the MMA input type)
   int overlap_ok;            // host side only: launch with programmatic stream serialization
   int* status;
+  MagicConsts mk;            // constants of the fp16 magic-number nibble decode (see w4_word_magic)
   int peer_on;               // decode tiles only: the output tile goes to the owner ranks' reduction slots (peer memory)
   PeerEpilogue peer;
 };
@@ -132,17 +121,24 @@ __device__ __forceinline__ void w4_word(uint32_t w, uint32_t s2, float sf, bool 
 // (q - 8) * s is rounded to fp16 once.  Output pair order: (n0,n4) (n1,n5) (n2,n6) (n3,n7) where n_i is the
 // nibble at bits 4i; the activation pre-pass stores x in the matching order.  Integer work per word: one
 // shift and four LOP3 (the ALU pipe, not the FP pipes, is what bounds the int4 transform).
-__device__ __forceinline__ void w4_word_magic(uint32_t w, uint32_t s2, uint32_t (&o)[4]) {
-  const uint32_t c1032 = 0x64086408u, r16 = 0x2C002C00u, m72 = 0xD480D480u;
+// The six constants arrive through the kernel's parameter block (MagicConsts), not as literals: with literals the
+// compiler folds them into immediates, and since an instruction takes one immediate at most it then spends two logic
+// operations per mask-and-or and a register move per fused multiply-add (measured: 82 logic operations and 61 moves
+// per 64 k of a row where 32 and a handful are needed).
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {      // (a & b) | c in one operation
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+__device__ __forceinline__ void w4_word_magic(uint32_t w, uint32_t s2, const MagicConsts& k, uint32_t (&o)[4]) {
   const uint32_t w8 = w >> 8;
-  uint32_t v[4] = {(w & 0x000F000Fu) | 0x64006400u, (w & 0x00F000F0u) | 0x64006400u,
-                   (w8 & 0x000F000Fu) | 0x64006400u, (w8 & 0x00F000F0u) | 0x64006400u};
+  uint32_t v[4] = {and_or(w, k.m_lo, k.magic), and_or(w, k.m_hi, k.magic), and_or(w8, k.m_lo, k.magic), and_or(w8, k.m_hi, k.magic)};
   const __half2 sc = *reinterpret_cast<const __half2*>(&s2);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     __half2 h = *reinterpret_cast<__half2*>(&v[i]);
-    if (i & 1) h = __hfma2(h, *reinterpret_cast<const __half2*>(&r16), *reinterpret_cast<const __half2*>(&m72));
-    else h = __hsub2(h, *reinterpret_cast<const __half2*>(&c1032));
+    if (i & 1) h = __hfma2(h, *reinterpret_cast<const __half2*>(&k.r16), *reinterpret_cast<const __half2*>(&k.m72));
+    else h = __hsub2(h, *reinterpret_cast<const __half2*>(&k.c1032));
     h = __hmul2(h, sc);
     o[i] = *reinterpret_cast<uint32_t*>(&h);
   }
@@ -196,7 +192,9 @@ template <int TOK> struct UmmaCfg {
   static constexpr int S = (TMEM_COLS - A_COL0) / 32 > 12 ? 12 : (TMEM_COLS - A_COL0) / 32;
 };
 
-template <int WK, bool BF16, int TOK, bool FAST>
+// MAGIC: INT4 weights behind the activation pre-pass (fp16 activations in the nibble decode's pair order): its own
+// instantiation so that the decode loop carries none of the other routes' code or registers.
+template <int WK, bool BF16, int TOK, bool FAST, bool MAGIC>
 __global__ void __launch_bounds__(UmmaCfg<TOK>::THREADS, UmmaCfg<TOK>::CTAS)
 umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const UmmaWoParams p) {
   using Cfg = UmmaCfg<TOK>;
@@ -219,9 +217,6 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   volatile int* last_flag = reinterpret_cast<volatile int*>(gen + (accum_full + 36 - base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-#ifdef B2Q_UMMA_PROF
-  const long long _kt0 = clock64();
-#endif
 
   // ---- which work ----
   // Dense launches let the next kernel of the stream begin at once and themselves wait for the kernels
@@ -292,7 +287,6 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   if (warp == 0) {
     // ---------------- raw weight producer ----------------
     if (lane == 0) {
-      PROF_DECL;
       tma_prefetch_desc(&tm_w);
       int grb = 0;                       // raw stages issued so far: ring position and phase carry across segments
       bool ok = true;
@@ -300,7 +294,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         const int nraw = (sg.nk + CPR - 1) / CPR;
         for (int r = 0; r < nraw; ++r) {
           const int gr = grb + r, rs = gr % RS;
-          { PROF_T0; if (gr >= RS && !mbar_wait(raw_empty + 8 * rs, ((gr / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) { ok = false; break; } PROF_ADD(0); }
+          { if (gr >= RS && !mbar_wait(raw_empty + 8 * rs, ((gr / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) { ok = false; break; } }
           mbar_expect_tx(raw_full + 8 * rs, Cfg::RAW_BYTES);
           if constexpr (WK == WK_W4K)
             tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, sg.n0, expert * p.w_rows_per_expert + (sg.c_begin / CPR + r) * 32, raw_full + 8 * rs);
@@ -309,12 +303,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
         grb += nraw;
       }
-      PROF_FLUSH(12);
     }
   } else if (warp == 2) {
     // ---------------- activation producer ----------------
     if (lane == 0) {
-      PROF_DECL;
       tma_prefetch_desc(&tm_x);
       if (!p.tiles) grid_dep_wait();
       int gb = 0;
@@ -322,13 +314,12 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       while (ok && next_segment(sg)) {
         for (int c = 0; c < sg.nk; ++c) {
           const int g = gb + c, s = g % XS;
-          { PROF_T0; if (g >= XS && !mbar_wait(x_empty + 8 * s, ((g / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; } PROF_ADD(0); }
+          { if (g >= XS && !mbar_wait(x_empty + 8 * s, ((g / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; } }
           mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
           tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, (sg.c_begin + c) * 64, xrow0 + tok0, x_full + 8 * s);
         }
         gb += sg.nk;
       }
-      PROF_FLUSH(16);
     }
   } else if (warp == 1 || (Cfg::NMMA == 2 && warp == 3)) {
     // ---------------- MMA issuer(s) ----------------
@@ -339,20 +330,15 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const uint64_t db0 = smem_desc_sw128(x_smem);
       bool ok = true;
       int gb = 0, si = 0;
-      PROF_DECL;
-#ifdef B2Q_UMMA_PROF
-      const long long _loop0 = clock64();
-#endif
       while (ok && next_segment(sg)) {
         // the accumulators are reused: wait until the epilogue warps have read the previous segment's
         if (BAL && si > 0) { ok = mbar_wait(accum_empty, (si - 1) & 1, abort_flag, p.status, ST_ACCEMPTY); if (!ok) break; tc_fence_after(); }
 #pragma unroll 1
         for (int c = me; c < sg.nk; c += Cfg::NMMA) {
           const int g = gb + c, s = g % S, xs = g % XS;
-          { PROF_T0; ok = mbar_wait(x_full + 8 * xs, (g / XS) & 1, abort_flag, p.status, ST_XFULL); PROF_ADD(0); }
-          if (ok) { PROF_T0; ok = mbar_wait(a_full + 8 * s, (g / S) & 1, abort_flag, p.status, ST_AFULL); PROF_ADD(1); }
+          { ok = mbar_wait(x_full + 8 * xs, (g / XS) & 1, abort_flag, p.status, ST_XFULL); }
+          if (ok) { ok = mbar_wait(a_full + 8 * s, (g / S) & 1, abort_flag, p.status, ST_AFULL); }
           if (!ok) break;
-          PROF_T0;
           tc_fence_after();
           const uint32_t ta = tmem + Cfg::A_COL0 + 32 * s;
           const uint64_t db = db0 + (uint64_t)(xs * (Cfg::X_BYTES >> 4));
@@ -362,15 +348,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           mma_f16_ts(dacc, ta + 24, db + 6, idesc, 1u);
           tc_commit(ab_empty + 8 * s);
           tc_commit(x_empty + 8 * xs);
-          PROF_ADD(2);
         }
         if (ok) tc_commit(accum_full);
         gb += sg.nk; ++si;
       }
-#ifdef B2Q_UMMA_PROF
-      _pa[3] = clock64() - _loop0;
-      if (me == 0) { PROF_FLUSH(0); }
-#endif
     }
   } else {
     // ---------------- transform, then epilogue (the NG x 4 warps after the control warps) ----------------
@@ -383,18 +364,16 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     const int kblocks = (p.K + 127) >> 7;
     bool ok = true;
     int gb = 0, grb = 0, si = 0, fixn = 0;       // chunks / raw stages / segments / fix-up barrier phases so far
-    PROF_DECL;
-#ifdef B2Q_UMMA_PROF
-    const long long _loop0 = clock64();
-#endif
     while (ok && next_segment(sg)) {
     const int n0 = sg.n0, nk = sg.nk, c_begin = sg.c_begin;
     int nrow = n0 + t; if (nrow >= p.N) nrow = p.N - 1;
     // The scale of a chunk (one per weight row for INT4, one per CTA for block-scaled FP8) comes from global memory,
-    // usually from DRAM (scales are read once per launch): about a thousand cycles.  It is requested four of this
-    // group's chunks ahead and kept as RAW BITS until its chunk is converted: decoding it to fp32 where it is loaded
-    // would make the warp wait for the load right there, on every chunk (measured: 1800 of the 2800 cycles a chunk
-    // cost a transform group).
+    // usually from DRAM (scales are read once per launch): about a thousand cycles.  Scales are requested four to
+    // eight of this group's chunks ahead, four at a time, and nothing touches a requested register before its chunk
+    // is converted: decoding a value to fp32 where it is loaded, or rotating a freshly requested register into the
+    // next variable, makes the warp wait for the load right there, on every chunk (measured: 1800 of the 2900
+    // cycles a chunk cost a transform group).  Hence two sets of four raw values: the set in use, loaded at least
+    // four chunks ago, and the set in flight, which replaces it every fourth chunk.
     auto chunk_scale_raw = [&](int c) -> uint32_t {
       if (c >= nk) return 0u;
       if constexpr (WK == WK_W4N || WK == WK_W4K) {
@@ -414,8 +393,12 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         return __uint_as_float(raw);
       }
     };
-    uint32_t sr0 = chunk_scale_raw(grp), sr1 = chunk_scale_raw(grp + NG), sr2 = chunk_scale_raw(grp + 2 * NG),
-             sr3 = chunk_scale_raw(grp + 3 * NG);
+    uint32_t sq0 = chunk_scale_raw(grp), sq1 = chunk_scale_raw(grp + NG), sq2 = chunk_scale_raw(grp + 2 * NG),
+             sq3 = chunk_scale_raw(grp + 3 * NG);
+    uint32_t sn0 = chunk_scale_raw(grp + 4 * NG), sn1 = chunk_scale_raw(grp + 5 * NG), sn2 = chunk_scale_raw(grp + 6 * NG),
+             sn3 = chunk_scale_raw(grp + 7 * NG);
+    int it4 = 0;                                   // position of the current chunk in its set of four
+    int pend = -1;                                 // MAGIC: operand stage whose tensor-memory stores are still in flight
     // fp16 magic route with bf16 / fp32 scales: the group scale is rounded to fp16, whose normal range starts at
     // 6.1e-5.  Every row of a segment therefore carries its own power of two, taken from the scale of the segment's
     // first group: the row's scales are multiplied by 2^row_e so that this first one lands in [0.5, 1), and the fp32
@@ -423,8 +406,8 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // operand stays exact).  Groups within 2^13 of the first one, either way, are exact; one further above would
     // overflow fp16 and is saturated and reported through the status word (ST_SCALERANGE).
     float row_mul = 1.f, row_post = 1.f;
-    if constexpr ((WK == WK_W4N || WK == WK_W4K) && !BF16 && FAST) {
-      if (p.magic && p.scale_dtype != B2Q_F16) {
+    if constexpr (MAGIC) {
+      if (p.scale_dtype != B2Q_F16) {
         const int ex = (int)((__float_as_uint(scale_value(chunk_scale_raw(0))) >> 23) & 0xFFu);   // biased exponent; 0 = zero / subnormal, 255 = inf / nan
         if (ex != 0 && ex != 255) {
           int k = 126 - ex;
@@ -436,24 +419,64 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
 #pragma unroll 1
     for (int c = grp; c < nk; c += NG) {
-      const uint32_t sr_cur = sr0;
-      sr0 = sr1; sr1 = sr2; sr2 = sr3;
-      sr3 = chunk_scale_raw(c + 4 * NG);
+      if (it4 == 4) {
+        it4 = 0;
+        sq0 = sn0; sq1 = sn1; sq2 = sn2; sq3 = sn3;                       // requested at least four chunks ago
+        sn0 = chunk_scale_raw(c + 4 * NG); sn1 = chunk_scale_raw(c + 5 * NG);
+        sn2 = chunk_scale_raw(c + 6 * NG); sn3 = chunk_scale_raw(c + 7 * NG);
+      }
+      const uint32_t sr_cur = it4 == 0 ? sq0 : (it4 == 1 ? sq1 : (it4 == 2 ? sq2 : sq3));
+      ++it4;
       const int r = c / CPR, j = c % CPR;
       const int gr = grb + r, rs = gr % RS;
-      { PROF_T0; ok = mbar_wait(raw_full + 8 * rs, (gr / RS) & 1, abort_flag, p.status, ST_RAWFULL); PROF_ADD(0); }
+      ok = mbar_wait(raw_full + 8 * rs, (gr / RS) & 1, abort_flag, p.status, ST_RAWFULL);
       if (!ok) break;
-      float sc_cur;
-      { PROF_T0; sc_cur = scale_value(sr_cur); asm volatile("" :: "f"(sc_cur)); PROF_ADD(4); }
+      const float sc_cur = scale_value(sr_cur);
       const uint32_t rawrow = raw_smem + rs * Cfg::RAW_BYTES + t * 128;     // N-major / fp8: this thread's row
       const uint32_t rawcol = raw_smem + rs * Cfg::RAW_BYTES + t * 4;       // K-major: this thread's column
       {
         const int g = gb + c, s = g % S;
-        if (g >= S) { PROF_T0; ok = mbar_wait(ab_empty + 8 * s, ((g / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); PROF_ADD(1); if (!ok) break; }
+        if (g >= S) { ok = mbar_wait(ab_empty + 8 * s, ((g / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); if (!ok) break; }
         tc_fence_after();
         const uint32_t ta = tmem + ((uint32_t)((warp & 3) * 32) << 16) + Cfg::A_COL0 + 32 * s;
+        if constexpr (MAGIC) {
+          // fp16 magic-number route.  The chunk goes to tensor memory in two halves of 32 k (16 registers each): with
+          // all 64 values of a row live at once the loop ran out of registers, and the decode's masks and fp16
+          // constants were re-created for every use.
+          float ss = sc_cur * row_mul;
+          if (fabsf(ss) > 8188.f) {              // 8 * scale would leave fp16: saturate, and say so
+            ss = copysignf(8188.f, ss);
+            atomicCAS(p.status, 0, ST_SCALERANGE);
+          }
+          const uint32_t hv = __half_as_ushort(__float2half_rn(ss));
+          const uint32_t m2 = hv | (hv << 16);
+          const bool twos = p.xor_mask != 0;       // two's-complement nibbles: flip the sign bits into offset form
+          const MagicConsts mk = p.mk;
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {
+            uint32_t w0, w1, w2, w3;
+            if constexpr (WK == WK_W4N) {
+              const uint4 rr = lds128(rawrow + (((2 * j + hf) ^ sw) << 4));
+              w0 = rr.x; w1 = rr.y; w2 = rr.z; w3 = rr.w;
+            } else {
+              w0 = lds32(rawcol + (8 * j + 4 * hf + 0) * 512); w1 = lds32(rawcol + (8 * j + 4 * hf + 1) * 512);
+              w2 = lds32(rawcol + (8 * j + 4 * hf + 2) * 512); w3 = lds32(rawcol + (8 * j + 4 * hf + 3) * 512);
+            }
+            if (twos) { w0 ^= 0x88888888u; w1 ^= 0x88888888u; w2 ^= 0x88888888u; w3 ^= 0x88888888u; }
+            uint32_t a16[16];
+            { uint32_t o[4]; w4_word_magic(w0, m2, mk, o); a16[0] = o[0]; a16[1] = o[1]; a16[2] = o[2]; a16[3] = o[3]; }
+            { uint32_t o[4]; w4_word_magic(w1, m2, mk, o); a16[4] = o[0]; a16[5] = o[1]; a16[6] = o[2]; a16[7] = o[3]; }
+            { uint32_t o[4]; w4_word_magic(w2, m2, mk, o); a16[8] = o[0]; a16[9] = o[1]; a16[10] = o[2]; a16[11] = o[3]; }
+            { uint32_t o[4]; w4_word_magic(w3, m2, mk, o); a16[12] = o[0]; a16[13] = o[1]; a16[14] = o[2]; a16[15] = o[3]; }
+            // The previous chunk's stores have had this half's conversion to complete: only now are they waited for and
+            // the chunk handed to the MMA warp.  Waiting right behind the store would leave the warp idle for the
+            // store's whole latency, once per chunk.
+            if (hf == 0 && pend >= 0) { tmem_st_wait(); tc_fence_before(); mbar_arrive(a_full + 8 * pend); }
+            tmem_st16(ta + 16 * hf, a16);
+          }
+          pend = s;
+        } else {
         uint32_t av[32];                         // this row's 64 values of the chunk, two per register, k ascending
-        PROF_T0;
         if constexpr (WK == WK_W4N || WK == WK_W4K) {
           uint32_t s2 = 0; float sf = 0.f;
           if constexpr (FAST) {
@@ -472,28 +495,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 #pragma unroll
             for (int i = 0; i < 8; ++i) ww[i] = lds32(rawcol + (8 * j + i) * 512);
           }
-          bool done = false;
-          if constexpr (!BF16 && FAST) {
-            if (p.magic) {
-              // fp16 magic-number path: the activation pre-pass stored x in the pair order this produces
-              float ss = sc_cur * row_mul;
-              if (fabsf(ss) > 8188.f) {            // 8 * scale would leave fp16: saturate, and say so
-                ss = copysignf(8188.f, ss);
-                atomicCAS(p.status, 0, ST_SCALERANGE);
-              }
-              const __half hs = __float2half_rn(ss);
-              const uint32_t hv = __half_as_ushort(hs);
-              const uint32_t m2 = hv | (hv << 16);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                uint32_t o[4];
-                w4_word_magic(ww[i], m2, o);
-                av[4 * i] = o[0]; av[4 * i + 1] = o[1]; av[4 * i + 2] = o[2]; av[4 * i + 3] = o[3];
-              }
-              done = true;
-            }
-          }
-          if (!done) {
+          {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
               uint32_t o[4];
@@ -537,15 +539,16 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(a_full + 8 * s);
-        PROF_ADD(2);
+        }
       }
       // release the raw stage once this group's last chunk in it is converted
       if (c + NG >= nk || (c + NG) / CPR != r) mbar_arrive(raw_empty + 8 * rs);
     }
+    if (pend >= 0) { tmem_st_wait(); tc_fence_before(); mbar_arrive(a_full + 8 * pend); pend = -1; }
     if (!ok) break;
 
     // ---------------- epilogue of this segment ----------------
-    { PROF_T0; ok = mbar_wait(accum_full, si & 1, abort_flag, p.status, ST_ACCUM); PROF_ADD(5); }
+    { ok = mbar_wait(accum_full, si & 1, abort_flag, p.status, ST_ACCUM); }
     if (!ok) break;
     tc_fence_after();
     const int quad = warp & 3;                   // tensor-memory lane quadrant this warp may read
@@ -616,7 +619,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(q[i]));
       }
-      if constexpr ((WK == WK_W4N || WK == WK_W4K) && !BF16 && FAST) {
+      if constexpr (MAGIC) {
         if (row_post != 1.f) {
 #pragma unroll
           for (int i = 0; i < CB; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * row_post);
@@ -692,19 +695,11 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
     gb += nk; grb += (nk + CPR - 1) / CPR; ++si;
     }   // segments
-#ifdef B2Q_UMMA_PROF
-    _pa[3] = clock64() - _loop0;
-    if (threadIdx.x == Cfg::CW * 32) { PROF_FLUSH(4); }
-    if (lane == 0) { PROF_FLUSH8(32 + (warp - Cfg::CW) * 8); }
-#endif
   }
 
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem, Cfg::TMEM_COLS); }
-#ifdef B2Q_UMMA_PROF
-  if (threadIdx.x == 0 && blockIdx.y == 7 && blockIdx.x == 0) { g_umma_prof[8] += clock64() - _kt0; g_umma_prof[9] += 1; }
-#endif
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -810,14 +805,6 @@ int umma_read_status(int* out) {
   return w4i_read_status(out);
 }
 
-#ifdef B2Q_UMMA_PROF
-extern "C" __attribute__((visibility("default"))) int b2q_debug_prof(long long* out, int reset) {
-  cudaDeviceSynchronize();
-  if (out && cudaMemcpyFromSymbol(out, g_umma_prof, sizeof(long long) * 128) != cudaSuccess) return -1;
-  if (reset) { long long z[128] = {0}; cudaMemcpyToSymbol(g_umma_prof, z, sizeof(z)); }
-  return 0;
-}
-#endif
 
 // ---- balanced mode (decode shapes) ----------------------------------------------------------------
 // Arrival counters of cut strips.  They are zero whenever no launch is in flight (the last arriver of a
@@ -880,12 +867,12 @@ static int plan_balanced(UmmaWoParams& p, const UmmaGroupArgs& a, int M, int N, 
 
 static int pick_tok(int m) { return m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256))); }
 
-template <int WK, bool BF16, int TOK, bool FAST>
+template <int WK, bool BF16, int TOK, bool FAST, bool MAGIC>
 static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWoParams& p_in, int token_tiles, cudaStream_t st) {
   UmmaWoParams p = p_in;
   p.tiles_on_y = (p.tiles && token_tiles <= 65535) ? 1 : 0;      // gridDim.y is limited to 65535
   using Cfg = UmmaCfg<TOK>;
-  auto kern = umma_wo_kernel<WK, BF16, TOK, FAST>;
+  auto kern = umma_wo_kernel<WK, BF16, TOK, FAST, MAGIC>;
   static thread_local bool configured[16] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -902,14 +889,14 @@ static int launch_one(const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWo
   return launch_status();
 }
 
-template <int WK, bool BF16, bool FAST>
+template <int WK, bool BF16, bool FAST, bool MAGIC = false>
 static int launch_tok(int tok, const CUtensorMap& tw, const CUtensorMap& tx, const UmmaWoParams& p, int tiles, cudaStream_t st) {
   switch (tok) {
-    case 16: return launch_one<WK, BF16, 16, FAST>(tw, tx, p, tiles, st);
-    case 32: return launch_one<WK, BF16, 32, FAST>(tw, tx, p, tiles, st);
-    case 64: return launch_one<WK, BF16, 64, FAST>(tw, tx, p, tiles, st);
-    case 128: return launch_one<WK, BF16, 128, FAST>(tw, tx, p, tiles, st);
-    default: return launch_one<WK, BF16, 256, FAST>(tw, tx, p, tiles, st);
+    case 16: return launch_one<WK, BF16, 16, FAST, MAGIC>(tw, tx, p, tiles, st);
+    case 32: return launch_one<WK, BF16, 32, FAST, MAGIC>(tw, tx, p, tiles, st);
+    case 64: return launch_one<WK, BF16, 64, FAST, MAGIC>(tw, tx, p, tiles, st);
+    case 128: return launch_one<WK, BF16, 128, FAST, MAGIC>(tw, tx, p, tiles, st);
+    default: return launch_one<WK, BF16, 256, FAST, MAGIC>(tw, tx, p, tiles, st);
   }
 }
 
@@ -962,6 +949,7 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.tiles = grouped ? a.tiles : nullptr; p.expert_offsets = a.expert_offsets; p.out_map = a.out_map;
   p.w_rows_per_expert = kmajor ? a.K / 8 : a.N;
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0; p.magic = a.magic ? 1 : 0;
+  p.mk = magic_consts();
   p.status = status_ptr();
   p.overlap_ok = (a.after_prep || tls().overlap_mode == 2) ? 1 : 0;
   p.sk_grid = plan_balanced(p, a, a.M, a.N, a.K, 4, tok);
@@ -971,6 +959,11 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   }
   const bool fast = a.magic || (a.scale_dtype == (a.bf16 ? B2Q_BF16 : B2Q_F16));
   const int tiles = grouped ? a.tile_cap : (a.M + tok - 1) / tok;
+  if (a.magic) {
+    if (a.bf16) return B2Q_ERR_UNSUPPORTED;       // the pre-pass always hands over fp16
+    return kmajor ? launch_tok<WK_W4K, false, true, true>(tok, tw, tx, p, tiles, st)
+                  : launch_tok<WK_W4N, false, true, true>(tok, tw, tx, p, tiles, st);
+  }
   return kmajor ? launch_wk<WK_W4K>(a.bf16, fast, tok, tw, tx, p, tiles, st)
                 : launch_wk<WK_W4N>(a.bf16, fast, tok, tw, tx, p, tiles, st);
 }

@@ -33,18 +33,6 @@ namespace b2q {
 using namespace sm100;
 
 __device__ int g_w4i_status = 0;
-#ifdef B2Q_W4I_PROF
-__device__ long long g_w4i_prof[32];
-#define WP_DECL long long _wp[6] = {0, 0, 0, 0, 0, 0}; const long long _wl0 = clock64()
-#define WP_T0 const long long _wt = clock64()
-#define WP_ADD(i) _wp[i] += clock64() - _wt
-#define WP_FLUSH(base) if (blockIdx.x == 5) { _wp[5] = clock64() - _wl0; for (int _i = 0; _i < 6; ++_i) g_w4i_prof[(base) + _i] = _wp[_i]; }
-#else
-#define WP_DECL
-#define WP_T0
-#define WP_ADD(i)
-#define WP_FLUSH(base)
-#endif
 constexpr int W4I_BANKS = 64, W4I_MAX_STRIPS = 2048;
 __device__ int g_w4i_counters[W4I_BANKS * W4I_MAX_STRIPS];
 
@@ -180,16 +168,14 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       constexpr uint32_t idesc = instr_desc_i8(0u, 1u, 128, NTOK);       // u8 weights x s8 activations -> s32
       int gc = 0;
       bool ok = true;
-      WP_DECL;
       while (ok && next_segment(sg)) {
 #pragma unroll 1
         for (int g = sg.g_begin; g < sg.g_end; ++g, ++gc) {
           const int sa = gc % SA, xs = gc % XS, nb = gc % NB;
-          { WP_T0; ok = mbar_wait(x_full + 8 * xs, (gc / XS) & 1, abort_flag, p.status, ST_XFULL); WP_ADD(0); }
-          if (ok) { WP_T0; ok = mbar_wait(a_full + 8 * sa, (gc / SA) & 1, abort_flag, p.status, ST_AFULL); WP_ADD(1); }
-          if (ok && gc >= NB) { WP_T0; ok = mbar_wait(acc_empty + 8 * nb, ((gc / NB) - 1) & 1, abort_flag, p.status, ST_ACCEMPTY); WP_ADD(2); }
+          { ok = mbar_wait(x_full + 8 * xs, (gc / XS) & 1, abort_flag, p.status, ST_XFULL); }
+          if (ok) { ok = mbar_wait(a_full + 8 * sa, (gc / SA) & 1, abort_flag, p.status, ST_AFULL); }
+          if (ok && gc >= NB) { ok = mbar_wait(acc_empty + 8 * nb, ((gc / NB) - 1) & 1, abort_flag, p.status, ST_ACCEMPTY); }
           if (!ok) break;
-          WP_T0;
           tc_fence_after();
           const uint32_t d = tmem + C::ACC0 + nb * NTOK, ta = tmem + sa * 32;
           const uint64_t db = smem_desc_sw128(x_smem + xs * C::X_BYTES);
@@ -200,10 +186,8 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tc_commit(a_empty + 8 * sa);
           tc_commit(x_empty + 8 * xs);
           tc_commit(acc_full + 8 * nb);
-          WP_ADD(3);
         }
       }
-      WP_FLUSH(0);
     }
   } else if (warp >= 8) {
     // ---- transform: two teams of four warps on alternate groups; a thread owns one weight row ----
@@ -213,7 +197,6 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     const uint32_t trow = tmem + ((uint32_t)((warp & 3) * 32) << 16);
     int gc = 0, gr = 0;
     bool ok = true;
-    WP_DECL;
     while (ok && next_segment(sg)) {
       const int ng = sg.g_end - sg.g_begin;
 #pragma unroll 1
@@ -221,11 +204,10 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         const int c = gc + j, r = gr + (j >> 1), rs = r % RS;
         const bool mine = (j & 1) == team;
         if (mine) {
-          { WP_T0; ok = mbar_wait(raw_full + 8 * rs, (r / RS) & 1, abort_flag, p.status, ST_RAWFULL); WP_ADD(0); }
+          { ok = mbar_wait(raw_full + 8 * rs, (r / RS) & 1, abort_flag, p.status, ST_RAWFULL); }
           if (!ok) break;
           const int sa = c % SA;
-          if (c >= SA) { WP_T0; ok = mbar_wait(a_empty + 8 * sa, ((c / SA) - 1) & 1, abort_flag, p.status, ST_AEMPTY); WP_ADD(1); if (!ok) break; }
-          WP_T0;
+          if (c >= SA) { ok = mbar_wait(a_empty + 8 * sa, ((c / SA) - 1) & 1, abort_flag, p.status, ST_AEMPTY); if (!ok) break; }
           tc_fence_after();
           const uint32_t rawrow = raw_smem + rs * C::RAW_BYTES + t * 128;
 #pragma unroll
@@ -247,7 +229,6 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tc_fence_before();
           mbar_arrive(a_full + 8 * sa);
           mbar_arrive(raw_empty + 8 * rs);      // a raw stage holds two groups, one per team
-          WP_ADD(2);
         }
       }
       if (!ok) break;
@@ -256,7 +237,6 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
       if ((ng & 1) && team == 1) mbar_arrive(raw_empty + 8 * ((gr + (ng >> 1)) % RS));
       gc += ng; gr += (ng + 1) >> 1;
     }
-    if (threadIdx.x == 8 * 32) { WP_FLUSH(8); }
   } else if (warp >= 4) {
     // ---- promotion + epilogue: warps 4..7, lane quadrant = warp & 3; a thread owns one weight row ----
     constexpr int MPMAX = NTOK <= 32 ? 8 : 16;        // tokens (rounded up to 8) a launch of this width can carry
@@ -265,7 +245,6 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
     uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
     int gc = 0, fixn = 0;
     bool ok = true;
-    WP_DECL;
     grid_dep_wait();                                   // reads what the pre-pass wrote (activation sums, token scales)
     while (ok && next_segment(sg)) {
       const int n = sg.n0 + rowi;
@@ -309,9 +288,8 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
                 xv[mb * 8 + 4] = x1.x; xv[mb * 8 + 5] = x1.y; xv[mb * 8 + 6] = x1.z; xv[mb * 8 + 7] = x1.w;
               }
             }
-            { WP_T0; ok = mbar_wait(acc_full + 8 * nb, (gc / NB) & 1, abort_flag, p.status, ST_ACCFULL); WP_ADD(0); }
+            { ok = mbar_wait(acc_full + 8 * nb, (gc / NB) & 1, abort_flag, p.status, ST_ACCFULL); }
             if (ok) {
-              WP_T0;
               tc_fence_after();
               const float scj = scalar_from_raw(sc_raw[j], p.scale_dtype);
 #pragma unroll
@@ -332,7 +310,6 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
               }
               tc_fence_before();
               mbar_arrive(acc_empty + 8 * nb);
-              WP_ADD(1);
               ++gc;
             }
           }
@@ -389,7 +366,6 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
         }
       }
     }
-    if (threadIdx.x == 4 * 32) { WP_FLUSH(16); }
   }
   tc_fence_before();
   __syncthreads();
@@ -493,12 +469,6 @@ int umma_w4_i8_linear(const UmmaW4I8Args& a, cudaStream_t st) {
   return ntok == 32 ? launch_w4i<32>(tw, tx, p, grid, overlap, st) : launch_w4i<64>(tw, tx, p, grid, overlap, st);
 }
 
-#ifdef B2Q_W4I_PROF
-extern "C" __attribute__((visibility("default"))) int b2q_debug_prof_w4i(long long* out) {
-  cudaDeviceSynchronize();
-  return cudaMemcpyFromSymbol(out, g_w4i_prof, sizeof(long long) * 32) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 int w4i_reset_state() {
   void* p = nullptr;

@@ -219,6 +219,30 @@ def linear_fp8(input, weight, weight_scale, output, scale_mode, N=None, K=None):
     return output
 
 
+def resadd_norm_linear_fp8(hidden_states, residual, norm_weight, normed_out, eps, scalar, weight, weight_scale, output,
+                           scale_mode):
+    """residual <- (hidden + residual) * scalar; normed_out <- rmsnorm(residual) * norm_weight; output <- normed_out @ W^T
+    (b2q_resadd_norm_linear_fp8: on the decode path the norm runs inside the GEMV's activation pre-pass)."""
+    L.require_cuda(hidden_states, residual, norm_weight, normed_out, weight, weight_scale, output)
+    _chk(hidden_states.dim() == 2 and hidden_states.dtype in (torch.bfloat16, torch.float16), "hidden_states must be 2-D bf16 / fp16")
+    M, K = hidden_states.shape
+    for t, what in ((hidden_states, "hidden_states"), (residual, "residual"), (normed_out, "normed_out")):
+        _chk(t.dtype == hidden_states.dtype and tuple(t.shape) == (M, K) and t.is_contiguous(), what + " must be a contiguous [M, K] tensor of the activation type")
+    _chk(norm_weight.dtype == hidden_states.dtype and norm_weight.numel() == K and norm_weight.is_contiguous(), "norm_weight must be a contiguous [K] tensor")
+    _chk(weight.dim() == 2 and weight.is_contiguous() and weight.shape[1] == K, "fp8 weight must be a contiguous [N, K] tensor")
+    N = weight.shape[0]
+    _chk(tuple(output.shape) == (M, N) and output.dtype == hidden_states.dtype and output.stride(1) == 1, "output must be [M, N] of the activation type")
+    with L.on_device(hidden_states):
+        wsb = L.lib.b2q_linear_fp8_workspace_bytes(M, N, K)
+        ws = torch.empty(wsb, dtype=torch.uint8, device=hidden_states.device)
+        L.check(L.lib.b2q_resadd_norm_linear_fp8(hidden_states.data_ptr(), residual.data_ptr(), norm_weight.data_ptr(),
+                                                  normed_out.data_ptr(), float(eps), float(scalar), L.dt(hidden_states),
+                                                  weight.data_ptr(), L.fp8_fmt(weight), weight_scale.data_ptr(), L.dt(weight_scale),
+                                                  scale_mode, output.data_ptr(), output.stride(0) if M > 1 else N, M, N, K,
+                                                  L.ptr(ws), wsb, L.stream(hidden_states)))
+    return output
+
+
 def dequant_fp8(weight, weight_scale, scale_mode, out_dtype=torch.float32):
     L.require_cuda(weight, weight_scale)
     N, K = weight.shape

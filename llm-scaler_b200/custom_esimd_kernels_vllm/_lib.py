@@ -36,6 +36,8 @@ _SIGS = {
     "b2q_linear_int4": (i32, [vp, i32, i64, vp, i32, vp, i32, i64, i64, vp, i64, i64, i64, i64, i32, vp, sz, vp]),
     "b2q_linear_fp8_workspace_bytes": (sz, [i64, i64, i64]),
     "b2q_linear_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, i32, vp, i64, i64, i64, i64, vp, sz, vp]),
+    "b2q_resadd_norm_linear_fp8": (i32, [vp, vp, vp, vp, C.c_float, C.c_float, i32, vp, i32, vp, i32, i32, vp, i64, i64, i64,
+                                         i64, vp, sz, vp]),
     "b2q_act_quant_fp8_1x128": (i32, [vp, i32, i64, vp, vp, i64, i64, vp]),
     "b2q_gemm_fp8_block_w8a8": (i32, [vp, vp, vp, vp, vp, i32, i64, i64, i64, i64, vp]),
     "b2q_moe_topk": (i32, [vp, i32, i64, i32, i32, i32, vp, i32, vp, vp]),

@@ -187,10 +187,12 @@ _op(NS, "esimd_moe_scatter_fused(Tensor hidden_states, Tensor top_values, Tensor
         "Tensor scattered_hidden, Tensor scattered_weights, Tensor topk_ids, Tensor expert_start, Tensor max_tokens_out, "
         "int K, int topk, int T, int num_experts) -> Tensor", _moe_scatter_fused)
 # residual add + RMSNorm + decode GEMV (reference: ops.py:411-489; kernels esimd_kernels/resadd_norm_gemv_int4.h,
-# norm_gemv_fused.h).  Here: one norm kernel, then the ordinary GEMV on normed_out; the kernels overlap on the stream.
+# norm_gemv_fused.h).  FP8 with one GEMV: the norm runs inside the GEMV's activation pre-pass (two launches in all).
+# INT4 and the two-GEMV form: one norm kernel, then the ordinary GEMV(s) on normed_out; the kernels overlap on the stream.
 def _resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps):
-    I.resadd_rmsnorm(hidden_states, residual, norm_weight, normed_out, eps)
-    return I.linear_fp8(normed_out, gemv_weight, gemv_scale, output, L.SCALE_TENSOR)
+    _chk_scale = I._chk(gemv_scale.numel() == 1 and gemv_scale.dtype == torch.float32, "per-tensor scale must be one fp32")
+    return I.resadd_norm_linear_fp8(hidden_states, residual, norm_weight, normed_out, eps, 1.0, gemv_weight, gemv_scale,
+                                    output, L.SCALE_TENSOR)
 
 
 def _resadd_norm_gemv_int4_pert(hidden_states, residual, norm_weight, gemv_weight, gemv_scale, output, normed_out, eps):
@@ -208,8 +210,8 @@ def _resadd_norm_gemv2_fp8_pert(hidden_states, residual, norm_weight, w0, s0, o0
 
 def _scaled_resadd_norm_gemv_fp8_pert(hidden_states, residual, norm_weight, qkv_weight, qkv_scale, qkv_out, eps, scalar):
     normed = torch.empty_like(residual)
-    I.rmsnorm_fused(hidden_states, residual, scalar, norm_weight, normed, None, None, eps)
-    I.linear_fp8(normed, qkv_weight, qkv_scale, qkv_out, L.SCALE_TENSOR)
+    I.resadd_norm_linear_fp8(hidden_states, residual, norm_weight, normed, eps, scalar, qkv_weight, qkv_scale, qkv_out,
+                             L.SCALE_TENSOR)
 
 
 def _norm_gemv_norm_fp16(residual, scale_with_root, proj_w, pre_ff_w, router_logits, moe_input, eps):

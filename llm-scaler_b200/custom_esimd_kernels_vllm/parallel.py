@@ -111,6 +111,48 @@ def tp_layer_forward(x: torch.Tensor, layer: TPLayer, backend, group=None, reduc
     return row_linear(act, *layer.down) if row_linear else reduce(backend.linear_int4(act, *layer.down), group)
 
 
+def _any_nan_globally(t: torch.Tensor, group) -> bool:
+    """True on every rank when any rank's tensor holds a NaN (one scalar MAX all-reduce)."""
+    flag = torch.isnan(t).any().to(torch.int32).reshape(1)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
+    return bool(flag.item())
+
+
+def guarded_all_reduce(t: torch.Tensor, group=None, max_retries: int = 3, collective=None, stats=None) -> torch.Tensor:
+    """All-reduce (sum) with the reference's repair for a collective that returns NaN from finite input
+    (vllm/patches/vllm_for_multi_arc.patch:1568-1666): keep a copy of the input; after the collective every rank
+    learns through one scalar MAX all-reduce whether ANY rank sees a NaN (all ranks must take the same branch);
+    while one does, restore the input and repeat the collective, at most max_retries times; if the NaN is still
+    there, restore once more and replace the collective by an all-gather followed by a local sum in rank order
+    (:1540-1556).  Off the hot path by design: it costs a clone, a NaN scan and a host round trip per call, so it
+    is never the default reduce of tp_layer_forward.  `collective(t, group)` is the in-place sum being guarded
+    (default dist.all_reduce); `stats`, if given, receives retries / fallback_used / nan_left."""
+    collective = collective or (lambda x, g: dist.all_reduce(x, op=dist.ReduceOp.SUM, group=g))
+    if not (dist.is_initialized() and dist.get_world_size(group) > 1) or not t.is_floating_point() or t.numel() == 0:
+        return all_reduce(t, group)
+    saved = t.clone()
+    collective(t, group)
+    bad = _any_nan_globally(t, group)
+    retries, fallback = 0, False
+    while bad and retries < max_retries:
+        retries += 1
+        t.copy_(saved)
+        collective(t, group)
+        bad = _any_nan_globally(t, group)
+    if bad:
+        t.copy_(saved)
+        parts = [torch.empty_like(t) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(parts, t, group=group)
+        t.copy_(parts[0])
+        for other in parts[1:]:
+            t.add_(other)
+        fallback = True
+        bad = _any_nan_globally(t, group)
+    if stats is not None:
+        stats.update(retries=retries, fallback_used=fallback, nan_left=bad)
+    return t
+
+
 class NcclReducer:
     """Sum of row-parallel partial results through the process group's all-reduce (NCCL over NVLink on GPUs)."""
 

@@ -72,6 +72,22 @@ def _worker(rank, world, port, what, q):
                               down=P.shard_row(*packed["down"], rank, world))
             out = P.tp_layer_forward(full["x"], layer, be)
             q.put((rank, _pack(out)))
+        elif what.startswith("guard"):
+            # a collective that returns NaN from finite input, as the reference's repair path assumes: rank 1's
+            # first `fail` calls (all of them for "guard_fallback") poison the result
+            fail = {"guard_once": 1, "guard_fallback": 10 ** 6, "guard_clean": 0}[what]
+            calls = {"n": 0}
+
+            def flaky(t, g):
+                dist.all_reduce(t, op=dist.ReduceOp.SUM, group=g)
+                calls["n"] += 1
+                if rank == 1 and calls["n"] <= fail:
+                    t[0, 0] = float("nan")
+            x = torch.full((4, 8), float(rank + 1)).to(torch.bfloat16)
+            stats = {}
+            out = P.guarded_all_reduce(x, collective=flaky, stats=stats)
+            q.put((rank, _pack(out), stats, calls["n"]))
+            return
         else:
             c = configs.c4(seed=5, T=24, E=8, top_k=2, H=128, I=128)
             T = c["x"].shape[0] // world
@@ -106,7 +122,10 @@ def _run(what):
     for p in procs:
         p.start()
     try:
-        outs = {r: _unpack(a) for r, a in (q.get(timeout=120) for _ in range(world))}
+        outs = {}
+        for _ in range(world):
+            item = q.get(timeout=120)
+            outs[item[0]] = _unpack(item[1]) if len(item) == 2 else (_unpack(item[1]),) + tuple(item[2:])
         for p in procs:
             p.join(timeout=60)
             assert p.exitcode == 0
@@ -152,3 +171,16 @@ def test_shard_helpers():
     assert w0[:, 0].tolist() == [w[r, 0].item() for r in (4, 5, 6, 7, 12, 13, 14, 15)]
     w1, s1 = P.shard_row(w, s, 1, 2)
     assert w1.shape == (16, 32) and s1.shape == (16, 2) and w1[0, 0] == w[0, 32] and s1[0, 0] == s[0, 2]
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("what,retries,fallback", [("guard_clean", 0, False), ("guard_once", 1, False), ("guard_fallback", 3, True)])
+def test_guarded_all_reduce_repairs_a_nan(lib_built, what, retries, fallback):
+    """One rank's collective returns a NaN: every rank learns of it, all repeat the collective, and when the NaN
+    persists the all-gather + local sum takes over; both ranks end with the same finite sum and took the same path."""
+    outs = _run(what)
+    for r in (0, 1):
+        out, stats, n_calls = outs[r]
+        assert torch.equal(out, torch.full((4, 8), 3.0).to(torch.bfloat16)), (r, out)
+        assert stats == {"retries": retries, "fallback_used": fallback, "nan_left": False}
+        assert n_calls == 1 + retries

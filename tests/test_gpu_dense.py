@@ -295,8 +295,13 @@ def test_resadd_norm_gemv_fused_ops(e, N, K, dtype):
     w2 = torch.randn(2 * N, K, generator=g) * 0.05
     wq2, ws2 = fp8.quantize_tensor(w2)
     res_d = residual.to(DEV).clone()
-    e.esimd_resadd_norm_gemv_fp8_pert(hidden.to(DEV), res_d, nw.to(DEV), wq.to(DEV), ws.to(DEV), out, normed_d, 1e-6)
+    normed_d.zero_()
+    hd, nwd, wqd, wsd = hidden.to(DEV), nw.to(DEV), wq.to(DEV), ws.to(DEV)
+    before = e.launch_count()
+    e.esimd_resadd_norm_gemv_fp8_pert(hd, res_d, nwd, wqd, wsd, out, normed_d, 1e-6)
+    assert e.launch_count() - before == 2, "the norm must run inside the GEMV's activation pre-pass: two launches in all"
     assert torch.equal(res_d.cpu(), ref_res)
+    assert_close(normed_d, ref_normed, what="normed_out of the fused pre-pass", tol=4e-3)
     assert_close(out, fp8.linear_tensor(normed_d.cpu(), wq, ws), what="resadd+norm+fp8 gemv")
     res_d = residual.to(DEV).clone()
     o1 = torch.empty(1, 2 * N, dtype=dtype, device=DEV)
