@@ -127,15 +127,20 @@ def tp_case(M, rank, world, dev, P, be):
         us = measure(stack, reducer.reduce, world, getattr(reducer, "row_linear", None))
         us_nosum = measure(stack, lambda t, group=None: t, world)
         if isinstance(reducer, P.PeerReducer):
-            # for comparison: the same sharded kernels with the process group's all-reduce, and with this library's
-            # reduction kernel run after the GEMM instead of being fed by its epilogue
+            # for comparison: the same sharded kernels with the process group's all-reduce, and with the two-step form
+            # of this library's reduction fed by the GEMM epilogue (the default form for up to four ranks is one step
+            # over the links, run behind the GEMM)
             rec["us_per_layer_nccl_all_reduce"] = round(measure(stack, P.NcclReducer().reduce, world), 1)
-            rec["us_per_layer_unfused_peer_reduce"] = round(measure(stack, reducer.reduce, world), 1)
-            rec["reduction_status"] = reducer.status()
+            two = P.make_reducer(M, HID, torch.bfloat16, dev, kind="peer", mode=2)
+            rec["us_per_layer_two_step_fed_by_gemm_epilogue"] = round(measure(stack, two.reduce, world, two.row_linear), 1)
+            rec["reduction_status"] = max(reducer.status(), two.status())
+            two.close()
         rec.update(us_per_layer=round(us, 1), exchange_us_per_layer=round(max(0.0, us - us_nosum), 1),
                    exchange="sum of the [M, 8192] partial results after o_proj and down: " + reducer.describe(),
                    all_reduce_bytes_per_layer=2 * M * HID * 2, speedup_vs_one_gpu=round(us1 / us, 2),
                    efficiency=round(us1 / us / world, 3))
+        if hasattr(reducer, "close"):
+            reducer.close()
     else:
         us = us1
         rec["us_per_layer"] = round(us, 1)

@@ -328,8 +328,19 @@ B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
  * communicator must then be re-created on all ranks).  *out receives the DEVICE address of the [M, N]
  * result inside this rank's buffer (row pitch N); it stays valid until the next call but one.
  * All ranks must call with the same M, N, dtype, in the same order.  N % (8 * world) == 0, N / world <=
- * 65536, M <= max_rows <= 4096.  No multicast, no library collective, no allocation per call.        */
+ * 65536, M <= max_rows <= 4096.  No multicast, no library collective, no allocation per call.
+ * Two forms of the same sum, chosen when the communicator is made (the same on all ranks):
+ *   B2Q_COMM_TWO_STEPS  the form described above: bytes per rank independent of world
+ *   B2Q_COMM_ONE_STEP   every rank stores its whole tile into every rank's buffer and every rank adds the world
+ *                       tiles itself (rank order, fp32): one trip over the links instead of two, world - 1 times
+ *                       the bytes; needs N <= 65536
+ *   B2Q_COMM_AUTO       one step for world <= 4 and max_rows <= 256 (decode tiles), two steps otherwise;
+ *                       b2q_comm_create uses this                                                        */
+#define B2Q_COMM_AUTO 0
+#define B2Q_COMM_ONE_STEP 1
+#define B2Q_COMM_TWO_STEPS 2
 B2Q_API int b2q_comm_create(int rank, int world, int64_t max_rows, int64_t max_cols, void** comm, void* ipc_handle_out);
+B2Q_API int b2q_comm_create_mode(int rank, int world, int64_t max_rows, int64_t max_cols, int mode, void** comm, void* ipc_handle_out);
 B2Q_API int b2q_comm_connect(void* comm, const void* all_ipc_handles /* world x 64 bytes */);
 B2Q_API int b2q_comm_destroy(void* comm);
 B2Q_API int b2q_comm_status(void* comm, int* out);

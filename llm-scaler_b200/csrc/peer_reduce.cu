@@ -4,12 +4,21 @@
 // reference calls the framework's all-reduce).
 //
 // Every rank owns a buffer that all ranks of the box can address (cudaMalloc + CUDA IPC between the processes of
-// one box).  The sum runs in two steps over plain peer stores and loads; no multicast, no library collective:
+// one box).  The sum runs over plain peer stores and loads; no multicast, no library collective.  Two forms:
+//
+// two steps (reduce-scatter, then broadcast; the traffic per rank does not grow with W):
 //   1. rank r writes columns [j * N/W, (j + 1) * N/W) of its partial tile into slot r of rank j's buffer, for every
 //      j, then raises flag1[r][block] on rank j                       (the GEMM epilogue can do this step itself)
 //   2. rank j waits for the W flags of a column block, adds the W slots in rank order in fp32 (every rank therefore
 //      computes bit-identical sums), rounds once, writes the block into the result area of EVERY rank, raises
 //      flag2[j][block] there, and waits for the W flags of its own result.
+// one step (W <= 4 and decode-sized tiles, where the time is latency, not bytes: one trip over NVLink instead of two):
+//   1. rank r writes its WHOLE partial tile into slot r of every rank's buffer and raises flag1[r][block] there
+//   2. every rank waits for the W flags of a column block and adds the W slots in rank order in fp32 into its own
+//      result area: all ranks add the same values in the same order, so the results are bit-identical here too.
+//   Nothing tells a writer that its slot has been read, so the slots exist twice and calls alternate between the
+//   sets: a rank can only be two calls ahead of a peer after that peer has raised its flags for the call in
+//   between, i.e. after the peer's kernel of the call before that one has finished.
 // A column block is 128 columns wide and belongs to one CTA; CTA b of rank j depends only on CTA b (or the GEMM
 // CTAs that own those columns) of the other ranks, never on another CTA of its own GPU.
 // Flags carry an epoch that the buffer's owner advances once per call, so nothing is cleared between calls.
@@ -25,6 +34,7 @@ namespace b2q {
 struct PeerComm {
   int rank, world, device;
   bool emulated;              // all ranks live in this process on one device (tests)
+  bool oneshot;               // one-step form: full-width slots, two slot sets
   size_t bytes, slot_bytes, out_bytes;
   uint8_t* local;
   uint8_t* peers[PR_MAX_WORLD];
@@ -40,7 +50,7 @@ struct PeerRankArgs {
 };
 struct PeerReduceParams {
   PeerRankArgs r[PR_MAX_WORLD];        // r[0] only, except in the one-device emulation
-  int world, M, N, slice, nblocks, bf16, out_sel;
+  int world, M, N, slice, nblocks, bf16, out_sel, oneshot;
   size_t slot_off, slot_bytes, out_off, out_bytes;
   long long limit_ticks;
 };
@@ -51,10 +61,8 @@ __device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t epoch, 
   const long long t0 = clock64();
   for (;;) {
 #pragma unroll 1
-    for (int i = 0; i < 64; ++i) {
+    for (int i = 0; i < 256; ++i)          // the flag lives in this GPU's own memory (peers write it): polling is a local load
       if ((int32_t)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-      __nanosleep(64);
-    }
     if (clock64() - t0 > limit) {
       atomicCAS(&ctrl->status, 0, code);
       return false;
@@ -99,7 +107,7 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const PeerReduceParams
   PeerCtrl* ctrl = reinterpret_cast<PeerCtrl*>(ra.bufs[me]);
   const uint32_t epoch = ctrl->epoch + 1;      // stable for the whole call: only the last CTA to finish advances it
   const int c0 = b * PR_CB;
-  const int cw = min(PR_CB, p.slice - c0);      // columns of this block (multiple of 8)
+  const int cw = min(PR_CB, (p.oneshot ? p.N : p.slice) - c0);      // columns of this block (multiple of 8)
   const int vpr = cw >> 3;                      // 16-byte vectors per row
   const int nvec = p.M * vpr;
   // slot layout: [source rank][block][row][128 columns]; result layout: [row][N]
@@ -111,17 +119,19 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const PeerReduceParams
     for (int jj = 0; jj < W; ++jj) {
       const int j = (me + 1 + jj) % W;            // start with the neighbour: spreads the links
       uint8_t* dst = ra.bufs[j] + p.slot_off + (size_t)me * p.slot_bytes + blk_off;
-      const uint16_t* src = reinterpret_cast<const uint16_t*>(ra.in) + (size_t)j * p.slice + c0;
+      const uint16_t* src = reinterpret_cast<const uint16_t*>(ra.in) + (p.oneshot ? 0 : (size_t)j * p.slice) + c0;
       for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
         const int m = v / vpr, c8 = v - m * vpr;
         const uint4 val = *reinterpret_cast<const uint4*>(src + (size_t)m * ra.ldi + c8 * 8);
         *reinterpret_cast<uint4*>(dst + ((size_t)m * PR_CB + c8 * 8) * 2) = val;
       }
     }
-    __threadfence_system();
+    // one system-scope release per flag covers the whole CTA's stores: the barrier orders them before it
     __syncthreads();
-    if (threadIdx.x < W)
+    if (threadIdx.x < W) {
+      __threadfence_system();
       st_release_sys(&reinterpret_cast<PeerCtrl*>(ra.bufs[threadIdx.x])->flag1[me][b], epoch);
+    }
   }
 
   // ---- step 2: wait for the W partial blocks, add them in rank order, publish the sum to every rank ----
@@ -140,18 +150,23 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const PeerReduceParams
       for (int r = 0; r < W; ++r)
         add8<BF16>(acc, __ldcg(reinterpret_cast<const uint4*>(slots + (size_t)r * p.slot_bytes + ((size_t)m * PR_CB + c8 * 8) * 2)));   // past L1: peers wrote it
       const uint4 o = pack8<BF16>(acc);
+      if (p.oneshot) {
+        *reinterpret_cast<uint4*>(ra.bufs[me] + out_base + ((size_t)m * p.N + c0 + c8 * 8) * 2) = o;
+        continue;
+      }
       const size_t off = out_base + ((size_t)m * p.N + (size_t)me * p.slice + c0 + c8 * 8) * 2;
       for (int jj = 0; jj < W; ++jj) {
         const int j = (me + jj) % W;
         *reinterpret_cast<uint4*>(ra.bufs[j] + off) = o;
       }
     }
-    __threadfence_system();
     __syncthreads();
-    if (threadIdx.x < W)
+    if (!p.oneshot && threadIdx.x < W) {
+      __threadfence_system();
       st_release_sys(&reinterpret_cast<PeerCtrl*>(ra.bufs[threadIdx.x])->flag2[me][b], epoch);
+    }
     // ---- step 3: the same block of every other owner has landed here ----
-    if (threadIdx.x < W && !wait_flag(&ctrl->flag2[threadIdx.x][b], epoch, p.limit_ticks, ctrl, PST_FLAG2)) s_ok = 0;
+    if (!p.oneshot && threadIdx.x < W && !wait_flag(&ctrl->flag2[threadIdx.x][b], epoch, p.limit_ticks, ctrl, PST_FLAG2)) s_ok = 0;
     __syncthreads();
   }
   // the last CTA of this rank to finish closes the call (also after an expired wait: the next call starts clean)
@@ -166,13 +181,15 @@ __global__ void __launch_bounds__(256) peer_reduce_kernel(const PeerReduceParams
   }
 }
 
-static size_t layout_bytes(int world, int64_t max_rows, int64_t max_cols, size_t* slot_bytes, size_t* out_bytes) {
-  const int64_t slice = max_cols / world;
-  const int64_t nblocks = (slice + PR_CB - 1) / PR_CB;
+// buffer: control area | slot sets (one, or two in the one-step form) of W slots | two result areas
+static size_t layout_bytes(int world, bool oneshot, int64_t max_rows, int64_t max_cols, size_t* slot_bytes, size_t* out_bytes) {
+  const int64_t width = oneshot ? max_cols : max_cols / world;
+  const int64_t nblocks = (width + PR_CB - 1) / PR_CB;
   *slot_bytes = (size_t)nblocks * (size_t)max_rows * PR_CB * 2;
   *out_bytes = ((size_t)max_rows * (size_t)max_cols * 2 + 255) / 256 * 256;
-  return (size_t)PR_CTRL_BYTES + (size_t)world * *slot_bytes + 2 * *out_bytes;
+  return (size_t)PR_CTRL_BYTES + (oneshot ? 2 : 1) * (size_t)world * *slot_bytes + 2 * *out_bytes;
 }
+static size_t out_offset(const PeerComm* c) { return (size_t)PR_CTRL_BYTES + (c->oneshot ? 2 : 1) * (size_t)c->world * c->slot_bytes; }
 
 }  // namespace b2q
 
@@ -180,17 +197,20 @@ using namespace b2q;
 
 extern "C" {
 
-int b2q_comm_create(int rank, int world, int64_t max_rows, int64_t max_cols, void** comm_out, void* ipc_handle_out) {
+int b2q_comm_create_mode(int rank, int world, int64_t max_rows, int64_t max_cols, int mode, void** comm_out, void* ipc_handle_out) {
   if (!comm_out) return B2Q_ERR_NULL;
   if (world < 1 || world > PR_MAX_WORLD || rank < 0 || rank >= world) return B2Q_ERR_SHAPE;
   if (max_rows <= 0 || max_cols <= 0 || (max_cols % (world * 8)) != 0) return B2Q_ERR_SHAPE;
-  if ((max_cols / world + PR_CB - 1) / PR_CB > PR_MAX_BLOCKS || max_rows > 4096) return B2Q_ERR_LIMIT;
+  if (mode < B2Q_COMM_AUTO || mode > B2Q_COMM_TWO_STEPS) return B2Q_ERR_SHAPE;
+  // one step while every rank's whole tile to every peer is still a few microseconds of NVLink time
+  const bool oneshot = mode == B2Q_COMM_ONE_STEP || (mode == B2Q_COMM_AUTO && world <= 4 && max_rows <= 256);
+  if (((oneshot ? max_cols : max_cols / world) + PR_CB - 1) / PR_CB > PR_MAX_BLOCKS || max_rows > 4096) return B2Q_ERR_LIMIT;
   PeerComm* c = new (std::nothrow) PeerComm();
   if (!c) return B2Q_ERR_CUDA;
-  c->rank = rank; c->world = world; c->emulated = false; c->calls = 0;
+  c->rank = rank; c->world = world; c->emulated = false; c->oneshot = oneshot; c->calls = 0;
   c->max_rows = max_rows; c->max_cols = max_cols;
   if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; return B2Q_ERR_CUDA; }
-  c->bytes = layout_bytes(world, max_rows, max_cols, &c->slot_bytes, &c->out_bytes);
+  c->bytes = layout_bytes(world, oneshot, max_rows, max_cols, &c->slot_bytes, &c->out_bytes);
   void* p = nullptr;
   if (cudaMalloc(&p, c->bytes) != cudaSuccess) { delete c; return B2Q_ERR_CUDA; }
   if (cudaMemset(p, 0, c->bytes) != cudaSuccess) { cudaFree(p); delete c; return B2Q_ERR_CUDA; }
@@ -204,6 +224,10 @@ int b2q_comm_create(int rank, int world, int64_t max_rows, int64_t max_cols, voi
   }
   *comm_out = c;
   return B2Q_OK;
+}
+
+int b2q_comm_create(int rank, int world, int64_t max_rows, int64_t max_cols, void** comm_out, void* ipc_handle_out) {
+  return b2q_comm_create_mode(rank, world, max_rows, max_cols, B2Q_COMM_AUTO, comm_out, ipc_handle_out);
 }
 
 int b2q_comm_connect(void* comm, const void* all_handles) {
@@ -229,7 +253,7 @@ int b2q_comm_connect_local(void** comms, int world) {
     if (!ca || ca->world != world || ca->rank != a) return B2Q_ERR_SHAPE;
     for (int b = 0; b < world; ++b) {
       PeerComm* cb = reinterpret_cast<PeerComm*>(comms[b]);
-      if (!cb || cb->device != ca->device) return B2Q_ERR_SHAPE;
+      if (!cb || cb->device != ca->device || cb->oneshot != ca->oneshot) return B2Q_ERR_SHAPE;
       ca->peers[b] = cb->local;
     }
     ca->emulated = true;
@@ -252,7 +276,7 @@ int b2q_comm_result_ptr(void* comm, int which, void** out) {
   PeerComm* c = reinterpret_cast<PeerComm*>(comm);
   if (!c || !out) return B2Q_ERR_NULL;
   if (which < 0 || which > 1) return B2Q_ERR_SHAPE;
-  *out = c->local + PR_CTRL_BYTES + (size_t)c->world * c->slot_bytes + (size_t)which * c->out_bytes;
+  *out = c->local + out_offset(c) + (size_t)which * c->out_bytes;
   return B2Q_OK;
 }
 
@@ -281,10 +305,10 @@ static int fill_params(PeerComm* c, PeerReduceParams& p, int slot, const void* i
     if (!c->peers[r]) return B2Q_ERR_NULL;       // not connected
     p.r[slot].bufs[r] = c->peers[r];
   }
-  p.world = c->world; p.M = (int)M; p.N = (int)N; p.slice = (int)(N / c->world);
-  p.nblocks = (p.slice + PR_CB - 1) / PR_CB; p.bf16 = dtype == B2Q_BF16;
-  p.slot_off = PR_CTRL_BYTES; p.slot_bytes = c->slot_bytes;
-  p.out_off = PR_CTRL_BYTES + (size_t)c->world * c->slot_bytes; p.out_bytes = c->out_bytes;
+  p.world = c->world; p.M = (int)M; p.N = (int)N; p.slice = (int)(N / c->world); p.oneshot = c->oneshot ? 1 : 0;
+  p.nblocks = ((c->oneshot ? p.N : p.slice) + PR_CB - 1) / PR_CB; p.bf16 = dtype == B2Q_BF16;
+  p.slot_off = PR_CTRL_BYTES + (c->oneshot ? (size_t)(c->calls & 1) * c->world * c->slot_bytes : 0); p.slot_bytes = c->slot_bytes;
+  p.out_off = out_offset(c); p.out_bytes = c->out_bytes;
   p.limit_ticks = (long long)(limit_ms * 1.9e6);
   return B2Q_OK;
 }
@@ -296,7 +320,7 @@ namespace b2q {
 int peer_epilogue(void* comm, int64_t M, int64_t N, PeerEpilogue* out) {
   PeerComm* c = reinterpret_cast<PeerComm*>(comm);
   if (!c || !out) return B2Q_ERR_NULL;
-  if (c->emulated) return B2Q_ERR_UNSUPPORTED;
+  if (c->emulated || c->oneshot) return B2Q_ERR_UNSUPPORTED;
   if (M <= 0 || M > c->max_rows || N > c->max_cols || (N % (c->world * 128)) != 0) return B2Q_ERR_SHAPE;
   for (int r = 0; r < c->world; ++r) {
     if (!c->peers[r]) return B2Q_ERR_NULL;
@@ -321,6 +345,9 @@ int b2q_allreduce_sum(void* comm, const void* in, int dtype, int64_t ldi, int64_
   p.out_sel = (int)(c->calls & 1);
   c->calls++;
   dim3 grid(p.nblocks, 1, 1);
+  // A plain launch, on purpose: let the kernels behind this one begin early (programmatic stream serialization) and
+  // the next GEMM's CTAs sit on the SMs polling their barriers while these 32 to 64 CTAs, whose time is all latency,
+  // do the exchange: the tensor-parallel decoder layer measured 3 % slower on two GPUs that way.
   if (p.bf16) peer_reduce_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   else peer_reduce_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(p);
   note_launch("peer_reduce");
@@ -348,10 +375,12 @@ int b2q_allreduce_sum_emulated(void** comms, int world, int n_present, const voi
   }
   // the CTAs of different ranks wait for one another inside this one launch: they must all be resident
   dim3 grid(p.nblocks, n_present, 1);
-  int dev = 0, sms = 0;
+  int dev = 0, sms = 0, per_sm = 0;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if ((int)(grid.x * grid.y) > sms) return B2Q_ERR_LIMIT;
+  if (p.bf16) cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, peer_reduce_kernel<true>, 256, 0);
+  else cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, peer_reduce_kernel<false>, 256, 0);
+  if ((int)(grid.x * grid.y) > sms * per_sm) return B2Q_ERR_LIMIT;
   void* args[] = {(void*)&p};
   cudaError_t e = p.bf16 ? cudaLaunchCooperativeKernel((void*)peer_reduce_kernel<true>, grid, dim3(256), args, 0, (cudaStream_t)stream)
                          : cudaLaunchCooperativeKernel((void*)peer_reduce_kernel<false>, grid, dim3(256), args, 0, (cudaStream_t)stream);

@@ -6,7 +6,7 @@
 namespace b2q {
 
 constexpr int PR_MAX_WORLD = 8;
-constexpr int PR_MAX_BLOCKS = 512;        // column blocks of 128 per rank slice: N / W <= 65536
+constexpr int PR_MAX_BLOCKS = 512;        // column blocks of 128 per flag row: N / W (two steps) or N (one step) <= 65536
 constexpr int PR_CB = 128;                // columns per block
 constexpr int PR_CTRL_BYTES = 4096 + 2 * PR_MAX_WORLD * PR_MAX_BLOCKS * 4;
 
@@ -34,7 +34,9 @@ __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
 
 
 // What a GEMM needs in order to deliver its output tile straight into the slots of the owner ranks (step 1 of the
-// reduction) instead of into local memory: a strip of 128 output columns belongs to one owner rank and one block.
+// two-step reduction) instead of into local memory: a strip of 128 output columns belongs to one owner rank and one
+// block.  The one-step form is not fed this way: there the strip would go to every rank with 2-byte peer stores from
+// inside the GEMM, which measured slower on two GPUs than the GEMM followed by the reduction kernel.
 struct PeerEpilogue {
   uint8_t* bufs[PR_MAX_WORLD];     // every rank's buffer as addressed from this rank
   int world, rank, slice, M;       // slice = N / world (a multiple of 128 for this path), M = rows of the tile

@@ -58,6 +58,7 @@ _SIGS = {
     "b2q_moe_gemm_fp8": (i32, [vp, i32, i64, vp, i32, vp, i32, vp, i32, vp, i32, vp, i64, vp,
                                i64, i64, i64, i32, vp, sz, vp]),
     "b2q_comm_create": (i32, [i32, i32, i64, i64, vp, vp]),
+    "b2q_comm_create_mode": (i32, [i32, i32, i64, i64, i32, vp, vp]),
     "b2q_comm_connect": (i32, [vp, vp]),
     "b2q_comm_connect_local": (i32, [vp, i32]),
     "b2q_comm_destroy": (i32, [vp]),
@@ -85,6 +86,7 @@ W4_NMAJOR, W4_KMAJOR, W4_KMAJOR_MARLIN, W4_NMAJOR_S4 = 0, 1, 2, 3
 E4M3, E5M2 = 0, 1
 SCALE_CHANNEL, SCALE_TENSOR, SCALE_BLOCK128 = 0, 1, 2
 ACT_NONE, ACT_SILU_MUL, ACT_SILU_MUL_IN, ACT_GELU_TANH_MUL = 0, 1, 2, 3
+COMM_AUTO, COMM_ONE_STEP, COMM_TWO_STEPS = 0, 1, 2
 
 _DT = {torch.bfloat16: BF16, torch.float16: F16, torch.float32: F32}
 

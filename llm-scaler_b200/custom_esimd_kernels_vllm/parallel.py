@@ -170,16 +170,19 @@ class PeerReducer:
 
     reduce(t) returns a view of the communicator's result area, valid until the next call but one."""
 
-    def __init__(self, M, N, dtype, device, group=None):
+    def __init__(self, M, N, dtype, device, group=None, mode=0):
+        """mode: _lib.COMM_AUTO (one step over the links for up to four ranks, two steps beyond), COMM_ONE_STEP or
+        COMM_TWO_STEPS; the same on every rank."""
         import ctypes as C
         from . import _lib as L
         self.L, self.C = L, C
+        self.mode = mode
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.M, self.N, self.dtype, self.device = M, N, dtype, torch.device(device)
         self.comm = C.c_void_p()
         handle = (C.c_uint8 * 64)()
         with torch.cuda.device(self.device):
-            L.check(L.lib.b2q_comm_create(self.rank, self.world, M, N, C.byref(self.comm), handle))
+            L.check(L.lib.b2q_comm_create_mode(self.rank, self.world, M, N, mode, C.byref(self.comm), handle))
             mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
             every = [torch.empty_like(mine) for _ in range(self.world)]
             dist.all_gather(every, mine, group=group)
@@ -233,7 +236,10 @@ class PeerReducer:
         return int(v.value)
 
     def describe(self):
-        return "b2q_allreduce_sum: one kernel, peer stores over NVLink, partial tiles added in rank order (fp32), bounded flag waits"
+        one = self.mode == 1 or (self.mode == 0 and self.world <= 4 and self.M <= 256)
+        form = ("every rank stores its tile into every rank's buffer, every rank adds (one trip over NVLink)" if one else
+                "reduce-scatter then broadcast (two trips over NVLink)")
+        return "b2q_allreduce_sum: one kernel, plain peer stores, " + form + ", tiles added in rank order (fp32), bounded flag waits"
 
     def close(self):
         if self.comm:
@@ -242,7 +248,7 @@ class PeerReducer:
             self.comm = None
 
 
-def make_reducer(M, N, dtype, device, group=None, kind=None):
+def make_reducer(M, N, dtype, device, group=None, kind=None, mode=0):
     """The object whose reduce(t) sums a [M, N] partial result over the ranks of `group`: this library's peer-memory
     kernel for decode-sized tiles on CUDA devices, the process group's all-reduce otherwise (kind / B2Q_REDUCER =
     "peer" or "nccl" forces one)."""
@@ -253,7 +259,7 @@ def make_reducer(M, N, dtype, device, group=None, kind=None):
     if kind is None:
         kind = "peer" if (cuda and world > 1 and world <= 8 and M <= 64 and N % (8 * world) == 0) else "nccl"
     if kind == "peer" and cuda and world > 1:
-        return PeerReducer(M, N, dtype, device, group)
+        return PeerReducer(M, N, dtype, device, group, mode)
     return NcclReducer()
 
 

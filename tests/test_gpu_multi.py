@@ -45,9 +45,11 @@ def _worker(rank, world, port, what, q):
             if what == "tp":
                 out = P.tp_layer_forward(full["x"].to(dev), layer, be)
             else:
-                # the library's own exchange: peer-memory reduction kernel, alone ("tp_peer") or fed directly by the GEMM
-                # epilogue ("tp_fused"); three passes so that the flag epochs and both result areas are exercised
-                red = P.make_reducer(40, hidden, torch.bfloat16, dev, kind="peer")
+                # the library's own exchange: peer-memory reduction kernel, alone ("tp_peer": the default form for two
+                # ranks, one trip over the links) or fed directly by the GEMM epilogue ("tp_fused": the two-step form,
+                # the one a GEMM epilogue can feed); three passes so that the flag epochs, both slot sets and both
+                # result areas are exercised
+                red = P.make_reducer(40, hidden, torch.bfloat16, dev, kind="peer", mode=2 if what == "tp_fused" else 0)
                 assert isinstance(red, P.PeerReducer)
                 x = full["x"].to(dev)
                 for _ in range(3):

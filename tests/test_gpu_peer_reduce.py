@@ -26,12 +26,12 @@ def L(lib_built):
 
 
 class Ranks:
-    def __init__(self, L, world, M, N):
+    def __init__(self, L, world, M, N, mode=0):
         self.L, self.world, self.M, self.N = L, world, M, N
         self.comms = (C.c_void_p * world)()
         for r in range(world):
             c = C.c_void_p()
-            L.check(L.lib.b2q_comm_create(r, world, M, N, C.byref(c), None))
+            L.check(L.lib.b2q_comm_create_mode(r, world, M, N, mode, C.byref(c), None))
             self.comms[r] = c
         L.check(L.lib.b2q_comm_connect_local(self.comms, world))
 
@@ -64,11 +64,12 @@ def _ordered_sum(ins):
 
 @pytest.mark.parametrize("world,M,N,dtype", [(2, 64, 8192, torch.bfloat16), (4, 64, 8192, torch.bfloat16), (8, 64, 8192, torch.bfloat16),
                                              (4, 7, 768, torch.float16), (8, 1, 1024, torch.bfloat16), (3, 16, 1200, torch.float16)])
-def test_sum_is_bit_identical_to_rank_order_fp32(L, world, M, N, dtype):
-    ranks = Ranks(L, world, M, N)
+@pytest.mark.parametrize("mode", [1, 2])           # one step over the links / two steps (reduce-scatter, broadcast)
+def test_sum_is_bit_identical_to_rank_order_fp32(L, world, M, N, dtype, mode):
+    ranks = Ranks(L, world, M, N, mode)
     try:
         g = torch.Generator(device=DEV).manual_seed(world * 1000 + M)
-        for call in range(3):                    # several epochs on the same buffers, nothing cleared in between
+        for call in range(5):                    # several epochs on the same buffers (both slot sets), nothing cleared in between
             ins = [torch.randn(M, N, generator=g, device=DEV).to(dtype) for _ in range(world)]
             outs = ranks.reduce(ins)
             torch.cuda.synchronize()
@@ -80,8 +81,9 @@ def test_sum_is_bit_identical_to_rank_order_fp32(L, world, M, N, dtype):
         ranks.close()
 
 
-def test_row_pitch_and_smaller_tile_than_the_bound(L):
-    ranks = Ranks(L, 4, 64, 8192)
+@pytest.mark.parametrize("mode", [0, 2])
+def test_row_pitch_and_smaller_tile_than_the_bound(L, mode):
+    ranks = Ranks(L, 4, 64, 8192, mode)
     try:
         g = torch.Generator(device=DEV).manual_seed(5)
         wide = [torch.randn(40, 4096 + 64, generator=g, device=DEV).to(torch.bfloat16) for _ in range(4)]
@@ -93,8 +95,9 @@ def test_row_pitch_and_smaller_tile_than_the_bound(L):
         ranks.close()
 
 
-def test_absent_rank_makes_the_wait_give_up_and_report(L):
-    ranks = Ranks(L, 2, 16, 1024)
+@pytest.mark.parametrize("mode", [1, 2])
+def test_absent_rank_makes_the_wait_give_up_and_report(L, mode):
+    ranks = Ranks(L, 2, 16, 1024, mode)
     x = [torch.ones(16, 1024, dtype=torch.bfloat16, device=DEV) for _ in range(2)]
     try:
         ranks.reduce(x, present=1, limit_ms=1.0)                 # rank 1 never arrives
@@ -103,7 +106,7 @@ def test_absent_rank_makes_the_wait_give_up_and_report(L):
     finally:
         ranks.close()
     # the context is intact: a fresh set of communicators works
-    ranks = Ranks(L, 2, 16, 1024)
+    ranks = Ranks(L, 2, 16, 1024, mode)
     try:
         outs = ranks.reduce(x)
         torch.cuda.synchronize()
