@@ -126,6 +126,8 @@ def tp_case(M, rank, world, dev, P, be):
         stack = _tp_stack(world, layers, dev, g, P)
         us = measure(stack, reducer.reduce, world, getattr(reducer, "row_linear", None))
         us_nosum = measure(stack, lambda t, group=None: t, world)
+        if isinstance(reducer, P.OverlappedReducer):
+            rec["us_per_layer_unchunked_all_reduce"] = round(measure(stack, P.NcclReducer().reduce, world), 1)
         if isinstance(reducer, P.PeerReducer):
             # for comparison: the same sharded kernels with the process group's all-reduce, and with the two-step form
             # of this library's reduction fed by the GEMM epilogue (the default form for up to four ranks is one step
@@ -171,7 +173,11 @@ def ep_case(rank, world, dev, P, be):
     rec = {"case": "ep_c4_moe_int4_t4096", "n_gpus": world, "parallelism": f"ep{world}", "one_gpu_us": round(us1, 1)}
     if world > 1:
         a = build(world, rank)
-        us = _timed(lambda i: P.ep_moe_forward(*a, k, E, be), 8, 3, world)
+        ex = P.EpExchange(T // world * k, H, torch.bfloat16, dev)
+        fwd = lambda marks=None: P.ep_moe_forward_device(*a, k, E, be, ex, marks=marks)
+        us = _timed(lambda i: fwd(), 8, 3, world)
+        # for comparison: the same pass with the process group's all-to-all, whose row counts go through the host
+        rec["us_nccl_all_to_all_host_counts"] = round(_timed(lambda i: P.ep_moe_forward(*a, k, E, be), 8, 3, world), 1)
         # time inside the exchange steps: events at the phase boundaries of a few further passes
         spans = {"dispatch": [], "combine": []}
         for _ in range(4):
@@ -180,15 +186,17 @@ def ep_case(rank, world, dev, P, be):
             def mark(label):
                 evs[label] = torch.cuda.Event(enable_timing=True)
                 evs[label].record()
-            P.ep_moe_forward(*a, k, E, be, marks=mark)
+            fwd(mark)
             torch.cuda.synchronize()
             spans["dispatch"].append(evs["dispatch_begin"].elapsed_time(evs["dispatch_end"]) * 1e3)
             spans["combine"].append(evs["combine_begin"].elapsed_time(evs["combine_end"]) * 1e3)
-        ex = _max_over_ranks(statistics.median(spans["dispatch"]) + statistics.median(spans["combine"]), world)
-        rec.update(us=round(us, 1), exchange_us=round(ex, 1),
-                   exchange="counts exchange + all-to-all of rows and expert ids (dispatch), all-to-all of results (combine): " + P.EP_EXCHANGE,
+        ex_us = _max_over_ranks(statistics.median(spans["dispatch"]) + statistics.median(spans["combine"]), world)
+        rec.update(us=round(us, 1), exchange_us=round(ex_us, 1),
+                   exchange="rows and expert indices to the owners (dispatch), results back (combine): " + ex.describe(),
+                   exchange_status=ex.status(),
                    all_to_all_bytes_per_pass=int(2 * T * k * H * 2 * (world - 1) / world),
                    speedup_vs_one_gpu=round(us1 / us, 2), efficiency=round(us1 / us / world, 3))
+        ex.close()
     else:
         us = us1
         rec["us"] = round(us, 1)

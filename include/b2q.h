@@ -371,6 +371,43 @@ B2Q_API int b2q_comm_connect_local(void** comms, int world);
 B2Q_API int b2q_allreduce_sum_emulated(void** comms, int world, int n_present, const void* const* ins, int dtype,
                                int64_t ldi, int64_t M, int64_t N, double wait_limit_ms, void** outs, void* stream);
 
+/* ---- token exchange of an expert-parallel MoE layer over the GPUs of one box ---------------------------
+ * The reference splits the experts contiguously over the ranks (vllm/patches/vllm_for_multi_arc.patch:3356-3365)
+ * and emulates the all-to-all with an all-gather and a reduce-scatter of the whole batch (:1559-1563).  Here the
+ * rows travel by plain peer stores and every count stays on the device (a library all-to-all wants the counts on
+ * the host first).  One communicator per rank; cap_rows = the most (token, slot) pairs one rank sends in a pass
+ * (its tokens x top_k), H = row width in 16-bit values (H % 8 == 0).  Set-up as for b2q_comm_create: the
+ * communicator allocates its buffer (the receive area [world x cap_rows x H], the expert indices of those rows
+ * [world x cap_rows] int32, the return area [cap_rows x H]) and hands out a 64-byte CUDA IPC handle; gather the
+ * handles in rank order and pass them to b2q_ep_connect.  One pass, all calls on one stream:
+ *   b2q_ep_dispatch  x [T, ldx]; order[n_pairs] = pair indices (token * top_k + slot) sorted by destination rank,
+ *                    dest_offsets[world + 1] = where each rank's segment starts (both from b2q_moe_route over
+ *                    expert / experts_per_rank with `world` buckets), local_ids[n_pairs] = expert index on the
+ *                    owner, in the same order.  Copies the rows into slot `rank` of every owner's receive area;
+ *                    unused positions of the slot get the index -1 (b2q_moe_route drops those).
+ *   b2q_ep_wait(0)   returns on the stream once the slots of all ranks have landed here.  The caller then routes
+ *                    the world * cap_rows indices and runs the grouped GEMMs over the receive area with
+ *                    rows = world * cap_rows as an upper bound; results go back to the rows' positions.
+ *   b2q_ep_return    y [world * cap_rows, ldy] in receive-area order: every filled row goes to its source rank's
+ *                    return area at the position it had in that rank's `order`.
+ *   b2q_ep_wait(1)   returns once all owners' results have landed; the return area then holds [n_pairs, H] in
+ *                    `order` order, ready for b2q_moe_combine.
+ * Waits are bounded by wait_limit_ms (<= 0: two seconds); an expired wait is reported by b2q_ep_status (301: rows
+ * missing, 302: results missing) and the communicators must then be re-created on all ranks.  All ranks make the
+ * same calls in the same order.  No multicast, no library collective, no allocation and no host read per pass.
+ * b2q_ep_connect_local wires communicators of ONE process on ONE device (tests): run each step for all ranks
+ * before the next step, so that no kernel waits for a later launch.                                      */
+B2Q_API int b2q_ep_create(int rank, int world, int64_t cap_rows, int64_t H, void** comm, void* ipc_handle_out);
+B2Q_API int b2q_ep_connect(void* comm, const void* all_ipc_handles /* world x 64 bytes */);
+B2Q_API int b2q_ep_connect_local(void** comms, int world);
+B2Q_API int b2q_ep_destroy(void* comm);
+B2Q_API int b2q_ep_status(void* comm, int* out);
+B2Q_API int b2q_ep_buffers(void* comm, void** recv_rows, void** recv_ids, void** ret_rows);
+B2Q_API int b2q_ep_dispatch(void* comm, const void* x, int dtype, int64_t ldx, const int32_t* order, int top_k,
+                    const int32_t* dest_offsets, const int32_t* local_ids, int64_t n_pairs, void* stream);
+B2Q_API int b2q_ep_return(void* comm, const void* y, int dtype, int64_t ldy, void* stream);
+B2Q_API int b2q_ep_wait(void* comm, int phase, double wait_limit_ms, void* stream);
+
 /* Code of the first bounded device-side wait that expired since the library was loaded
  * (0 = none).  Synchronises the device; meant for tests and post-mortems.       */
 B2Q_API int b2q_device_status(int* out);

@@ -25,7 +25,7 @@ int quantize_fp8(const void*, int, int64_t, void*, float*, int, int64_t, int64_t
 int shared_gate_add(const void*, const void*, const void*, const void*, void*, int, int64_t, int64_t, cudaStream_t);
 int moe_combine(const void*, const void*, int, const int32_t*, void*, int, int64_t, int, int64_t, int, cudaStream_t);
 int act_quant_1x128(const void*, int, int64_t, void*, float*, int64_t, int64_t, cudaStream_t);
-int act_prep(const void*, bool, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t);
+int act_prep(const void*, bool, bool, int64_t, const int32_t*, int, void*, float*, int64_t, int, int, cudaStream_t, const int32_t* n_valid = nullptr);
 int act_split_fp8(const void*, bool, int64_t, void*, float*, int64_t, int, cudaStream_t);
 int quantize_q4_0(const void*, bool, int64_t, void*, void*, int64_t, int64_t, cudaStream_t);
 int resadd_rmsnorm(const void*, void*, const void*, void*, const void*, void*, bool, int64_t, int, float, float, cudaStream_t);
@@ -579,8 +579,10 @@ int b2q_moe_gemm_int4(const void* x, int act_dtype, int64_t ldx, const int32_t* 
   if (umma_w4_supported(ua) && want_umma) {
     // gather (if any), fp16 re-scaling and pair permutation in one pre-pass over the rows
     // (with a gated input also silu(gate) * up, so that the gate_up result is read once and never re-written)
+    // `rows` may be an upper bound (expert-parallel receive buffers of fixed capacity): the rows actually routed
+    // to these experts are expert_offsets[E], known on the device only
     rc = act_prep(x, bf, gated_in, ldx, row_map, row_div, pl.xg, pl.inv, rows, (int)K,
-                  w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1, st);
+                  w_layout == B2Q_W4_KMAJOR_MARLIN ? 2 : 1, st, expert_offsets + E);
     if (rc) return rc;
     ua.x = pl.xg; ua.ldx = K; ua.bf16 = false; ua.tok_scale = pl.inv; ua.magic = true;
     const int tile = umma_w4_token_tile(ua);

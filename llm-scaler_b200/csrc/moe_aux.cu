@@ -604,7 +604,8 @@ namespace b2q {
 // fp32 and rounded to the source type first, exactly as the separate silu_mul_kernel writes it.
 template <bool IN_BF16, bool GATED>
 __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const int32_t* __restrict__ idx, int div,
-                                __half* __restrict__ x16, float* __restrict__ inv_scale, int K, int perm, int release_early) {
+                                __half* __restrict__ x16, float* __restrict__ inv_scale, int K, int perm, int release_early,
+                                const int32_t* __restrict__ n_valid) {
   using A = Act<IN_BF16>;
   using T = typename A::T;
   __shared__ float red[32];
@@ -616,6 +617,8 @@ __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const i
   grid_dep_wait();
   if (!release_early) grid_dep_release();
   const int64_t r = blockIdx.x;
+  // the launch covers the caller's upper bound of rows; the number actually routed here is only known on the device
+  if (n_valid && r >= *n_valid) return;
   const int64_t srow = idx ? (int64_t)(idx[r] / div) : r;
   const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + srow * ldx;
   // eight consecutive source values of the row as floats that are exactly representable in the source type
@@ -700,7 +703,8 @@ __global__ void act_prep_kernel(const void* __restrict__ x, int64_t ldx, const i
 template <bool IN_BF16, bool GATED, int MAXI>
 __global__ void __launch_bounds__(256) act_prep_warp_kernel(const void* __restrict__ x, int64_t ldx, const int32_t* __restrict__ idx,
                                                             int div, __half* __restrict__ x16, float* __restrict__ inv_scale,
-                                                            int64_t rows, int K, int perm, int release_early) {
+                                                            int64_t rows, int K, int perm, int release_early,
+                                                            const int32_t* __restrict__ n_valid) {
   using A = Act<IN_BF16>;
   using T = typename A::T;
   if (release_early) grid_dep_release();
@@ -708,7 +712,7 @@ __global__ void __launch_bounds__(256) act_prep_warp_kernel(const void* __restri
   if (!release_early) grid_dep_release();
   const int lane = threadIdx.x & 31;
   const int64_t r = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (r >= rows) return;
+  if (r >= rows || (n_valid && r >= *n_valid)) return;
   const int64_t srow = idx ? (int64_t)(idx[r] / div) : r;
   const uint16_t* row = reinterpret_cast<const uint16_t*>(x) + srow * ldx;
   const int iters = K >> 8;
@@ -770,12 +774,12 @@ __global__ void __launch_bounds__(256) act_prep_warp_kernel(const void* __restri
 
 template <bool IN_BF16, bool GATED>
 static cudaError_t act_prep_warp_launch(const void* x, int64_t ldx, const int32_t* idx, int div, void* x16, float* inv_scale,
-                                        int64_t rows, int K, int perm, int mode, cudaStream_t st) {
+                                        int64_t rows, int K, int perm, int mode, cudaStream_t st, const int32_t* n_valid) {
   const dim3 grid((unsigned)((rows + 7) / 8)), block(256);
   const int iters = K >> 8;
   auto go = [&](auto kern) {
     return launch_overlapped(kern, grid, block, 0, st, mode > 0, x, ldx, idx, div > 0 ? div : 1,
-                             reinterpret_cast<__half*>(x16), inv_scale, rows, K, perm, mode == 2 ? 1 : 0);
+                             reinterpret_cast<__half*>(x16), inv_scale, rows, K, perm, mode == 2 ? 1 : 0, n_valid);
   };
   if (iters <= 4) return go(act_prep_warp_kernel<IN_BF16, GATED, 4>);
   if (iters <= 8) return go(act_prep_warp_kernel<IN_BF16, GATED, 8>);
@@ -783,16 +787,16 @@ static cudaError_t act_prep_warp_launch(const void* x, int64_t ldx, const int32_
 }
 
 int act_prep(const void* x, bool in_bf16, bool gated, int64_t ldx, const int32_t* idx, int div, void* x16,
-             float* inv_scale, int64_t rows, int K, int perm, cudaStream_t st) {
+             float* inv_scale, int64_t rows, int K, int perm, cudaStream_t st, const int32_t* n_valid) {
   if (rows == 0) return B2Q_OK;
   // many short rows (the grouped GEMMs' pre-pass): one warp per row
   if (rows >= 1024 && (K & 255) == 0 && K <= (gated ? 2048 : 4096)) {
     const int mode = tls().overlap_mode;
     cudaError_t e;
-    if (in_bf16) e = gated ? act_prep_warp_launch<true, true>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st)
-                           : act_prep_warp_launch<true, false>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st);
-    else         e = gated ? act_prep_warp_launch<false, true>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st)
-                           : act_prep_warp_launch<false, false>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st);
+    if (in_bf16) e = gated ? act_prep_warp_launch<true, true>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st, n_valid)
+                           : act_prep_warp_launch<true, false>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st, n_valid);
+    else         e = gated ? act_prep_warp_launch<false, true>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st, n_valid)
+                           : act_prep_warp_launch<false, false>(x, ldx, idx, div, x16, inv_scale, rows, K, perm, mode, st, n_valid);
     note_launch("act_prep");
     return e == cudaSuccess ? launch_status() : B2Q_ERR_CUDA;
   }
@@ -801,7 +805,7 @@ int act_prep(const void* x, bool in_bf16, bool gated, int64_t ldx, const int32_t
   const int mode = tls().overlap_mode;
   auto go = [&](auto kern) {
     return launch_overlapped(kern, dim3((unsigned)rows), dim3(threads), 0, st, mode > 0, x, ldx, idx,
-                             div > 0 ? div : 1, reinterpret_cast<__half*>(x16), inv_scale, K, perm, mode == 2 ? 1 : 0);
+                             div > 0 ? div : 1, reinterpret_cast<__half*>(x16), inv_scale, K, perm, mode == 2 ? 1 : 0, n_valid);
   };
   cudaError_t e;
   if (in_bf16) e = gated ? go(act_prep_kernel<true, true>) : go(act_prep_kernel<true, false>);

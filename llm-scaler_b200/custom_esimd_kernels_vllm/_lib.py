@@ -60,6 +60,15 @@ _SIGS = {
     "b2q_comm_create": (i32, [i32, i32, i64, i64, vp, vp]),
     "b2q_comm_create_mode": (i32, [i32, i32, i64, i64, i32, vp, vp]),
     "b2q_comm_connect": (i32, [vp, vp]),
+    "b2q_ep_create": (i32, [i32, i32, i64, i64, vp, vp]),
+    "b2q_ep_connect": (i32, [vp, vp]),
+    "b2q_ep_connect_local": (i32, [vp, i32]),
+    "b2q_ep_destroy": (i32, [vp]),
+    "b2q_ep_status": (i32, [vp, vp]),
+    "b2q_ep_buffers": (i32, [vp, vp, vp, vp]),
+    "b2q_ep_dispatch": (i32, [vp, vp, i32, i64, vp, i32, vp, vp, i64, vp]),
+    "b2q_ep_return": (i32, [vp, vp, i32, i64, vp]),
+    "b2q_ep_wait": (i32, [vp, i32, C.c_double, vp]),
     "b2q_comm_connect_local": (i32, [vp, i32]),
     "b2q_comm_destroy": (i32, [vp]),
     "b2q_comm_status": (i32, [vp, vp]),

@@ -248,18 +248,60 @@ class PeerReducer:
             self.comm = None
 
 
+class OverlappedReducer:
+    """Row-parallel linear + sum for prefill-sized tiles (hundreds of tokens and more), where the sum is bytes, not
+    latency: the tokens are cut into chunks, and while the GEMM of chunk i + 1 runs on the caller's stream the
+    process group's all-reduce of chunk i runs on a second stream (NCCL over NVLink, a few tens of CTAs).  The weights
+    of a rank's shard are re-read once per chunk (from L2 where the shard fits).  The results are those of the
+    unchunked form: every output row depends on its own token only and the all-reduce adds the same values."""
+
+    def __init__(self, chunks=4, min_chunk_rows=256, group=None):
+        from . import _impl
+        self.I, self.group = _impl, group
+        self.chunks, self.min_rows = int(chunks), int(min_chunk_rows)
+        self.side = torch.cuda.Stream()
+
+    def reduce(self, t, group=None):
+        return all_reduce(t, group if group is not None else self.group)
+
+    def row_linear(self, x, w, s):
+        M, N = x.shape[0], w.shape[0]
+        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        step = max(self.min_rows, -(-M // self.chunks))
+        main = torch.cuda.current_stream(x.device)
+        for lo in range(0, M, step):
+            part = out[lo:lo + step]
+            self.I.linear_int4(x[lo:lo + step], w, s, part)
+            done = torch.cuda.Event()
+            done.record(main)
+            self.side.wait_event(done)
+            with torch.cuda.stream(self.side):
+                dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group)
+        main.wait_stream(self.side)            # also keeps `out` from being reused before the second stream is done
+        return out
+
+    def describe(self):
+        return ("torch.distributed all_reduce (NCCL) per chunk of %d tokens at least, on a second stream under the GEMM "
+                "of the next chunk" % self.min_rows)
+
+
 def make_reducer(M, N, dtype, device, group=None, kind=None, mode=0):
     """The object whose reduce(t) sums a [M, N] partial result over the ranks of `group`: this library's peer-memory
-    kernel for decode-sized tiles on CUDA devices, the process group's all-reduce otherwise (kind / B2Q_REDUCER =
-    "peer" or "nccl" forces one)."""
+    kernel for decode-sized tiles on CUDA devices, the process group's all-reduce otherwise, chunked and overlapped
+    with the GEMM for prefill-sized tiles (kind / B2Q_REDUCER = "peer", "overlap" or "nccl" forces one)."""
     import os
     kind = kind or os.environ.get("B2Q_REDUCER")
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     cuda = torch.device(device).type == "cuda"
     if kind is None:
-        kind = "peer" if (cuda and world > 1 and world <= 8 and M <= 64 and N % (8 * world) == 0) else "nccl"
+        if cuda and world > 1 and world <= 8 and M <= 64 and N % (8 * world) == 0:
+            kind = "peer"
+        else:
+            kind = "overlap" if (cuda and world > 1 and M >= 512) else "nccl"
     if kind == "peer" and cuda and world > 1:
         return PeerReducer(M, N, dtype, device, group, mode)
+    if kind == "overlap" and cuda and world > 1:
+        return OverlappedReducer(group=group)
     return NcclReducer()
 
 
@@ -276,6 +318,92 @@ def ep_plan(ids: torch.Tensor, experts_per_rank: int, world: int, backend):
 
 
 EP_EXCHANGE = "torch.distributed all_to_all_single (NCCL send/recv), row counts read on the host"
+
+
+class EpExchange:
+    """Token exchange of the expert-parallel layer through this library's own kernels over peer memory (b2q_ep_* in
+    include/b2q.h): rows go to their experts' ranks and results come back by plain peer stores, every count stays on
+    the device, so a pass has no host read and no stalled stream.  cap_rows = this rank's tokens x top_k (the same on
+    every rank), H = row width."""
+
+    def __init__(self, cap_rows, H, dtype, device, group=None):
+        import ctypes as C
+        from . import _lib as L
+        self.L, self.C = L, C
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.cap, self.H, self.dtype, self.device = int(cap_rows), int(H), dtype, torch.device(device)
+        self.comm = C.c_void_p()
+        handle = (C.c_uint8 * 64)()
+        with torch.cuda.device(self.device):
+            L.check(L.lib.b2q_ep_create(self.rank, self.world, self.cap, self.H, C.byref(self.comm), handle))
+            mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+            every = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(every, mine, group=group)
+            L.check(L.lib.b2q_ep_connect(self.comm, bytes(torch.cat(every).cpu().tolist())))
+            dist.barrier(group)
+        self._views()
+
+    def _views(self):
+        L, C = self.L, self.C
+        rows, ids, ret = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        L.check(L.lib.b2q_ep_buffers(self.comm, C.byref(rows), C.byref(ids), C.byref(ret)))
+        n = self.world * self.cap
+        self.recv_rows = L.view_as_tensor(rows.value, (n, self.H), self.dtype, self.device, owner=self)
+        self.recv_ids = L.view_as_tensor(ids.value, (n,), torch.int32, self.device, owner=self)
+        self.ret_rows = L.view_as_tensor(ret.value, (self.cap, self.H), self.dtype, self.device, owner=self)
+
+    def dispatch(self, x, order, top_k, dest_offsets, local_ids):
+        L = self.L
+        L.check(L.lib.b2q_ep_dispatch(self.comm, x.data_ptr(), L.dt(x), x.stride(0), order.data_ptr(), top_k,
+                                       dest_offsets.data_ptr(), local_ids.data_ptr(), order.numel(), L.stream(x)))
+
+    def wait(self, phase, like):
+        self.L.check(self.L.lib.b2q_ep_wait(self.comm, phase, 0.0, self.L.stream(like)))
+
+    def give_back(self, y):
+        L = self.L
+        L.check(L.lib.b2q_ep_return(self.comm, y.data_ptr(), L.dt(y), y.stride(0), L.stream(y)))
+
+    def status(self):
+        v = self.C.c_int(0)
+        self.L.check(self.L.lib.b2q_ep_status(self.comm, self.C.byref(v)))
+        return v.value
+
+    def describe(self):
+        return ("b2q_ep_dispatch / b2q_ep_return: rows and results by plain peer stores over NVLink into fixed-capacity "
+                "slots, counts and offsets exchanged as data, bounded flag waits, no host read per pass")
+
+    def close(self):
+        if self.comm:
+            self.recv_rows = self.recv_ids = self.ret_rows = None
+            self.L.lib.b2q_ep_destroy(self.comm)
+            self.comm = None
+
+
+def ep_moe_forward_device(x, logits, w13, s13, w2, s2, top_k: int, num_experts: int, backend, exchange, marks=None):
+    """ep_moe_forward with the exchange done by `exchange` (EpExchange): the same steps, no count ever read on the
+    host.  The owner runs its grouped GEMMs over the whole receive area (world x cap rows as an upper bound); the
+    counting sort drops the empty positions and the kernels take the row count from its last offset."""
+    mark = marks if marks is not None else (lambda label: None)
+    world = exchange.world
+    T, H = x.shape
+    e_local = num_experts // world
+    wts, ids = backend.topk(logits, top_k, x.dtype)
+    dest = torch.div(ids, e_local, rounding_mode="floor").to(torch.int32).contiguous()
+    offsets, order, p2s, _ = backend.route(dest, world)
+    local_e = (ids.reshape(-1) % e_local).to(torch.int32)[order.long()].contiguous()
+    mark("dispatch_begin")
+    exchange.dispatch(x, order, top_k, offsets, local_e)
+    exchange.wait(0, x)
+    mark("dispatch_end")
+    n = world * exchange.cap
+    r_off, r_tok, _, _ = backend.route(exchange.recv_ids.reshape(-1, 1), e_local)
+    y = backend.expert_mlp(exchange.recv_rows, w13, s13, w2, s2, r_off, r_tok, n)
+    mark("combine_begin")
+    exchange.give_back(y)
+    exchange.wait(1, x)
+    mark("combine_end")
+    return backend.combine(exchange.ret_rows[:T * top_k], wts, p2s, T, top_k)
 
 
 def ep_moe_forward(x, logits, w13, s13, w2, s2, top_k: int, num_experts: int, backend, group=None, marks=None, world=None):

@@ -29,7 +29,7 @@ def _worker(rank, world, port, what, q):
     try:
         from custom_esimd_kernels_vllm import parallel as P
         be = P.CudaBackend()
-        if what in ("tp", "tp_peer", "tp_fused"):
+        if what in ("tp", "tp_peer", "tp_fused", "tp_overlap"):
             full = configs.c5_layer(seed=3, M=40, tp=1, rank=0, scale=1 / 16)
             packed = {n: (int4.pack_nmajor_i32(full[n][0]), full[n][1]) for n in ("qkv", "o", "gate_up", "down")}
             hidden = full["x"].shape[1]
@@ -44,6 +44,12 @@ def _worker(rank, world, port, what, q):
                               down=to(P.shard_row(*packed["down"], rank, world)))
             if what == "tp":
                 out = P.tp_layer_forward(full["x"].to(dev), layer, be)
+            elif what == "tp_overlap":
+                # the prefill form: token chunks, the all-reduce of a chunk on a second stream under the next chunk's GEMM
+                red = P.OverlappedReducer(chunks=3, min_chunk_rows=8)
+                x = full["x"].to(dev)
+                for _ in range(2):
+                    out = P.tp_layer_forward(x, layer, be, reduce=red.reduce, row_linear=red.row_linear)
             else:
                 # the library's own exchange: peer-memory reduction kernel, alone ("tp_peer": the default form for two
                 # ranks, one trip over the links) or fed directly by the GEMM epilogue ("tp_fused": the two-step form,
@@ -66,9 +72,20 @@ def _worker(rank, world, port, what, q):
             T = c["x"].shape[0] // world
             el = 8 // world
             sl, es = slice(rank * T, (rank + 1) * T), slice(rank * el, (rank + 1) * el)
-            out = P.ep_moe_forward(c["x"][sl].contiguous().to(dev), c["logits"][sl].contiguous().to(dev),
-                                   int4.pack_nmajor_i32(c["q13"][es]).to(dev), c["s13"][es].contiguous().to(dev),
-                                   int4.pack_nmajor_i32(c["q2"][es]).to(dev), c["s2"][es].contiguous().to(dev), 2, 8, be)
+            args = (c["x"][sl].contiguous().to(dev), c["logits"][sl].contiguous().to(dev),
+                    int4.pack_nmajor_i32(c["q13"][es]).to(dev), c["s13"][es].contiguous().to(dev),
+                    int4.pack_nmajor_i32(c["q2"][es]).to(dev), c["s2"][es].contiguous().to(dev), 2, 8, be)
+            if what == "ep":
+                out = P.ep_moe_forward(*args)
+            else:
+                # the library's own exchange over peer memory, counts on the device; three passes on the same buffers
+                ex = P.EpExchange(T * 2, c["x"].shape[1], torch.bfloat16, dev)
+                for _ in range(3):
+                    out = P.ep_moe_forward_device(*args, ex).clone()
+                torch.cuda.synchronize()
+                assert ex.status() == 0, "a bounded wait of the exchange expired"
+                dist.barrier()
+                ex.close()
         torch.cuda.synchronize()
         q.put((rank, out.cpu().contiguous().view(torch.int16).numpy().copy()))   # by value: a shared-memory handle dies with the sender
     finally:
@@ -122,10 +139,11 @@ def test_tensor_parallel_layer_two_gpus(two_gpus):
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("what", ["tp_peer", "tp_fused"])
+@pytest.mark.parametrize("what", ["tp_peer", "tp_fused", "tp_overlap"])
 def test_tensor_parallel_layer_two_gpus_own_exchange(two_gpus, what):
     """The same layer with the sum of the row-parallel partial results done by this library's kernels over peer
-    memory instead of the process group's all-reduce; every rank must hold bit-identical results."""
+    memory instead of the process group's all-reduce, or by the chunked all-reduce that overlaps the GEMM; every
+    rank must hold bit-identical results."""
     outs = _run(what)
     assert torch.equal(outs[0], outs[1])
     full = configs.c5_layer(seed=3, M=40, tp=1, rank=0, scale=1 / 16)
@@ -137,8 +155,11 @@ def test_tensor_parallel_layer_two_gpus_own_exchange(two_gpus, what):
 
 
 @pytest.mark.timeout(600)
-def test_expert_parallel_two_gpus(two_gpus):
-    outs = _run("ep")
+@pytest.mark.parametrize("what", ["ep", "ep_device"])
+def test_expert_parallel_two_gpus(two_gpus, what):
+    """Experts split over two ranks; rows exchanged by the process group's all-to-all ("ep") or by this library's
+    peer-memory kernels with all counts on the device ("ep_device")."""
+    outs = _run(what)
     c = configs.c4(seed=5, T=256, E=8, top_k=2, H=256, I=128)
     ref = moe.forward(c["x"], c["logits"], int4.dequant(c["q13"], c["s13"], torch.bfloat16),
                       int4.dequant(c["q2"], c["s2"], torch.bfloat16), 2)
