@@ -151,7 +151,7 @@ def test_moe_prefill_ops_with_ipex_kmajor_marlin_weights(e):
     w2, s2 = int4.to_kmajor(int4.pack_nmajor_i32(c["q2"]), c["s2"], marlin=True)
     out = e.moe_prefill_full_int4(c["x"].to(DEV), c["logits"].to(DEV), w13.to(DEV), s13.to(DEV), w2.to(DEV), s2.to(DEV), 2, 8)
     # three 16-bit roundings sit between the stages, hence the wider gate for the whole pipeline
-    assert_close(out, ref.float(), tol=3e-2, what="moe kmajor marlin")
+    assert_close(out, ref.float(), tol=1e-2, what="moe kmajor marlin")
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 128), (300, 384, 512), (1000, 1000, 1024), (64, 256, 5120)])
