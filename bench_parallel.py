@@ -126,8 +126,9 @@ def tp_case(M, rank, world, dev, P, be):
         stack = _tp_stack(world, layers, dev, g, P)
         us = measure(stack, reducer.reduce, world, getattr(reducer, "row_linear", None))
         us_nosum = measure(stack, lambda t, group=None: t, world)
-        if isinstance(reducer, P.OverlappedReducer):
-            rec["us_per_layer_unchunked_all_reduce"] = round(measure(stack, P.NcclReducer().reduce, world), 1)
+        if M >= 512:
+            ov = P.OverlappedReducer()
+            rec["us_per_layer_chunked_all_reduce_under_next_gemm"] = round(measure(stack, ov.reduce, world, ov.row_linear), 1)
         if isinstance(reducer, P.PeerReducer):
             # for comparison: the same sharded kernels with the process group's all-reduce, and with the two-step form
             # of this library's reduction fed by the GEMM epilogue (the default form for up to four ranks is one step
@@ -167,7 +168,8 @@ def ep_case(rank, world, dev, P, be):
         return x, logits, w13, s13, w2, s2
 
     a1 = build(1, 0)
-    us1 = _timed(lambda i: P.ep_moe_forward(*a1, k, E, be, world=1), 8, 3, 1)
+    import custom_esimd_kernels_vllm as pkg
+    us1 = _timed_graph(lambda i: pkg.moe_prefill_full_int4(*a1, k, E), 2, 10, 1)      # the one-GPU pipeline op, as a graph too
     del a1
     torch.cuda.empty_cache()
     rec = {"case": "ep_c4_moe_int4_t4096", "n_gpus": world, "parallelism": f"ep{world}", "one_gpu_us": round(us1, 1)}
@@ -175,7 +177,10 @@ def ep_case(rank, world, dev, P, be):
         a = build(world, rank)
         ex = P.EpExchange(T // world * k, H, torch.bfloat16, dev)
         fwd = lambda marks=None: P.ep_moe_forward_device(*a, k, E, be, ex, marks=marks)
-        us = _timed(lambda i: fwd(), 8, 3, world)
+        # nothing in this pass reads a count on the host, so a serving engine can replay it as a CUDA graph
+        us = _timed_graph(lambda i: fwd(), 2, 10, world)
+        rec["launch"] = "two passes captured in one CUDA graph, exchange included; every replay one sample"
+        rec["us_eager"] = round(_timed(lambda i: fwd(), 8, 3, world), 1)
         # for comparison: the same pass with the process group's all-to-all, whose row counts go through the host
         rec["us_nccl_all_to_all_host_counts"] = round(_timed(lambda i: P.ep_moe_forward(*a, k, E, be), 8, 3, world), 1)
         # time inside the exchange steps: events at the phase boundaries of a few further passes
@@ -191,6 +196,7 @@ def ep_case(rank, world, dev, P, be):
             spans["dispatch"].append(evs["dispatch_begin"].elapsed_time(evs["dispatch_end"]) * 1e3)
             spans["combine"].append(evs["combine_begin"].elapsed_time(evs["combine_end"]) * 1e3)
         ex_us = _max_over_ranks(statistics.median(spans["dispatch"]) + statistics.median(spans["combine"]), world)
+        # the spans include the wait for the slowest rank's rows (ranks drift apart between the synchronised passes)
         rec.update(us=round(us, 1), exchange_us=round(ex_us, 1),
                    exchange="rows and expert indices to the owners (dispatch), results back (combine): " + ex.describe(),
                    exchange_status=ex.status(),

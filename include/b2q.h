@@ -334,8 +334,8 @@ B2Q_API int b2q_moe_gemm_fp8(const void* x, int act_dtype, int64_t ldx,
  *   B2Q_COMM_ONE_STEP   every rank stores its whole tile into every rank's buffer and every rank adds the world
  *                       tiles itself (rank order, fp32): one trip over the links instead of two, world - 1 times
  *                       the bytes; needs N <= 65536
- *   B2Q_COMM_AUTO       one step for world <= 4 and max_rows <= 256 (decode tiles), two steps otherwise;
- *                       b2q_comm_create uses this                                                        */
+ *   B2Q_COMM_AUTO       one step while (world - 1) * max_rows * max_cols * 2 bytes <= 8 MiB (decode tiles on
+ *                       any number of ranks), two steps otherwise; b2q_comm_create uses this             */
 #define B2Q_COMM_AUTO 0
 #define B2Q_COMM_ONE_STEP 1
 #define B2Q_COMM_TWO_STEPS 2

@@ -12,7 +12,7 @@
 //   2. rank j waits for the W flags of a column block, adds the W slots in rank order in fp32 (every rank therefore
 //      computes bit-identical sums), rounds once, writes the block into the result area of EVERY rank, raises
 //      flag2[j][block] there, and waits for the W flags of its own result.
-// one step (W <= 4 and decode-sized tiles, where the time is latency, not bytes: one trip over NVLink instead of two):
+// one step (decode-sized tiles, where the time is latency, not bytes: one trip over NVLink instead of two):
 //   1. rank r writes its WHOLE partial tile into slot r of every rank's buffer and raises flag1[r][block] there
 //   2. every rank waits for the W flags of a column block and adds the W slots in rank order in fp32 into its own
 //      result area: all ranks add the same values in the same order, so the results are bit-identical here too.
@@ -202,8 +202,10 @@ int b2q_comm_create_mode(int rank, int world, int64_t max_rows, int64_t max_cols
   if (world < 1 || world > PR_MAX_WORLD || rank < 0 || rank >= world) return B2Q_ERR_SHAPE;
   if (max_rows <= 0 || max_cols <= 0 || (max_cols % (world * 8)) != 0) return B2Q_ERR_SHAPE;
   if (mode < B2Q_COMM_AUTO || mode > B2Q_COMM_TWO_STEPS) return B2Q_ERR_SHAPE;
-  // one step while every rank's whole tile to every peer is still a few microseconds of NVLink time
-  const bool oneshot = mode == B2Q_COMM_ONE_STEP || (mode == B2Q_COMM_AUTO && world <= 4 && max_rows <= 256);
+  // one step while every rank's whole tile to every peer is still a few microseconds of NVLink time (8 MiB out per
+  // rank at most): decode tiles on any number of ranks of a box
+  const bool oneshot = mode == B2Q_COMM_ONE_STEP ||
+                       (mode == B2Q_COMM_AUTO && (int64_t)(world - 1) * max_rows * max_cols * 2 <= ((int64_t)8 << 20));
   if (((oneshot ? max_cols : max_cols / world) + PR_CB - 1) / PR_CB > PR_MAX_BLOCKS || max_rows > 4096) return B2Q_ERR_LIMIT;
   PeerComm* c = new (std::nothrow) PeerComm();
   if (!c) return B2Q_ERR_CUDA;

@@ -171,8 +171,8 @@ class PeerReducer:
     reduce(t) returns a view of the communicator's result area, valid until the next call but one."""
 
     def __init__(self, M, N, dtype, device, group=None, mode=0):
-        """mode: _lib.COMM_AUTO (one step over the links for up to four ranks, two steps beyond), COMM_ONE_STEP or
-        COMM_TWO_STEPS; the same on every rank."""
+        """mode: _lib.COMM_AUTO (one step over the links while a rank sends 8 MiB at most, i.e. for decode tiles; two
+        steps beyond), COMM_ONE_STEP or COMM_TWO_STEPS; the same on every rank."""
         import ctypes as C
         from . import _lib as L
         self.L, self.C = L, C
@@ -236,7 +236,7 @@ class PeerReducer:
         return int(v.value)
 
     def describe(self):
-        one = self.mode == 1 or (self.mode == 0 and self.world <= 4 and self.M <= 256)
+        one = self.mode == 1 or (self.mode == 0 and (self.world - 1) * self.M * self.N * 2 <= (8 << 20))
         form = ("every rank stores its tile into every rank's buffer, every rank adds (one trip over NVLink)" if one else
                 "reduce-scatter then broadcast (two trips over NVLink)")
         return "b2q_allreduce_sum: one kernel, plain peer stores, " + form + ", tiles added in rank order (fp32), bounded flag waits"
@@ -253,7 +253,10 @@ class OverlappedReducer:
     latency: the tokens are cut into chunks, and while the GEMM of chunk i + 1 runs on the caller's stream the
     process group's all-reduce of chunk i runs on a second stream (NCCL over NVLink, a few tens of CTAs).  The weights
     of a rank's shard are re-read once per chunk (from L2 where the shard fits).  The results are those of the
-    unchunked form: every output row depends on its own token only and the all-reduce adds the same values."""
+    unchunked form: every output row depends on its own token only and the all-reduce adds the same values.
+    Measured on the Llama-70B-shape layer at 2048 tokens: level with the plain all-reduce on two GPUs (1970 against
+    1994 us per layer), slower on four and eight (1490 against 1223, 1169 against 930): 512-token GEMMs run at a lower
+    rate than one 2048-token GEMM and the all-reduce's CTAs take SMs from them.  Opt-in only."""
 
     def __init__(self, chunks=4, min_chunk_rows=256, group=None):
         from . import _impl
@@ -287,8 +290,9 @@ class OverlappedReducer:
 
 def make_reducer(M, N, dtype, device, group=None, kind=None, mode=0):
     """The object whose reduce(t) sums a [M, N] partial result over the ranks of `group`: this library's peer-memory
-    kernel for decode-sized tiles on CUDA devices, the process group's all-reduce otherwise, chunked and overlapped
-    with the GEMM for prefill-sized tiles (kind / B2Q_REDUCER = "peer", "overlap" or "nccl" forces one)."""
+    kernel for decode-sized tiles on CUDA devices, the process group's all-reduce otherwise (kind / B2Q_REDUCER =
+    "peer", "nccl" or "overlap" forces one; "overlap" = OverlappedReducer, which measured slower than the plain
+    all-reduce on 4 and 8 GPUs and is therefore never chosen by default)."""
     import os
     kind = kind or os.environ.get("B2Q_REDUCER")
     world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -297,7 +301,7 @@ def make_reducer(M, N, dtype, device, group=None, kind=None, mode=0):
         if cuda and world > 1 and world <= 8 and M <= 64 and N % (8 * world) == 0:
             kind = "peer"
         else:
-            kind = "overlap" if (cuda and world > 1 and M >= 512) else "nccl"
+            kind = "nccl"
     if kind == "peer" and cuda and world > 1:
         return PeerReducer(M, N, dtype, device, group, mode)
     if kind == "overlap" and cuda and world > 1:
