@@ -17,6 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 OUT = os.path.join(HERE, "custom_esimd_kernels_vllm", "libb2q.so")
+OUT_TORCH = os.path.join(HERE, "custom_esimd_kernels_vllm", "libb2q_torch.so")
 INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 
 NVCC_FLAGS = [
@@ -71,7 +72,33 @@ def build(force=False, verbose=False):
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
+    build_torch_ops(force or bool(jobs))
     return OUT
+
+
+def build_torch_ops(force=False):
+    """libb2q_torch.so: the C++ torch-op registration of the dense linears (csrc/torch_ops.cpp) over libb2q.so.
+    Host code only: compiled with g++ against the installed torch's headers and linked with its libraries."""
+    src = os.path.join(CSRC, "torch_ops.cpp")
+    hdr = os.path.join(INCLUDE, "b2q.h")
+    if not force and os.path.exists(OUT_TORCH) and os.path.getmtime(OUT_TORCH) >= max(os.path.getmtime(src), os.path.getmtime(hdr), os.path.getmtime(OUT)):
+        return OUT_TORCH
+    import torch
+    tdir = os.path.dirname(torch.__file__)
+    cuda_home = os.environ.get("CUDA_HOME") or os.path.dirname(os.path.dirname(_nvcc()))
+    gxx = os.environ.get("CXX") or shutil.which("g++")
+    if not gxx:
+        raise RuntimeError("g++ not found; libb2q_torch.so cannot be built")
+    cmd = [gxx, "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+           "-I", INCLUDE, "-I", os.path.join(tdir, "include"), "-I", os.path.join(tdir, "include", "torch", "csrc", "api", "include"),
+           "-I", os.path.join(cuda_home, "include"), src, "-o", OUT_TORCH,
+           "-L", os.path.dirname(OUT), "-l:libb2q.so", "-L", os.path.join(tdir, "lib"), "-ltorch", "-ltorch_cpu", "-ltorch_cuda",
+           "-lc10", "-lc10_cuda", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
+    return OUT_TORCH
 
 
 if __name__ == "__main__":

@@ -9,6 +9,9 @@ csrc/moe_batch/moe_int4.sycl:3896-3937) so that callers written against
 registers them for the XPU key; here the implementation key is CUDA.  Dense ops keep the
 reference's alias-return convention: the caller pre-allocates `output` and gets it back.
 """
+import ctypes
+import os
+
 import torch
 
 from . import _impl as I
@@ -16,6 +19,19 @@ from . import _lib as L
 
 _LIBS = {}
 IMPLEMENTED = {}      # namespace -> names of the ops registered with an implementation
+
+# The dense linears are implemented for the CUDA key in C++ (csrc/torch_ops.cpp -> libb2q_torch.so, straight over the
+# C ABI): loading that library registers them, and the Python implementations below are then not attached to those
+# names.  B2Q_PYTHON_DISPATCH=1 keeps every op on its Python implementation (the two must agree; a test runs both).
+CPP_OPS = frozenset()
+_CPP_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libb2q_torch.so")
+if os.environ.get("B2Q_PYTHON_DISPATCH") != "1":
+    if not os.path.exists(_CPP_PATH):
+        raise ImportError("b2q: %s is missing; build it with `python llm-scaler_b200/build.py`" % _CPP_PATH)
+    torch.ops.load_library(_CPP_PATH)
+    _h = ctypes.CDLL(_CPP_PATH)
+    _h.b2q_torch_ops.restype = ctypes.c_char_p
+    CPP_OPS = frozenset(_h.b2q_torch_ops().decode().split(","))
 
 
 def _lib(ns):
@@ -29,7 +45,8 @@ def _op(ns, schema, fn, meta=None):
     lib.define(schema)
     name = schema.split("(", 1)[0]
     IMPLEMENTED.setdefault(ns, []).append(name)
-    lib.impl(name, fn, "CUDA")
+    if not (ns == "custom_esimd_kernels_vllm" and name in CPP_OPS):
+        lib.impl(name, fn, "CUDA")
     if meta is not None:
         lib.impl(name, meta, "Meta")
 

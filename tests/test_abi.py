@@ -133,3 +133,23 @@ def test_whole_reference_op_surface_is_registered(lib_built):
     with pytest.raises(RuntimeError, match="b2q: custom_esimd_kernels_vllm::esimd_rms_norm not implemented"):
         torch.ops.custom_esimd_kernels_vllm.esimd_rms_norm(x, x, x[0], 1e-6)
     assert getattr(pkg.moe_ops, "moe_forward_full_v2", None) is not None
+
+
+def test_cpp_op_library_loads_and_registers_the_dense_linears(lib_built):
+    """libb2q_torch.so (csrc/torch_ops.cpp) carries the CUDA-key implementations of the dense linears; the Python
+    registration leaves exactly those names to it.  No compute call here."""
+    import torch
+    import custom_esimd_kernels_vllm as pkg
+    from custom_esimd_kernels_vllm import _register as R
+    assert os.path.exists(R._CPP_PATH)
+    assert R.CPP_OPS == {"esimd_gemv_int4", "esimd_gemm_int4_pgrp", "esimd_gemv_fp8_pern", "esimd_gemv_fp8_pert",
+                         "esimd_gemv_fp8_pert_bmg", "esimd_gemm_fp8_pert", "esimd_gemm_fp8_blockscale"}
+    for name in R.CPP_OPS:
+        assert name in R.IMPLEMENTED["custom_esimd_kernels_vllm"]
+        assert torch._C._dispatch_has_kernel_for_dispatch_key("custom_esimd_kernels_vllm::" + name, "CUDA")
+    # a CPU tensor is refused by the dispatcher or by the op itself, never computed
+    import pytest
+    x = torch.zeros(1, 128, dtype=torch.bfloat16)
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        torch.ops.custom_esimd_kernels_vllm.esimd_gemv_int4(x, torch.zeros(8, 64, dtype=torch.uint8), torch.zeros(8, 1, dtype=torch.bfloat16),
+                                                            torch.zeros(1, 8, dtype=torch.bfloat16))

@@ -404,3 +404,30 @@ def test_fp8_weight_quantisers_bit_exact(e, N, K, dtype, golden):
         wq, ws = I_.quantize_fp8(torch.from_numpy(gg["w"]).to(DEV), L.SCALE_BLOCK128)
         assert torch.equal(ws.cpu(), torch.from_numpy(gg["ws"]))
         assert torch.equal(wq.cpu().view(torch.uint8), torch.from_numpy(gg["wq"]))
+
+
+def test_cpp_and_python_dispatch_agree(e):
+    """The dense linears reach the C ABI through the C++ registration (torch.ops) and, inside the package, through the
+    Python host functions (_impl): same checks, same launches, bit-identical results; a shape error is a RuntimeError
+    on both routes."""
+    g = torch.Generator().manual_seed(11)
+    N, K, M = 384, 512, 5
+    q = torch.randint(0, 16, (N, K), generator=g, dtype=torch.uint8)
+    s = (0.01 + torch.rand(N, K // 128, generator=g) * 0.02).to(torch.bfloat16).to(DEV)
+    w = int4.pack_nmajor_i32(q).to(DEV)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(DEV)
+    a, b = torch.empty(M, N, dtype=torch.bfloat16, device=DEV), torch.empty(M, N, dtype=torch.bfloat16, device=DEV)
+    torch.ops.custom_esimd_kernels_vllm.esimd_gemm_int4_pgrp(x, w, s, a)
+    e._impl.linear_int4(x, w, s, b)
+    assert torch.equal(a, b)
+    torch.ops.custom_esimd_kernels_vllm.esimd_gemm_int4_pgrp(x, w.t(), s, a)            # the transposed alias of the same bytes
+    assert torch.equal(a, b)
+    wq = torch.randint(0, 120, (N, K), generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn).to(DEV)
+    sc = (0.5 + torch.rand(N, generator=g)).to(DEV)
+    torch.ops.custom_esimd_kernels_vllm.esimd_gemv_fp8_pern(x, wq, sc, a, N, K)
+    e._impl.linear_fp8(x, wq, sc, b, e._lib.SCALE_CHANNEL, N, K)
+    assert torch.equal(a, b)
+    with pytest.raises(RuntimeError):
+        torch.ops.custom_esimd_kernels_vllm.esimd_gemv_fp8_pern(x, wq, sc, a, N + 1, K)
+    with pytest.raises(RuntimeError):
+        torch.ops.custom_esimd_kernels_vllm.esimd_gemm_int4_pgrp(x[:, :256], w, s, a)
