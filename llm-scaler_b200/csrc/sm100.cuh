@@ -77,6 +77,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// After a give-up: copies this producer has issued may still be landing in shared memory.  Waits, each wait bounded
+// to about a millisecond, for the barriers of the last `depth` stages it armed (issue number i used barrier
+// full0 + 8 * (i % depth) in phase (i / depth) & 1), so that the CTA does not free its tensor memory and hand its
+// shared memory to the next CTA with copies of its own still in flight.  Failure path only.
+__device__ __forceinline__ void drain_issued(uint32_t full0, int depth, int issued, long long limit_ticks = 2000000) {
+  const int n = issued < depth ? issued : depth;
+  for (int i = issued - n; i < issued; ++i) {
+    const uint32_t bar = full0 + 8 * (uint32_t)(i % depth), parity = (uint32_t)((i / depth) & 1);
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+      if (clock64() - t0 > limit_ticks) break;
+    }
+  }
+}
+
 // Whole-warp wait: lane 0 spins, the other lanes park at the shuffle, then every lane observes
 // the completed phase itself (one try_wait that succeeds at once) so each has its own acquire.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {

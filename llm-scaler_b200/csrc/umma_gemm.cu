@@ -289,12 +289,14 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     if (lane == 0) {
       tma_prefetch_desc(&tm_w);
       int grb = 0;                       // raw stages issued so far: ring position and phase carry across segments
+      int issued = 0;
       bool ok = true;
       while (ok && next_segment(sg)) {
         const int nraw = (sg.nk + CPR - 1) / CPR;
         for (int r = 0; r < nraw; ++r) {
           const int gr = grb + r, rs = gr % RS;
           { if (gr >= RS && !mbar_wait(raw_empty + 8 * rs, ((gr / RS) - 1) & 1, abort_flag, p.status, ST_RAWEMPTY)) { ok = false; break; } }
+          issued = gr + 1;
           mbar_expect_tx(raw_full + 8 * rs, Cfg::RAW_BYTES);
           if constexpr (WK == WK_W4K)
             tma_load_2d(raw_smem + rs * Cfg::RAW_BYTES, &tm_w, sg.n0, expert * p.w_rows_per_expert + (sg.c_begin / CPR + r) * 32, raw_full + 8 * rs);
@@ -303,23 +305,26 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         }
         grb += nraw;
       }
+      if (!ok) drain_issued(raw_full, RS, issued);
     }
   } else if (warp == 2) {
     // ---------------- activation producer ----------------
     if (lane == 0) {
       tma_prefetch_desc(&tm_x);
       if (!p.tiles) grid_dep_wait();
-      int gb = 0;
+      int gb = 0, issued = 0;
       bool ok = true;
       while (ok && next_segment(sg)) {
         for (int c = 0; c < sg.nk; ++c) {
           const int g = gb + c, s = g % XS;
           { if (g >= XS && !mbar_wait(x_empty + 8 * s, ((g / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; } }
+          issued = g + 1;
           mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
           tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, (sg.c_begin + c) * 64, xrow0 + tok0, x_full + 8 * s);
         }
         gb += sg.nk;
       }
+      if (!ok) drain_issued(x_full, XS, issued);
     }
   } else if (warp == 1 || (Cfg::NMMA == 2 && warp == 3)) {
     // ---------------- MMA issuer(s) ----------------

@@ -143,6 +143,7 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tma_load_2d(raw_smem + rs * C::RAW_BYTES, &tm_w, (g >> 1) * 128, sg.n0, raw_full + 8 * rs);
         }
       }
+      if (!ok) drain_issued(raw_full, RS, gr);
     }
   } else if (warp == 2) {
     // ---- activation producer: the NTOK term rows of one group per stage ----
@@ -161,6 +162,7 @@ umma_w4_i8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constan
           tma_load_2d(x_smem + s * C::X_BYTES, &tm_x, g * 128, 0, x_full + 8 * s);
         }
       }
+      if (!ok) drain_issued(x_full, XS, gc);
     }
   } else if (warp == 1) {
     // ---- MMA issuer: one group (128 k) = four MMAs into that group's own accumulator ----

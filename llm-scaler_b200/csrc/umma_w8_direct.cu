@@ -139,6 +139,7 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           tma_load_2d(base + s * C::STAGE, &tm_w, r * 128, sg.n0, full + 8 * s);
         }
       }
+      if (!ok) drain_issued(full, NS, g);
     }
   } else if (warp == 2) {
     // ---- activation producer: the NTOK term rows of the same 128 k ----
@@ -157,6 +158,7 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
           tma_load_2d(base + s * C::STAGE + C::W_BYTES, &tm_x, r * 128, 0, full + 8 * s);
         }
       }
+      if (!ok) drain_issued(full, NS, g);
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----

@@ -82,13 +82,15 @@ umma_w8a8_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     if (lane == 0) {
       tma_prefetch_desc(&tm_w);
       tma_prefetch_desc(&tm_x);
-      for (int kb = 0; kb < nkb; ++kb) {
+      int kb = 0;
+      for (; kb < nkb; ++kb) {
         const int s = kb % S;
         if (kb >= S && !mbar_wait(empty + 8 * s, ((kb / S) - 1) & 1, abort_flag, p.status, ST_EMPTY)) break;
         mbar_expect_tx(full + 8 * s, STAGE_BYTES);
         tma_load_2d(base + s * STAGE_BYTES, &tm_w, kb * 128, n0, full + 8 * s);
         tma_load_2d(base + s * STAGE_BYTES + 16384, &tm_x, kb * 128, tok0, full + 8 * s);
       }
+      if (kb < nkb) drain_issued(full, S, kb);       // gave up: let the copies already issued land first
     }
   } else if (warp == 1) {
     if (lane == 0) {

@@ -25,7 +25,10 @@ IMPLEMENTED = {}      # namespace -> names of the ops registered with an impleme
 # names.  B2Q_PYTHON_DISPATCH=1 keeps every op on its Python implementation (the two must agree; a test runs both).
 CPP_OPS = frozenset()
 _CPP_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "libb2q_torch.so")
-if os.environ.get("B2Q_PYTHON_DISPATCH") != "1":
+# B2Q_CHECK_STATUS=1 (debugging, tests): every op synchronises after its launches and raises if a bounded device-side
+# wait has expired, instead of leaving that to a caller who polls b2q_device_status.  It implies Python dispatch.
+CHECK_STATUS = os.environ.get("B2Q_CHECK_STATUS") == "1"
+if os.environ.get("B2Q_PYTHON_DISPATCH") != "1" and not CHECK_STATUS:
     if not os.path.exists(_CPP_PATH):
         raise ImportError("b2q: %s is missing; build it with `python llm-scaler_b200/build.py`" % _CPP_PATH)
     torch.ops.load_library(_CPP_PATH)
@@ -40,11 +43,23 @@ def _lib(ns):
     return _LIBS[ns]
 
 
+def _checked(fn, what):
+    def run(*a, **k):
+        out = fn(*a, **k)
+        code = L.device_status()
+        if code:
+            raise RuntimeError("b2q: %s: a bounded device-side wait expired (code %d); results are not valid" % (what, code))
+        return out
+    return run
+
+
 def _op(ns, schema, fn, meta=None):
     lib = _lib(ns)
     lib.define(schema)
     name = schema.split("(", 1)[0]
     IMPLEMENTED.setdefault(ns, []).append(name)
+    if CHECK_STATUS:
+        fn = _checked(fn, ns + "::" + name)
     if not (ns == "custom_esimd_kernels_vllm" and name in CPP_OPS):
         lib.impl(name, fn, "CUDA")
     if meta is not None:

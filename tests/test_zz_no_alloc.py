@@ -69,3 +69,49 @@ def test_static_route_rejects_sizes_beyond_its_table(L):
     assert L.lib.b2q_moe_route_static(ids.data_ptr(), 8, 257, p, p, p, p, None) == -10
     assert L.lib.b2q_strerror(-10).startswith(b"b2q:")
     assert L.lib.b2q_moe_route_static(None, 8, 8, p, p, p, p, None) == -1
+
+
+@pytest.mark.gpu
+def test_route_static_inside_a_stream_capture_and_on_a_second_device(lib_built):
+    """The stated use: one eager call per device, then the routing sort captured into a CUDA graph on a side stream
+    and replayed with different ids; every replay must equal b2q_moe_route bit for bit.  With two GPUs visible the
+    eager comparison is repeated on cuda:1 (the scratch table's address is looked up per device)."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.fail("GPU test selected but no CUDA device is visible")
+    import custom_esimd_kernels_vllm as pkg
+    L, I = pkg._lib, pkg._impl
+    E, n = 32, 4096
+
+    def static_route(ids, outs, stream):
+        L.check(L.lib.b2q_moe_route_static(ids.data_ptr(), n, E, outs[0].data_ptr(), outs[1].data_ptr(), outs[2].data_ptr(),
+                                            outs[3].data_ptr(), stream.cuda_stream))
+
+    for dev in range(min(2, torch.cuda.device_count())):
+        d = torch.device("cuda", dev)
+        with torch.cuda.device(d):
+            g = torch.Generator(device=d).manual_seed(dev)
+            ids = torch.randint(0, E, (n, 1), generator=g, device=d, dtype=torch.int32)
+            outs = [torch.empty(E + 1, dtype=torch.int32, device=d), torch.empty(n, dtype=torch.int32, device=d),
+                    torch.empty(n, dtype=torch.int32, device=d), torch.empty(E, dtype=torch.int32, device=d)]
+            static_route(ids, outs, torch.cuda.current_stream())              # the first call on this device, eager
+            torch.cuda.synchronize()
+            for got, want in zip(outs, I.moe_route(ids, E)):
+                assert torch.equal(got, want)
+            if dev > 0:
+                continue
+            side = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    static_route(ids, outs, side)
+            for rep in range(2):
+                ids.copy_(torch.randint(0, E, (n, 1), generator=g, device=d, dtype=torch.int32))
+                for o in outs:
+                    o.fill_(-7)
+                torch.cuda.synchronize()
+                graph.replay()
+                torch.cuda.synchronize()
+                for got, want in zip(outs, I.moe_route(ids, E)):
+                    assert torch.equal(got, want), rep
