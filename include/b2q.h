@@ -155,8 +155,10 @@ B2Q_API int b2q_quantize_fp8(const void* w, int w_dtype, int64_t ldw, void* wq, 
  * of two in the element order its nibble decode produces; the dequantised weight is then
  * (q - 8) * scale rounded once to fp16 (11 significant bits) instead of to the activation type.
  * Scales of any magnitude are safe on that route: bf16 / fp32 scales are brought into fp16's normal
- * range by a power of two per output row (chosen from the row's largest scale) that is taken out
- * of the fp32 accumulator again; a group more than 2^22 below its row's largest scale loses bits.
+ * range by a power of two per output row, chosen from the row's first group of the K range a CTA
+ * works on and taken out of the fp32 accumulator again.  Groups within 2^13 of that first one, either
+ * way, are exact; a group further below loses bits, one further above is saturated and reported
+ * through b2q_device_status (code 109).
  * Without scratch the weight is rounded exactly as the torch reference rounds it.  For M <= 64
  * the scratch also holds partial sums: layers with few output rows are cut along K over several CTAs
  * per strip of rows so that they still occupy every SM; the partial sums are added in a fixed order,
