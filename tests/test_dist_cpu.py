@@ -37,12 +37,56 @@ class OracleBackend:
         xs = x[tokens.long()]
         inter = moe.silu_mul(moe.grouped_linear(xs, d13, offsets).to(x.dtype))
         ys = moe.grouped_linear(inter, d2, offsets).to(x.dtype)
-        y = torch.empty_like(ys)
+        y = torch.zeros(rows, ys.shape[1], dtype=ys.dtype)       # `rows` may be an upper bound (fixed-capacity receive area)
         y[tokens.long()] = ys
         return y
 
     def combine(self, y, weights, perm, T, k):
         return moe.combine(y, weights, perm)
+
+
+class HostExchange:
+    """Stand-in for parallel.EpExchange on CPU ranks: the same interface and the same buffer layout (a receive area
+    of world x cap rows with one slot per source rank, expert index -1 in unused positions, a return area in the
+    source's send order), moved by gloo all-to-alls.  It lets the host-side arithmetic of ep_moe_forward_device
+    (destination sort, local expert indices, upper-bound row counts, combine from the return area) run against the
+    CPU oracle; the peer-memory kernels themselves are tested on GPUs."""
+
+    def __init__(self, cap, H, dtype):
+        self.world, self.rank, self.cap = dist.get_world_size(), dist.get_rank(), cap
+        self.recv_rows = torch.zeros(self.world * cap, H, dtype=dtype)
+        self.recv_ids = torch.full((self.world * cap,), -1, dtype=torch.int32)
+        self.ret_rows = torch.zeros(cap, H, dtype=dtype)
+
+    def dispatch(self, x, order, top_k, offsets, local_ids):
+        W, cap = self.world, self.cap
+        self.sc = (offsets[1:] - offsets[:-1]).tolist()
+        sc = torch.tensor(self.sc, dtype=torch.int64)
+        rc = torch.empty_like(sc)
+        dist.all_to_all_single(rc, sc)
+        self.rc = rc.tolist()
+        rows = x[(order // top_k).long()].contiguous()
+        got = torch.empty(sum(self.rc), x.shape[1], dtype=x.dtype)
+        got_e = torch.empty(sum(self.rc), dtype=torch.int32)
+        dist.all_to_all_single(got, rows, self.rc, self.sc)
+        dist.all_to_all_single(got_e, local_ids.contiguous(), self.rc, self.sc)
+        self.recv_ids.fill_(-1)
+        at = 0
+        for s_ in range(W):
+            n = self.rc[s_]
+            self.recv_rows[s_ * cap:s_ * cap + n] = got[at:at + n]
+            self.recv_ids[s_ * cap:s_ * cap + n] = got_e[at:at + n]
+            at += n
+
+    def wait(self, phase, like):
+        pass
+
+    def give_back(self, y):
+        cap = self.cap
+        send = torch.cat([y[s_ * cap:s_ * cap + self.rc[s_]] for s_ in range(self.world)]).contiguous()
+        back = torch.empty(sum(self.sc), y.shape[1], dtype=y.dtype)
+        dist.all_to_all_single(back, send, self.sc, self.rc)
+        self.ret_rows[:back.shape[0]] = back
 
 
 def _free_port():
@@ -94,9 +138,13 @@ def _worker(rank, world, port, what, q):
             e_local = 8 // world
             sl = slice(rank * T, (rank + 1) * T)
             es = slice(rank * e_local, (rank + 1) * e_local)
-            out = P.ep_moe_forward(c["x"][sl].contiguous(), c["logits"][sl].contiguous(),
-                                   int4.pack_nmajor_i32(c["q13"][es]), c["s13"][es].contiguous(),
-                                   int4.pack_nmajor_i32(c["q2"][es]), c["s2"][es].contiguous(), 2, 8, be)
+            args = (c["x"][sl].contiguous(), c["logits"][sl].contiguous(),
+                    int4.pack_nmajor_i32(c["q13"][es]), c["s13"][es].contiguous(),
+                    int4.pack_nmajor_i32(c["q2"][es]), c["s2"][es].contiguous(), 2, 8, be)
+            if what == "ep_device":
+                out = P.ep_moe_forward_device(*args, HostExchange(T * 2, c["x"].shape[1], torch.bfloat16))
+            else:
+                out = P.ep_moe_forward(*args)
             q.put((rank, _pack(out)))
     finally:
         dist.destroy_process_group()
@@ -154,8 +202,11 @@ def test_tensor_parallel_layer_matches_unsharded(lib_built):
 
 
 @pytest.mark.timeout(300)
-def test_expert_parallel_matches_single_rank(lib_built):
-    outs = _run("ep")
+@pytest.mark.parametrize("what", ["ep", "ep_device"])
+def test_expert_parallel_matches_single_rank(lib_built, what):
+    """"ep": the all-to-all form with host counts; "ep_device": the form whose exchange keeps every count on the
+    device (fixed-capacity slots, upper-bound row counts), here over a CPU stand-in for the peer-memory kernels."""
+    outs = _run(what)
     c = configs.c4(seed=5, T=24, E=8, top_k=2, H=128, I=128)
     ref = moe.forward(c["x"], c["logits"], int4.dequant(c["q13"], c["s13"], torch.bfloat16),
                       int4.dequant(c["q2"], c["s2"], torch.bfloat16), 2)
