@@ -40,8 +40,14 @@ enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWE
 struct Segment { int n0, c_begin, nk, strip, part, slot; };
 
 // constants of the fp16 magic-number nibble decode, handed to the kernel as parameters (see w4_word_magic)
-struct MagicConsts { uint32_t m_lo, m_hi, magic, c1032, r16, m72; };
-__host__ __device__ inline MagicConsts magic_consts() { return MagicConsts{0x000F000Fu, 0x00F000F0u, 0x64006400u, 0x64086408u, 0x2C002C00u, 0xD480D480u}; }
+struct MagicConsts { uint32_t m_lo, m_hi, magic_lo, magic_hi, c1032, r16, m72; };
+// twos: the nibbles are two's complement (value, not value + 8).  Flipping their sign bits gives the offset form; the
+// flip is folded into the constant that is merged in: (w & m) ^ (0x6400 ^ flip) is 0x6400 | ((w ^ flip) & m) because
+// the 0x6400 bits and the nibble bits do not overlap.  No extra operation, no branch in the decode.
+__host__ __device__ inline MagicConsts magic_consts(bool twos) {
+  return MagicConsts{0x000F000Fu, 0x00F000F0u, 0x64006400u ^ (twos ? 0x00080008u : 0u), 0x64006400u ^ (twos ? 0x00800080u : 0u),
+                     0x64086408u, 0x2C002C00u, 0xD480D480u};
+}
 
 struct UmmaWoParams {
   const void* scale; int scale_dtype; int scale_mode;      // scale_mode: B2Q_SCALE_* (fp8) ; ignored for int4
@@ -125,14 +131,23 @@ __device__ __forceinline__ void w4_word(uint32_t w, uint32_t s2, float sf, bool 
 // compiler folds them into immediates, and since an instruction takes one immediate at most it then spends two logic
 // operations per mask-and-or and a register move per fused multiply-add (measured: 82 logic operations and 61 moves
 // per 64 k of a row where 32 and a handful are needed).
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {      // (a & b) | c in one operation
+__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t b, uint32_t c) {      // (a & b) ^ c in one operation
   uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
   return d;
+}
+// a, b, c or d for i = 0, 1, 2, anything else: three compares and three selects, never a branch (written as a
+// conditional expression the selection of a chunk's prefetched scale became a jump table with a dozen register moves)
+__device__ __forceinline__ uint32_t sel4(int i, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  uint32_t r;
+  asm("{\n\t.reg .pred p0, p1, p2;\n\tsetp.eq.s32 p0, %1, 0;\n\tsetp.eq.s32 p1, %1, 1;\n\tsetp.eq.s32 p2, %1, 2;\n\t"
+      "selp.u32 %0, %4, %5, p2;\n\tselp.u32 %0, %3, %0, p1;\n\tselp.u32 %0, %2, %0, p0;\n\t}"
+      : "=&r"(r) : "r"(i), "r"(a), "r"(b), "r"(c), "r"(d));
+  return r;
 }
 __device__ __forceinline__ void w4_word_magic(uint32_t w, uint32_t s2, const MagicConsts& k, uint32_t (&o)[4]) {
   const uint32_t w8 = w >> 8;
-  uint32_t v[4] = {and_or(w, k.m_lo, k.magic), and_or(w, k.m_hi, k.magic), and_or(w8, k.m_lo, k.magic), and_or(w8, k.m_hi, k.magic)};
+  uint32_t v[4] = {and_xor(w, k.m_lo, k.magic_lo), and_xor(w, k.m_hi, k.magic_hi), and_xor(w8, k.m_lo, k.magic_lo), and_xor(w8, k.m_hi, k.magic_hi)};
   const __half2 sc = *reinterpret_cast<const __half2*>(&s2);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -391,9 +406,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     };
     auto scale_value = [&](uint32_t raw) -> float {
       if constexpr (WK == WK_W4N || WK == WK_W4K) {
-        if (p.scale_dtype == B2Q_F32) return __uint_as_float(raw);
-        if (p.scale_dtype == B2Q_BF16) return __uint_as_float(raw << 16);
-        return __half2float(__ushort_as_half((unsigned short)raw));
+        // all three readings, then two selects: no branch per chunk
+        const float as_f32 = __uint_as_float(raw), as_bf16 = __uint_as_float(raw << 16);
+        const float as_f16 = __half2float(__ushort_as_half((unsigned short)raw));
+        return p.scale_dtype == B2Q_F32 ? as_f32 : (p.scale_dtype == B2Q_BF16 ? as_bf16 : as_f16);
       } else {
         return __uint_as_float(raw);
       }
@@ -404,6 +420,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
              sn3 = chunk_scale_raw(grp + 7 * NG);
     int it4 = 0;                                   // position of the current chunk in its set of four
     int pend = -1;                                 // MAGIC: operand stage whose tensor-memory stores are still in flight
+    int saturated = 0;                             // MAGIC: a scale had to be clamped (reported once, behind the loop)
     // fp16 magic route with bf16 / fp32 scales: the group scale is rounded to fp16, whose normal range starts at
     // 6.1e-5.  Every row of a segment therefore carries its own power of two, taken from the scale of the segment's
     // first group: the row's scales are multiplied by 2^row_e so that this first one lands in [0.5, 1), and the fp32
@@ -430,7 +447,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
         sn0 = chunk_scale_raw(c + 4 * NG); sn1 = chunk_scale_raw(c + 5 * NG);
         sn2 = chunk_scale_raw(c + 6 * NG); sn3 = chunk_scale_raw(c + 7 * NG);
       }
-      const uint32_t sr_cur = it4 == 0 ? sq0 : (it4 == 1 ? sq1 : (it4 == 2 ? sq2 : sq3));
+      const uint32_t sr_cur = sel4(it4, sq0, sq1, sq2, sq3);
       ++it4;
       const int r = c / CPR, j = c % CPR;
       const int gr = grb + r, rs = gr % RS;
@@ -449,13 +466,11 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           // all 64 values of a row live at once the loop ran out of registers, and the decode's masks and fp16
           // constants were re-created for every use.
           float ss = sc_cur * row_mul;
-          if (fabsf(ss) > 8188.f) {              // 8 * scale would leave fp16: saturate, and say so
-            ss = copysignf(8188.f, ss);
-            atomicCAS(p.status, 0, ST_SCALERANGE);
-          }
+          const bool too_big = fabsf(ss) > 8188.f;            // 8 * scale would leave fp16: saturate, and say so (after the loop)
+          ss = too_big ? copysignf(8188.f, ss) : ss;
+          saturated |= too_big ? 1 : 0;
           const uint32_t hv = __half_as_ushort(__float2half_rn(ss));
           const uint32_t m2 = hv | (hv << 16);
-          const bool twos = p.xor_mask != 0;       // two's-complement nibbles: flip the sign bits into offset form
           const MagicConsts mk = p.mk;
 #pragma unroll
           for (int hf = 0; hf < 2; ++hf) {
@@ -467,7 +482,6 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
               w0 = lds32(rawcol + (8 * j + 4 * hf + 0) * 512); w1 = lds32(rawcol + (8 * j + 4 * hf + 1) * 512);
               w2 = lds32(rawcol + (8 * j + 4 * hf + 2) * 512); w3 = lds32(rawcol + (8 * j + 4 * hf + 3) * 512);
             }
-            if (twos) { w0 ^= 0x88888888u; w1 ^= 0x88888888u; w2 ^= 0x88888888u; w3 ^= 0x88888888u; }
             uint32_t a16[16];
             { uint32_t o[4]; w4_word_magic(w0, m2, mk, o); a16[0] = o[0]; a16[1] = o[1]; a16[2] = o[2]; a16[3] = o[3]; }
             { uint32_t o[4]; w4_word_magic(w1, m2, mk, o); a16[4] = o[0]; a16[5] = o[1]; a16[6] = o[2]; a16[7] = o[3]; }
@@ -550,6 +564,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       if (c + NG >= nk || (c + NG) / CPR != r) mbar_arrive(raw_empty + 8 * rs);
     }
     if (pend >= 0) { tmem_st_wait(); tc_fence_before(); mbar_arrive(a_full + 8 * pend); pend = -1; }
+    if (saturated) atomicCAS(p.status, 0, ST_SCALERANGE);
     if (!ok) break;
 
     // ---------------- epilogue of this segment ----------------
@@ -954,7 +969,7 @@ int umma_w4_linear(const UmmaW4Args& a, cudaStream_t st) {
   p.tiles = grouped ? a.tiles : nullptr; p.expert_offsets = a.expert_offsets; p.out_map = a.out_map;
   p.w_rows_per_expert = kmajor ? a.K / 8 : a.N;
   p.tok_scale = a.tok_scale; p.out_bf16 = a.out_bf16 ? 1 : 0; p.magic = a.magic ? 1 : 0;
-  p.mk = magic_consts();
+  p.mk = magic_consts(p.xor_mask != 0);
   p.status = status_ptr();
   p.overlap_ok = (a.after_prep || tls().overlap_mode == 2) ? 1 : 0;
   p.sk_grid = plan_balanced(p, a, a.M, a.N, a.K, 4, tok);
