@@ -699,7 +699,9 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const int64_t U = p.sk_units, G = gridDim.x;
       const int64_t us = (int64_t)sg.strip * p.sk_sps, ue = us + p.sk_sps - 1;
       const int b_lo = (int)(((us + 1) * G + U - 1) / U) - 1, b_hi = (int)(((ue + 1) * G + U - 1) / U) - 1;
-      __threadfence();
+      // the barrier hands every thread's partial sums to the leader (release / acquire at CTA scope); the leader's one
+      // device-scope fence then orders all of them before the count.  A fence per thread in front of the barrier adds
+      // nothing to that and cost 0.7 % of a decode layer.
       mbar_arrive(fix_bar);
       ok = mbar_wait(fix_bar, fixn & 1, abort_flag, p.status, ST_FIXUP); ++fixn;
       if (!ok) break;

@@ -245,8 +245,7 @@ umma_w8_direct_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_con
         const int64_t U = p.units, G = gridDim.x;
         const int64_t us = (int64_t)sg.strip * p.sps, ue = us + p.sps - 1;
         const int b_lo = (int)(((us + 1) * G + U - 1) / U) - 1, b_hi = (int)(((ue + 1) * G + U - 1) / U) - 1;
-        __threadfence();
-        mbar_arrive(fix_bar);
+        mbar_arrive(fix_bar);          // hands this thread's partial sums to the leader, whose fence orders them before the count
         ok = mbar_wait(fix_bar, fixn & 1, abort_flag, p.status, ST_FIXUP); ++fixn;
         if (!ok) break;
         if (threadIdx.x == 3 * 32) {
