@@ -472,7 +472,8 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       const uint32_t rawcol = raw_smem + rs * Cfg::RAW_BYTES + t * 4;       // K-major: this thread's column
       {
         const int g = gb + c, s = g % S;
-        if (g >= S) { ok = mbar_wait(ab_empty + 8 * s, ((g / S) - 1) & 1, abort_flag, p.status, ST_EMPTY); if (!ok) break; }
+        // no test for the ring's first round: a wait for the phase before a fresh barrier's first one returns at once
+        { ok = mbar_wait(ab_empty + 8 * s, ((g / S) + 1) & 1, abort_flag, p.status, ST_EMPTY); if (!ok) break; }
         tc_fence_after();
         const uint32_t ta = tmem + ((uint32_t)((warp & 3) * 32) << 16) + Cfg::A_COL0 + 32 * s;
         if constexpr (MAGIC) {
