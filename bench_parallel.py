@@ -129,6 +129,8 @@ def tp_case(M, rank, world, dev, P, be):
         if M >= 512:
             ov = P.OverlappedReducer()
             rec["us_per_layer_chunked_all_reduce_under_next_gemm"] = round(measure(stack, ov.reduce, world, ov.row_linear), 1)
+            oc = P.OverlappedReducer(chunks=2, split="columns")
+            rec["us_per_layer_all_reduce_by_2_column_blocks_under_next_block"] = round(measure(stack, oc.reduce, world, oc.row_linear), 1)
         if isinstance(reducer, P.PeerReducer):
             # for comparison: the same sharded kernels with the process group's all-reduce, and with the two-step form
             # of this library's reduction fed by the GEMM epilogue (the default form for up to four ranks is one step

@@ -46,9 +46,8 @@ def _worker(rank, world, port, what, q):
                 out = P.tp_layer_forward(full["x"].to(dev), layer, be)
             elif what == "tp_overlap":
                 # the prefill form: token chunks, the all-reduce of a chunk on a second stream under the next chunk's GEMM
-                red = P.OverlappedReducer(chunks=3, min_chunk_rows=8)
                 x = full["x"].to(dev)
-                for _ in range(2):
+                for red in (P.OverlappedReducer(chunks=3, min_chunk_rows=8), P.OverlappedReducer(chunks=2, split="columns")):
                     out = P.tp_layer_forward(x, layer, be, reduce=red.reduce, row_linear=red.row_linear)
             else:
                 # the library's own exchange: peer-memory reduction kernel, alone ("tp_peer": the default form for two
