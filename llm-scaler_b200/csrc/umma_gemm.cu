@@ -185,7 +185,9 @@ template <int TOK> struct UmmaCfg {
   // of six (fp8) to ten (int4) times, which is what capped the shared-memory variant near 3 TB/s.
   static constexpr int NG = 2;                                       // transform groups of 4 warps
   static constexpr int CTAS = TOK <= 128 ? 2 : 1;                    // two CTAs per SM except for the 256-token prefill tile: a second CTA hides fill and epilogue of short K loops (MoE) and doubles the issuers for decode
-  static constexpr int XS = TOK <= 64 ? 6 : (TOK == 128 ? 4 : 5);    // activation stages (64 k each)
+  // activation stages (64 k each).  Up to 128 tokens there are as many as operand stages, and one barrier per stage
+  // releases both (see SHARED_EMPTY in the kernel): one tcgen05.commit less per chunk for the issuing thread.
+  static constexpr int XS = TOK <= 128 ? 4 : 5;
   // Issuing tcgen05.mma is a serial job of one thread and costs it several hundred cycles per 64-k
   // chunk regardless of the tile width; decode tiles therefore use two issuer warps on alternate
   // chunks, each with its own accumulator (summed in the epilogue).
@@ -216,6 +218,10 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
   constexpr int S = Cfg::S, RS = Cfg::RS, NG = Cfg::NG, XS = Cfg::XS;
   constexpr int CPR = (WK == WK_W8) ? 2 : 4;          // 64-k chunks per raw stage
   constexpr int GPR = CPR < NG ? CPR : NG;            // transform groups that touch one raw stage
+  // With equally deep rings chunk g uses operand stage g % S and activation stage g % XS = the same index, and the MMAs
+  // that free one free the other: the activation producer waits on the operand stage's barrier, the issuer commits once
+  // (MoE pipeline 676 -> 664 us; the decode tiles are indifferent).
+  constexpr bool SHARED_EMPTY = S == XS;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -332,7 +338,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
       while (ok && next_segment(sg)) {
         for (int c = 0; c < sg.nk; ++c) {
           const int g = gb + c, s = g % XS;
-          { if (g >= XS && !mbar_wait(x_empty + 8 * s, ((g / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; } }
+          { if (g >= XS && !mbar_wait((SHARED_EMPTY ? ab_empty : x_empty) + 8 * s, ((g / XS) - 1) & 1, abort_flag, p.status, ST_EMPTY)) { ok = false; break; } }
           issued = g + 1;
           mbar_expect_tx(x_full + 8 * s, Cfg::X_BYTES);
           tma_load_2d(x_smem + s * Cfg::X_BYTES, &tm_x, (sg.c_begin + c) * 64, xrow0 + tok0, x_full + 8 * s);
@@ -367,7 +373,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
           mma_f16_ts(dacc, ta + 16, db + 4, idesc, 1u);
           mma_f16_ts(dacc, ta + 24, db + 6, idesc, 1u);
           tc_commit(ab_empty + 8 * s);
-          tc_commit(x_empty + 8 * xs);
+          if constexpr (!SHARED_EMPTY) tc_commit(x_empty + 8 * xs);
         }
         if (ok) tc_commit(accum_full);
         gb += sg.nk; ++si;
