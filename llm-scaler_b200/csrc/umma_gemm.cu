@@ -2,12 +2,13 @@
 //
 // The 128 weight rows of a CTA's strip are the MMA's M dimension and the tokens its N
 // dimension ("swap-AB"), so one kernel serves decode (16..64 tokens) and prefill (256-token
-// tiles).  Warp roles, one CTA of 11 warps per output tile:
+// tiles).  Warp roles, one CTA of 11 to 19 warps per output tile:
 //   warp 0     TMA producer of raw quantised weight tiles (runs up to RS stages ahead: this
 //              is the HBM stream)
 //   warp 1     tensor-memory owner and the single thread that issues tcgen05.mma
 //   warp 2     TMA producer of activation tiles [TOK x 64] (128-byte swizzle)
-//   warps 3-10 transform: raw int4 / fp8 -> 16-bit values written straight into the
+//   the rest   transform (two groups of four warps, four groups for the 256-token tile; decode tiles
+//              have a second MMA issuer in front of them): raw int4 / fp8 -> 16-bit values written straight into the
 //              128-byte-swizzled K-major operand layout the MMA reads; afterwards the same
 //              warps drain the fp32 accumulator from tensor memory, apply per-row scales and
 //              store out[tok, n].
@@ -183,7 +184,9 @@ template <int TOK> struct UmmaCfg {
   // MMA as its A operand.  Shared memory then carries only the raw quantised stream (written by TMA,
   // read once by the transform) and the activation tiles, i.e. about twice the HBM traffic instead
   // of six (fp8) to ten (int4) times, which is what capped the shared-memory variant near 3 TB/s.
-  static constexpr int NG = 2;                                       // transform groups of 4 warps
+  // transform groups of 4 warps.  The 256-token tile runs one CTA per SM: four groups give it the sixteen converting
+  // warps the narrower tiles get from two CTAs (prefill layer -3.4 %, FP8 block GEMM -2.7 %).
+  static constexpr int NG = TOK == 256 ? 4 : 2;
   static constexpr int CTAS = TOK <= 128 ? 2 : 1;                    // two CTAs per SM except for the 256-token prefill tile: a second CTA hides fill and epilogue of short K loops (MoE) and doubles the issuers for decode
   // activation stages (64 k each).  Up to 128 tokens there are as many as operand stages, and one barrier per stage
   // releases both (see SHARED_EMPTY in the kernel): one tcgen05.commit less per chunk for the issuing thread.
@@ -381,8 +384,8 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     }
   } else {
     // ---------------- transform, then epilogue (the NG x 4 warps after the control warps) ----------------
-    // Two groups of four warps; group g converts the 64-k chunks with (c & 1) == g, one weight row
-    // (N-major / fp8) or column (K-major) per thread, so two chunks are always in flight.
+    // NG groups of four warps; group g converts the 64-k chunks with c % NG == g, one weight row
+    // (N-major / fp8) or column (K-major) per thread, so NG chunks are always in flight.
     const int t = (warp & 3) * 32 + lane;        // row of the strip == tensor-memory lane this thread may write
     const int grp = (threadIdx.x - Cfg::CW * 32) >> 7;
     const int sw = t & 7;
@@ -450,7 +453,7 @@ umma_wo_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__
     // faster is a matter of what the register allocator makes of the loop, measured per tile width on one GPU: the
     // 128-token grouped tiles gain 3 % from counting (MoE pipeline 693 -> 672 us), the decode tiles lose 2 %
     // (gate_up at M = 64: 133 -> 136 us).
-    constexpr bool COUNTED = TOK > 64;
+    constexpr bool COUNTED = TOK > 64 && NG <= CPR;      // counting assumes every group has a chunk in every raw stage
     constexpr int CPG = CPR / NG > 0 ? CPR / NG : 1;
     int jj = 0, rs = grb % RS;
     uint32_t rpar = (uint32_t)(grb / RS) & 1u;
