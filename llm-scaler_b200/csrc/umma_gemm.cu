@@ -41,13 +41,12 @@ enum { ST_XFULL = 101, ST_AFULL = 102, ST_EMPTY = 103, ST_RAWFULL = 104, ST_RAWE
 struct Segment { int n0, c_begin, nk, strip, part, slot; };
 
 // constants of the fp16 magic-number nibble decode, handed to the kernel as parameters (see w4_word_magic)
-struct MagicConsts { uint32_t m_lo, m_hi, magic_lo, magic_hi, c1032, r16, m72; };
+struct MagicConsts { uint32_t magic_lo, magic_hi, m72; };
 // twos: the nibbles are two's complement (value, not value + 8).  Flipping their sign bits gives the offset form; the
 // flip is folded into the constant that is merged in: (w & m) ^ (0x6400 ^ flip) is 0x6400 | ((w ^ flip) & m) because
 // the 0x6400 bits and the nibble bits do not overlap.  No extra operation, no branch in the decode.
 __host__ __device__ inline MagicConsts magic_consts(bool twos) {
-  return MagicConsts{0x000F000Fu, 0x00F000F0u, 0x64006400u ^ (twos ? 0x00080008u : 0u), 0x64006400u ^ (twos ? 0x00800080u : 0u),
-                     0x64086408u, 0x2C002C00u, 0xD480D480u};
+  return MagicConsts{0x64006400u ^ (twos ? 0x00080008u : 0u), 0x64006400u ^ (twos ? 0x00800080u : 0u), 0xD480D480u};
 }
 
 struct UmmaWoParams {
@@ -128,33 +127,33 @@ __device__ __forceinline__ void w4_word(uint32_t w, uint32_t s2, float sf, bool 
 // (q - 8) * s is rounded to fp16 once.  Output pair order: (n0,n4) (n1,n5) (n2,n6) (n3,n7) where n_i is the
 // nibble at bits 4i; the activation pre-pass stores x in the matching order.  Integer work per word: one
 // shift and four LOP3 (the ALU pipe, not the FP pipes, is what bounds the int4 transform).
-// The six constants arrive through the kernel's parameter block (MagicConsts), not as literals: with literals the
-// compiler folds them into immediates, and since an instruction takes one immediate at most it then spends two logic
-// operations per mask-and-or and a register move per fused multiply-add (measured: 82 logic operations and 61 moves
-// per 64 k of a row where 32 and a handful are needed).
-__device__ __forceinline__ uint32_t and_xor(uint32_t a, uint32_t b, uint32_t c) {      // (a & b) ^ c in one operation
+// Where the constants live matters more than the arithmetic.  All of them as literals: the compiler folds them into
+// immediates, and since an instruction takes one immediate at most it then spends two logic operations per
+// mask-and-merge and a register move per fused multiply-add (measured: 82 logic operations and 61 moves per 64 k of a
+// row where 32 and a handful are needed).  All of them as kernel parameters: seven registers held through a loop that
+// has none to spare.  Hence one of each instruction's two constants as an immediate, the other in a register.
+__device__ __forceinline__ uint32_t and_xor_lo(uint32_t a, uint32_t c) {      // (a & 0x000F000F) ^ c: the mask as an immediate, c in a register
   uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0x6A;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  asm("lop3.b32 %0, %1, 0x000F000F, %2, 0x6A;" : "=r"(d) : "r"(a), "r"(c));
   return d;
 }
-// a, b, c or d for i = 0, 1, 2, anything else: three compares and three selects, never a branch (written as a
-// conditional expression the selection of a chunk's prefetched scale became a jump table with a dozen register moves)
-__device__ __forceinline__ uint32_t sel4(int i, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  uint32_t r;
-  asm("{\n\t.reg .pred p0, p1, p2;\n\tsetp.eq.s32 p0, %1, 0;\n\tsetp.eq.s32 p1, %1, 1;\n\tsetp.eq.s32 p2, %1, 2;\n\t"
-      "selp.u32 %0, %4, %5, p2;\n\tselp.u32 %0, %3, %0, p1;\n\tselp.u32 %0, %2, %0, p0;\n\t}"
-      : "=&r"(r) : "r"(i), "r"(a), "r"(b), "r"(c), "r"(d));
-  return r;
+__device__ __forceinline__ uint32_t and_xor_hi(uint32_t a, uint32_t c) {      // (a & 0x00F000F0) ^ c
+  uint32_t d;
+  asm("lop3.b32 %0, %1, 0x00F000F0, %2, 0x6A;" : "=r"(d) : "r"(a), "r"(c));
+  return d;
 }
+// An instruction takes ONE immediate: the masks, 1032 and 1/16 are written as literals, the merge constants (which depend
+// on the nibble encoding) and -72 come in registers.  Three registers of constants instead of seven.
 __device__ __forceinline__ void w4_word_magic(uint32_t w, uint32_t s2, const MagicConsts& k, uint32_t (&o)[4]) {
   const uint32_t w8 = w >> 8;
-  uint32_t v[4] = {and_xor(w, k.m_lo, k.magic_lo), and_xor(w, k.m_hi, k.magic_hi), and_xor(w8, k.m_lo, k.magic_lo), and_xor(w8, k.m_hi, k.magic_hi)};
+  uint32_t v[4] = {and_xor_lo(w, k.magic_lo), and_xor_hi(w, k.magic_hi), and_xor_lo(w8, k.magic_lo), and_xor_hi(w8, k.magic_hi)};
   const __half2 sc = *reinterpret_cast<const __half2*>(&s2);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     __half2 h = *reinterpret_cast<__half2*>(&v[i]);
-    if (i & 1) h = __hfma2(h, *reinterpret_cast<const __half2*>(&k.r16), *reinterpret_cast<const __half2*>(&k.m72));
-    else h = __hsub2(h, *reinterpret_cast<const __half2*>(&k.c1032));
+    const uint32_t c_r16 = 0x2C002C00u, c_1032 = 0x64086408u;
+    if (i & 1) h = __hfma2(h, *reinterpret_cast<const __half2*>(&c_r16), *reinterpret_cast<const __half2*>(&k.m72));      // h / 16 - 72
+    else h = __hsub2(h, *reinterpret_cast<const __half2*>(&c_1032));                                                     // h - 1032
     h = __hmul2(h, sc);
     o[i] = *reinterpret_cast<uint32_t*>(&h);
   }
