@@ -131,7 +131,18 @@ __device__ __forceinline__ void w4_word(uint32_t w, uint32_t s2, float sf, bool 
 // immediates, and since an instruction takes one immediate at most it then spends two logic operations per
 // mask-and-merge and a register move per fused multiply-add (measured: 82 logic operations and 61 moves per 64 k of a
 // row where 32 and a handful are needed).  All of them as kernel parameters: seven registers held through a loop that
-// has none to spare.  Hence one of each instruction's two constants as an immediate, the other in a register.
+// has none to spare.  Hence one of each instruction's two constants as an immediate, the other in a register
+// (and_xor_lo / and_xor_hi / w4_word_magic below).
+
+// a, b, c or d for i = 0, 1, 2, anything else: three compares and three selects, never a branch (written as a
+// conditional expression the selection of a chunk's prefetched scale became a jump table with a dozen register moves)
+__device__ __forceinline__ uint32_t sel4(int i, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  uint32_t r;
+  asm("{\n\t.reg .pred p0, p1, p2;\n\tsetp.eq.s32 p0, %1, 0;\n\tsetp.eq.s32 p1, %1, 1;\n\tsetp.eq.s32 p2, %1, 2;\n\t"
+      "selp.u32 %0, %4, %5, p2;\n\tselp.u32 %0, %3, %0, p1;\n\tselp.u32 %0, %2, %0, p0;\n\t}"
+      : "=&r"(r) : "r"(i), "r"(a), "r"(b), "r"(c), "r"(d));
+  return r;
+}
 __device__ __forceinline__ uint32_t and_xor_lo(uint32_t a, uint32_t c) {      // (a & 0x000F000F) ^ c: the mask as an immediate, c in a register
   uint32_t d;
   asm("lop3.b32 %0, %1, 0x000F000F, %2, 0x6A;" : "=r"(d) : "r"(a), "r"(c));
