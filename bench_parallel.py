@@ -47,6 +47,9 @@ def _max_over_ranks(v, world):
 
 def _timed(fn, iters, warm, world):
     """Eager calls, one sample per iteration; median over iterations of the slowest rank's time."""
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()          # ranks enter together: the peer-memory exchanges bound their waits (two seconds)
     for i in range(warm):
         fn(i)
     torch.cuda.synchronize()
@@ -65,6 +68,9 @@ def _timed(fn, iters, warm, world):
 def _timed_graph(fn, reps, iters, world):
     """Decode shapes: reps iterations (their exchange steps included) captured into one CUDA graph, every replay one
     sample, as a serving engine's decode loop runs them; no Python dispatch between the launches."""
+    if world > 1:
+        torch.cuda.synchronize()
+        dist.barrier()          # ranks enter together: the peer-memory exchanges bound their waits (two seconds)
     for i in range(3):
         fn(i)
     torch.cuda.synchronize()
